@@ -1,0 +1,190 @@
+/*
+ * moe_b200.h - C ABI of libmoe_b200.so: the MoE-layer forward pass of MixtureOfExperts.jl
+ * (router -> top-k -> dispatch -> GatedExpert FFN -> weighted combine -> Switch balance
+ * loss) as hand-written CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * The reference has no FFI today; its operator API is Julia multiple dispatch.  Each entry
+ * point below names the reference interface it stands in for (paths are relative to the
+ * reference project root).  Host bindings (Julia ccall, Python ctypes) sit on top of
+ * exactly these symbols; signatures use plain pointers and sizes only.
+ *
+ * Conventions
+ *   - Every function returns MOE_OK (0) or a negative MOE_ERR_* code; nothing throws, traps
+ *     or aborts across the boundary.  moe_last_error() gives the message for the calling
+ *     thread.
+ *   - Matrices follow the reference's memory: Julia arrays are column-major, so the
+ *     (input_dim x T) input is T contiguous token vectors, (k x T) index/gate arrays are
+ *     [T][k], (E x T) probability/logit arrays are [T][E], and the (output_dim x T) output
+ *     is [T][output_dim].
+ *   - A handle is not thread-safe (the reference layer mutates its own training_stats,
+ *     src/core/moe_layer.jl:153, so it is not re-entrant either); distinct handles are
+ *     independent.
+ *   - Device entry points enqueue all work on the caller's stream and return without
+ *     synchronising unless documented otherwise.  Caller-owned buffers must stay valid
+ *     until the stream reaches the end of the call.
+ *   - There is no CPU fallback: without a usable CUDA device every compute call fails
+ *     with MOE_ERR_CUDA.
+ */
+#ifndef MOE_B200_H
+#define MOE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------ */
+#define MOE_OK                 0
+#define MOE_ERR_INVALID       -1   /* bad argument (the reference raises ArgumentError / error()) */
+#define MOE_ERR_CUDA          -2   /* a CUDA runtime/driver call failed or no device */
+#define MOE_ERR_UNSUPPORTED   -3   /* valid request this build does not implement */
+#define MOE_ERR_STATE         -4   /* weights not set, EP not initialised, ... */
+#define MOE_ERR_TIMEOUT       -5   /* a bounded device-side wait gave up (status word set) */
+#define MOE_ERR_NCCL          -6   /* an NCCL call failed */
+
+/* ---- enums (int32 in moe_config_t) ------------------------------------------------- */
+/* gate_kind: which compute_gates method runs after the router GEMM */
+#define MOE_GATE_TOPK          0   /* TopKGating(k)            src/gating/topk.jl:16-44      */
+#define MOE_GATE_SWITCH        1   /* SwitchGating() = top-1   src/gating/switch.jl:7-11     */
+#define MOE_GATE_SHARED_TOPK   2   /* SharedExpertGating(S, TopKGating(k), E)
+                                      src/gating/advanced.jl:74-108 */
+/* activation of GatedExpert (MoEConfig.activation, src/core/moe_layer.jl:10) */
+#define MOE_ACT_SILU           0   /* x*sigmoid(x)  src/experts/gated.jl:36 */
+#define MOE_ACT_GELU_TANH      1   /* NNlib.gelu (tanh approximation) */
+#define MOE_ACT_RELU           2
+#define MOE_ACT_IDENTITY       3
+/* element types */
+#define MOE_DTYPE_F32          0
+#define MOE_DTYPE_BF16         1
+/* compute_dtype: MOE_DTYPE_F32  = FP32 FMA on CUDA cores (1e-5 parity class)
+ *                MOE_DTYPE_BF16 = BF16 operands on tcgen05 tensor cores, FP32 accumulate */
+/* shared_mode */
+#define MOE_SHARED_NONE        0
+#define MOE_SHARED_GATING      1   /* via SharedExpertGating: experts 1..S are always selected */
+#define MOE_SHARED_LAYER_BLEND 2   /* MoEConfig.num_shared_experts>0:
+                                      forward_with_shared_experts, src/core/moe_layer.jl:158-185 */
+/* memory layout of a weight matrix W with logical shape (out x in), y = W*x */
+#define MOE_LAYOUT_IN_CONTIG   0   /* [out][in], in fastest: Llama2.jl (in x out) column-major
+                                      (src/llama2/conversion.jl:277-331), NumPy (out,in) C-order */
+#define MOE_LAYOUT_OUT_CONTIG  1   /* [in][out], out fastest: Flux Dense.weight (out x in)
+                                      column-major (src/experts/gated.jl:18-24) */
+
+/* Mirror of the MoEConfig fields the forward pass reads (src/core/moe_layer.jl:4-29). */
+typedef struct moe_config {
+    int32_t num_experts;      /* E, shared experts included */
+    int32_t num_shared;       /* S (0 unless shared_mode != NONE) */
+    int32_t top_k;            /* k of the routed gate (gate_type.k; MoEConfig.top_k is not read) */
+    int32_t input_dim;        /* D */
+    int32_t hidden_dim;       /* H */
+    int32_t output_dim;       /* O */
+    int32_t gate_kind;        /* MOE_GATE_*   */
+    int32_t activation;       /* MOE_ACT_*    */
+    int32_t compute_dtype;    /* MOE_DTYPE_*  */
+    int32_t shared_mode;      /* MOE_SHARED_* */
+    float   balance_alpha;    /* SwitchTransformerLoss(alpha), src/balancing/losses.jl:11-36 */
+    float   z_loss_weight;    /* MoEConfig.z_loss_weight (added when training), moe_layer.jl:117-121 */
+    int32_t index_base;       /* 0 or 1: base of expert ids written to `indices` (Julia: 1) */
+    int32_t bias_gates_only;  /* 1: logit_bias changes indices/gates but not probs (the
+                                 AuxiliaryFreeLoss hook, moe_layer.jl:137-140); 0: bias is
+                                 part of the logits (a Dense router with bias) */
+} moe_config_t;
+
+typedef struct moe_layer moe_layer_t;   /* opaque: one per (layer, device) */
+
+/* Optional outputs of a forward call; every pointer may be NULL.  Device pointers for
+ * moe_layer_forward, host pointers for moe_layer_forward_host. */
+typedef struct moe_forward_outputs {
+    float*   loss;               /* [1]   balance loss (+ z-loss), 0 when training==0          */
+    int32_t* indices;            /* [T][k_tot] expert ids, index_base-based                   */
+    float*   gates;              /* [T][k_tot]                                                 */
+    float*   probs;              /* [T][E_probs]   router_probs                                */
+    float*   logits;             /* [T][E_router]  router_logits                               */
+    int64_t* tokens_per_expert;  /* [E]  counts of THIS call (training_stats[:tokens_per_expert]
+                                         accumulates them, src/core/moe_layer.jl:250-264)      */
+    float*   routing_entropy;    /* [1]  mean_t(-sum_i p*log(p+1e-8))                          */
+} moe_forward_outputs_t;
+
+/* ---- lifecycle --------------------------------------------------------------------- */
+
+/* MoELayer(config) (src/core/moe_layer.jl:44-63) / create_cuda_moe (src/cuda/utils.jl).
+ * Validates the config, binds the handle to CUDA device `device`, allocates weight storage. */
+int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out);
+
+/* Stands in for the weight copy of to_cuda / create_synchronized_moe_pair
+ * (src/cuda/utils.jl:4-15, src/amdgpu/utils.jl:62-105): copies and repacks the three
+ * matrices of expert `expert` (0-based) into the handle; the caller's arrays may be freed
+ * after return.  w1,w3: (H x D); w2: (O x H).  src_dtype MOE_DTYPE_*; layout MOE_LAYOUT_*;
+ * src_is_device != 0 if the pointers are device pointers on the handle's device.
+ * Synchronises the device before returning. */
+int moe_layer_set_expert(moe_layer_t*, int expert, const void* w1, const void* w2, const void* w3,
+                         int src_dtype, int layout, int src_is_device);
+
+/* Router.weight (src/core/router.jl:14-23): FP32 (E_router x D), E_router = E - S.
+ * logit_bias: optional FP32 [E_router] added to the logits (see bias_gates_only). */
+int moe_layer_set_router(moe_layer_t*, const float* w, const float* logit_bias,
+                         int layout, int src_is_device);
+
+/* Number of values per token in indices/gates (k_tot), probs (E_probs), logits (E_router). */
+int moe_layer_dims(const moe_layer_t*, int32_t* k_tot, int32_t* e_probs, int32_t* e_router);
+
+/* (moe::MoELayer)(x; training) (src/core/moe_layer.jl:107-128) and cuda_moe_forward!
+ * (src/cuda/layer.jl:3-32) on device buffers.  x: [T][D] of x_dtype; out: [T][O] FP32.
+ * Workspace grows to the largest T seen (no 1024-token cap); growing it synchronises. */
+int moe_layer_forward(moe_layer_t*, const void* x, int x_dtype, int64_t T, int training,
+                      float* out, const moe_forward_outputs_t* opt, void* cuda_stream);
+
+/* Same call with HOST buffers: stages x host->device, runs the layer, copies the results
+ * back and synchronises.  This is the path the per-token Llama2 glue uses
+ * (moe_ffn_forward!, src/llama2/inference.jl:58-121). */
+int moe_layer_forward_host(moe_layer_t*, const void* x, int x_dtype, int64_t T, int training,
+                           float* out, const moe_forward_outputs_t* opt);
+
+/* compute_gates(gate, logits) (src/gating/base.jl:22, topk.jl:24-44, advanced.jl:80-108) as a
+ * stand-alone device operator: logits [T][E] FP32 in; indices/gates/probs out (nullable). */
+int moe_compute_gates(int gate_kind, int num_experts, int num_shared, int top_k, int index_base,
+                      const float* logits, int64_t T,
+                      int32_t* indices, float* gates, float* probs, void* cuda_stream);
+
+/* compute_loss(SwitchTransformerLoss(alpha), indices, probs) (src/balancing/losses.jl:15-36)
+ * plus z_weight * mean(logsumexp(logits)^2) when logits != NULL (losses.jl:103-114).
+ * indices [T][k] (index_base-based), probs [T][n_probs]; writes one FP32 to `loss` (device). */
+int moe_compute_loss(float alpha, float z_weight, int n_probs, int k, int index_base,
+                     const int32_t* indices, const float* probs, const float* logits,
+                     int n_logits, int64_t T, float* loss, void* cuda_stream);
+
+/* Device time in milliseconds of each stage of the handle's last forward call, in order
+ * {router, scan+loss, permute, gemm1, gemm2, combine, exchange}; only recorded after
+ * moe_layer_set_profiling(h, 1).  Synchronises on the recorded events. */
+int moe_layer_set_profiling(moe_layer_t*, int enabled);
+int moe_layer_last_stage_ms(moe_layer_t*, float ms[7]);
+
+/* Number of kernel launches of this library issued through the handle since creation. */
+int64_t moe_layer_launch_count(const moe_layer_t*);
+
+/* Value of the device status word after the last synchronising call (0 = clean). */
+int moe_layer_device_status(moe_layer_t*, int32_t* status);
+
+/* ---- expert parallelism (no counterpart in the reference: it has no communication layer) */
+
+/* Fill `id128` (128 bytes) with a fresh NCCL unique id; rank 0 calls it and ships the
+ * bytes to the other ranks by any host channel. */
+int moe_ep_unique_id(void* id128);
+
+/* Joins the handle to an expert-parallel group of `world` ranks (one process per GPU).
+ * Experts are block-partitioned: rank r owns experts [r*E/world, (r+1)*E/world); only those
+ * need moe_layer_set_expert.  Tokens stay data-parallel; the router is replicated.
+ * After this, moe_layer_forward dispatches token rows with an all-to-all over NVLink,
+ * runs the local experts, returns the rows with a second all-to-all and combines them;
+ * the balance loss is reduced over all ranks' tokens. */
+int moe_ep_init(moe_layer_t*, const void* id128, int rank, int world);
+
+int moe_layer_destroy(moe_layer_t*);
+
+const char* moe_last_error(void);     /* thread-local message of the last failure */
+const char* moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H */

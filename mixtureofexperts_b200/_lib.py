@@ -1,0 +1,97 @@
+"""ctypes binding of libmoe_b200.so (declared in include/moe_b200.h).
+
+There is no CPU fallback: importing this module without the built shared library raises, and
+every compute call fails with MoEError when no sm_100 device is present.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmoe_b200.so"
+
+# status codes
+OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_STATE, ERR_TIMEOUT, ERR_NCCL = 0, -1, -2, -3, -4, -5, -6
+# enums
+GATE_TOPK, GATE_SWITCH, GATE_SHARED_TOPK = 0, 1, 2
+ACT_SILU, ACT_GELU_TANH, ACT_RELU, ACT_IDENTITY = 0, 1, 2, 3
+DTYPE_F32, DTYPE_BF16 = 0, 1
+SHARED_NONE, SHARED_GATING, SHARED_LAYER_BLEND = 0, 1, 2
+LAYOUT_IN_CONTIG, LAYOUT_OUT_CONTIG = 0, 1
+
+EXPORTS = [
+    "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_router", "moe_layer_dims",
+    "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_loss",
+    "moe_layer_set_profiling", "moe_layer_last_stage_ms", "moe_layer_launch_count",
+    "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_layer_destroy",
+    "moe_last_error", "moe_version",
+]
+
+
+class MoEError(RuntimeError):
+    """Raised for any non-zero status of the C ABI (the reference raises error()/ArgumentError)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[moe_b200 {code}] {message}")
+        self.code = code
+
+
+class MoeConfig(C.Structure):
+    _fields_ = [
+        ("num_experts", C.c_int32), ("num_shared", C.c_int32), ("top_k", C.c_int32),
+        ("input_dim", C.c_int32), ("hidden_dim", C.c_int32), ("output_dim", C.c_int32),
+        ("gate_kind", C.c_int32), ("activation", C.c_int32), ("compute_dtype", C.c_int32),
+        ("shared_mode", C.c_int32), ("balance_alpha", C.c_float), ("z_loss_weight", C.c_float),
+        ("index_base", C.c_int32), ("bias_gates_only", C.c_int32),
+    ]
+
+
+class ForwardOutputs(C.Structure):
+    _fields_ = [
+        ("loss", C.c_void_p), ("indices", C.c_void_p), ("gates", C.c_void_p), ("probs", C.c_void_p),
+        ("logits", C.c_void_p), ("tokens_per_expert", C.c_void_p), ("routing_entropy", C.c_void_p),
+    ]
+
+
+def _load():
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m mixtureofexperts_b200.build` "
+            "(this package has no CPU or PyTorch fallback)")
+    lib = C.CDLL(str(LIB_PATH))
+    vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
+    lib.moe_layer_create.argtypes = [C.POINTER(MoeConfig), i32, C.POINTER(vp)]
+    lib.moe_layer_set_expert.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32]
+    lib.moe_layer_set_router.argtypes = [vp, vp, vp, i32, i32]
+    lib.moe_layer_dims.argtypes = [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.moe_layer_forward.argtypes = [vp, vp, i32, i64, i32, vp, C.POINTER(ForwardOutputs), vp]
+    lib.moe_layer_forward_host.argtypes = [vp, vp, i32, i64, i32, vp, C.POINTER(ForwardOutputs)]
+    lib.moe_compute_gates.argtypes = [i32, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
+    lib.moe_compute_loss.argtypes = [f32, f32, i32, i32, i32, vp, vp, vp, i32, i64, vp, vp]
+    lib.moe_layer_set_profiling.argtypes = [vp, i32]
+    lib.moe_layer_last_stage_ms.argtypes = [vp, C.POINTER(C.c_float)]
+    lib.moe_layer_launch_count.argtypes = [vp]
+    lib.moe_layer_launch_count.restype = C.c_int64
+    lib.moe_layer_device_status.argtypes = [vp, C.POINTER(C.c_int32)]
+    lib.moe_ep_unique_id.argtypes = [vp]
+    lib.moe_ep_init.argtypes = [vp, vp, i32, i32]
+    lib.moe_layer_destroy.argtypes = [vp]
+    lib.moe_last_error.restype = C.c_char_p
+    lib.moe_version.restype = C.c_char_p
+    for name in EXPORTS:
+        fn = getattr(lib, name)
+        if name not in ("moe_last_error", "moe_version", "moe_layer_launch_count"):
+            fn.restype = C.c_int
+    return lib
+
+
+lib = _load()
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise MoEError(code, lib.moe_last_error().decode("utf-8", "replace"))
+
+
+def version() -> str:
+    return lib.moe_version().decode()

@@ -1,0 +1,156 @@
+// Shared declarations of libmoe_b200: launch-parameter structs, device status codes and the
+// host-side launcher prototypes of every kernel file.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/moe_b200.h"
+
+namespace moe {
+
+// ---- device status word (one int32 per handle) ---------------------------------------------
+// 0 = clean.  Kernels never trap; a kernel that gives up writes one of these and returns.
+enum : int32_t {
+    DEV_OK = 0,
+    DEV_TIMEOUT_TMA_FULL = 1,    // MMA warp waited too long for a TMA stage
+    DEV_TIMEOUT_SMEM_EMPTY = 2,  // TMA warp waited too long for a free stage
+    DEV_TIMEOUT_TMEM_FULL = 3,   // epilogue waited too long for an accumulator
+    DEV_TIMEOUT_TMEM_EMPTY = 4,  // MMA warp waited too long for a drained accumulator
+    DEV_BAD_INDEX = 5,           // an index check failed (recorded, access skipped)
+};
+
+constexpr int ROUTER_THREADS = 256;
+constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
+constexpr int ROUTER_KC = 128;          // K chunk: one float4 per lane
+constexpr int MAX_ROUTER_EXPERTS = 128; // upper bound on router rows
+constexpr int MAX_EXPERTS = 256;        // upper bound on experts per layer
+constexpr int MAX_KTOT = 16;            // upper bound on selected experts per token
+
+// Tile height of the grouped GEMMs: an expert's rows are cut into tiles of this many rows.
+constexpr int TC_TILE_M = 128;   // tcgen05 path
+constexpr int F32_TILE_M = 16;   // FP32 SIMT path
+
+struct RouterParams {
+    const void* x;            // [T][D]
+    const float* w;           // [E_router][D]
+    const float* bias;        // [E_router] or null
+    int64_t T;
+    int D;
+    int E;                    // layer experts (shared included)
+    int E_router;             // router rows
+    int E_probs;              // columns of probs (E for NONE/GATING, E_router for LAYER_BLEND)
+    int S;                    // shared experts
+    int k;                    // routed experts per token
+    int k_tot;                // S + k
+    int shared_mode;
+    int bias_gates_only;
+    int index_base;
+    int tokens_per_cta;       // 8 warps * tokens per warp pass
+    int want_entropy;
+    // internal results
+    int32_t* idx;             // [T][k_tot] layer expert id, 0-based
+    float* gate;              // [T][k_tot] combine-ready gate
+    int32_t* cta_counts;      // [num_cta][E]
+    float* cta_psum;          // [num_cta][E_probs + 1]: prob sums, then sum of lse^2
+    double* cta_entropy;      // [num_cta]
+    // user outputs (nullable)
+    int32_t* u_idx;
+    float* u_gate;
+    float* u_probs;
+    float* u_logits;
+};
+
+struct ScanParams {
+    int64_t T;
+    int E, E_probs, S, k, k_tot, shared_mode;
+    int num_cta;
+    int tile_m;
+    int training;
+    float alpha, z_weight;
+    int32_t* cta_counts;      // in: per-CTA counts; out: exclusive prefix over CTAs
+    const float* cta_psum;
+    const double* cta_entropy;
+    int32_t* expert_count;    // [E]
+    int32_t* expert_offset;   // [E+1] first permuted row of each expert
+    int32_t* tile_prefix;     // [E+1] first m-tile of each expert
+    float* loss_internal;     // [1]
+    // user outputs (nullable, device)
+    float* u_loss;
+    int64_t* u_tokens_per_expert;
+    float* u_entropy;
+    // expert-parallel: when non-null the loss is finished later from all ranks' sums
+    float* ep_sums;           // [E + E_probs + 3]: counts, prob sums, sum lse^2, T, entropy sum
+};
+
+struct PermuteParams {
+    const void* x;            // [T][D]
+    void* xp;                 // [P][D]
+    int64_t T;
+    int D, E, k_tot;
+    int tokens_per_cta;
+    const int32_t* idx;
+    const int32_t* cta_base;      // [num_cta][E] exclusive prefix over CTAs
+    const int32_t* expert_offset; // [E+1]
+    int32_t* pair_pos;            // [T][k_tot] permuted row of each pair
+    int32_t* row_token;           // [P]
+    int32_t* status;
+    int64_t P_cap;
+};
+
+struct CombineParams {
+    const void* y;            // [P][O]
+    float* out;               // [T][O]
+    int64_t T;
+    int O, k_tot;
+    const int32_t* idx;
+    const float* gate;
+    const int32_t* pair_pos;
+};
+
+// Grouped GEMM over the permuted rows: C[r][n] = sum_k A[r][k] * B[e(r)][n][k].
+struct GroupGemmParams {
+    const void* A;            // [P][K]
+    const void* B0;           // [E][N][K]  (w1 for mode 1, w2 for mode 2)
+    const void* B1;           // [E][N][K]  (w3 for mode 1, unused for mode 2)
+    void* C;                  // [P][N]
+    int N, K, E;
+    int activation;
+    const int32_t* expert_offset; // [E+1]
+    const int32_t* tile_prefix;   // [E+1]
+    int32_t* status;
+};
+
+// ---- launchers (each returns the number of kernels it launched, or <0 on a launch error) ---
+int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s);
+int router_tokens_per_cta(int e_router);
+int launch_scan(const ScanParams& p, cudaStream_t s);
+int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s);
+int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s);
+int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, cudaStream_t s);
+int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const float* logits, int64_t T,
+                      int32_t* indices, float* gates, float* probs, cudaStream_t s);
+int launch_loss_only(float alpha, float z_weight, int n_probs, int k, int index_base, const int32_t* indices,
+                     const float* probs, const float* logits, int n_logits, int64_t T, float* loss,
+                     cudaStream_t s);
+int launch_transpose_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int rows_out,
+                             int cols_out, int src_is_transposed, cudaStream_t s);
+
+// tcgen05 path (expert_tc.cu)
+struct TcGemmPlan;  // tensor maps + geometry, owned by the handle
+TcGemmPlan* tc_plan_create();
+void tc_plan_destroy(TcGemmPlan*);
+// (re)encodes the tensor maps; returns 0 or a negative MOE_ERR_* (message via out_msg)
+int tc_plan_encode(TcGemmPlan*, const void* xp, const void* h, int64_t P_cap, int D, int H, int O, int E,
+                   const void* w1, const void* w3, const void* w2, const char** out_msg);
+int launch_group_gemm_tc(const TcGemmPlan*, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
+                         cudaStream_t s);
+
+__host__ __device__ inline float bf16_bits_to_float(uint16_t b) {
+    union { uint32_t u; float f; } v;
+    v.u = ((uint32_t)b) << 16;
+    return v.f;
+}
+
+}  // namespace moe

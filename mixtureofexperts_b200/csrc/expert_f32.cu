@@ -1,0 +1,146 @@
+// Grouped GatedExpert FFN in FP32 on CUDA cores (the 1e-5 parity class): real FP32 FMAs, no
+// TF32/BF16 tensor cores.  Mode 1: h = act(A*W1^T) .* (A*W3^T); mode 2: y = h*W2^T -- the
+// three products of (expert::GatedExpert)(x) (src/experts/gated.jl:29-34,
+// src/llama2/inference.jl:154-167; src/cuda/experts.jl:20-26 ran them as three cuBLAS SGEMMs
+// on ALL tokens for every expert).
+//
+// Rows of the permuted buffer are grouped by expert; an m-tile (F32_TILE_M rows) never spans
+// two experts.  Weights are [E][N][K], K contiguous.  At the small per-expert row counts this
+// path serves, the kernel is bound by streaming the expert weights from HBM once.
+#include "activation.cuh"
+
+namespace moe {
+namespace {
+
+constexpr int BM = F32_TILE_M;  // 16
+constexpr int BN = 128;
+constexpr int BK = 32;
+constexpr int THREADS = 256;
+
+__device__ __forceinline__ float4 ldg4(const float* row, int kk, int K, bool vec) {
+    if (vec && kk + 3 < K) return __ldg(reinterpret_cast<const float4*>(row + kk));
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (kk + 0 < K) v.x = row[kk + 0];
+    if (kk + 1 < K) v.y = row[kk + 1];
+    if (kk + 2 < K) v.z = row[kk + 2];
+    if (kk + 3 < K) v.w = row[kk + 3];
+    return v;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemmParams p) {
+    constexpr int NB = (MODE == 1) ? 2 : 1;
+    __shared__ float As[BM][BK];
+    __shared__ float Bs[NB][BN][BK + 1];
+
+    const int mtile = blockIdx.x;
+    if (mtile >= p.tile_prefix[p.E]) return;
+    const int e = find_segment(p.tile_prefix, p.E, mtile);
+    const int row0 = p.expert_offset[e] + (mtile - p.tile_prefix[e]) * BM;
+    const int row_end = p.expert_offset[e + 1];
+    const int n0 = blockIdx.y * BN;
+
+    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    const float* A = reinterpret_cast<const float*>(p.A);
+    const float* Bm[2] = {reinterpret_cast<const float*>(p.B0) + (size_t)e * p.N * p.K,
+                          MODE == 1 ? reinterpret_cast<const float*>(p.B1) + (size_t)e * p.N * p.K : nullptr};
+    const bool vec = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.A) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.B0) & 15) == 0) &&
+                     (MODE != 1 || (reinterpret_cast<uintptr_t>(p.B1) & 15) == 0);
+
+    // global -> register staging (prefetch of the next K block while the current one computes)
+    float4 a_reg = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 b_reg[NB][4];
+    const int a_row = tid >> 3, a_c4 = tid & 7;  // threads 0..127 load A: 16 rows x 8 float4
+    auto load_tiles = [&](int k0) {
+        if (tid < BM * (BK / 4)) {
+            const int r = row0 + a_row;
+            a_reg = (r < row_end) ? ldg4(A + (size_t)r * p.K, k0 + a_c4 * 4, p.K, vec)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = tid + i * THREADS;
+                const int n = n0 + (idx >> 3), c4 = idx & 7;
+                b_reg[b][i] = (n < p.N) ? ldg4(Bm[b] + (size_t)n * p.K, k0 + c4 * 4, p.K, vec)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+    };
+    auto store_tiles = [&]() {
+        if (tid < BM * (BK / 4)) {
+            As[a_row][a_c4 * 4 + 0] = a_reg.x;
+            As[a_row][a_c4 * 4 + 1] = a_reg.y;
+            As[a_row][a_c4 * 4 + 2] = a_reg.z;
+            As[a_row][a_c4 * 4 + 3] = a_reg.w;
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = tid + i * THREADS;
+                const int n = idx >> 3, c4 = idx & 7;
+                Bs[b][n][c4 * 4 + 0] = b_reg[b][i].x;
+                Bs[b][n][c4 * 4 + 1] = b_reg[b][i].y;
+                Bs[b][n][c4 * 4 + 2] = b_reg[b][i].z;
+                Bs[b][n][c4 * 4 + 3] = b_reg[b][i].w;
+            }
+    };
+
+    float acc[NB][2][4];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[b][r][i] = 0.f;
+
+    load_tiles(0);
+    for (int k0 = 0; k0 < p.K; k0 += BK) {
+        __syncthreads();
+        store_tiles();
+        __syncthreads();
+        if (k0 + BK < p.K) load_tiles(k0 + BK);
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            const float a0 = As[ty * 2 + 0][k], a1 = As[ty * 2 + 1][k];
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float w = Bs[b][tx + 32 * i][k];
+                    acc[b][0][i] = fmaf(a0, w, acc[b][0][i]);
+                    acc[b][1][i] = fmaf(a1, w, acc[b][1][i]);
+                }
+        }
+    }
+
+    float* C = reinterpret_cast<float*>(p.C);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + ty * 2 + r;
+        if (row >= row_end) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int n = n0 + tx + 32 * i;
+            if (n >= p.N) continue;
+            float v;
+            if (MODE == 1) v = apply_act(p.activation, acc[0][r][i]) * acc[NB - 1][r][i];
+            else v = acc[0][r][i];
+            C[(size_t)row * p.N + n] = v;
+        }
+    }
+}
+
+}  // namespace
+
+int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, cudaStream_t s) {
+    if (max_mtiles <= 0) return 0;
+    dim3 grid(max_mtiles, (p.N + BN - 1) / BN);
+    if (mode == 1) group_gemm_f32_kernel<1><<<grid, THREADS, 0, s>>>(p);
+    else group_gemm_f32_kernel<2><<<grid, THREADS, 0, s>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+}  // namespace moe

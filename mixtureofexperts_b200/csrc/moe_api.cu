@@ -1,0 +1,757 @@
+// C ABI of libmoe_b200 (declared in include/moe_b200.h): handle lifecycle, weight repack,
+// workspace management and the forward pipeline
+//     router -> scan+loss -> permute -> grouped GEMM 1 (gate/up + act) -> grouped GEMM 2 -> combine
+// that replaces (moe::MoELayer)(x; training) (src/core/moe_layer.jl:107-156) and
+// cuda_moe_forward! (src/cuda/layer.jl:3-32).  No CPU fallback exists in this file: every
+// compute entry point fails with MOE_ERR_CUDA when the device is unusable.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "ep.h"
+
+using namespace moe;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                                   \
+    do {                                                                                                 \
+        cudaError_t _e = (expr);                                                                         \
+        if (_e != cudaSuccess) return fail(MOE_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+size_t dtype_size(int d) { return d == MOE_DTYPE_BF16 ? 2 : 4; }
+
+template <typename T>
+int dev_alloc(T** p, size_t n) {
+    *p = nullptr;
+    if (n == 0) n = 1;
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(p), n * sizeof(T)));
+    return MOE_OK;
+}
+template <typename T>
+void dev_free(T*& p) {
+    if (p) cudaFree(p);
+    p = nullptr;
+}
+
+}  // namespace
+
+struct moe_layer {
+    moe_config_t cfg;
+    int device = 0;
+    int num_sms = 0;
+    int E = 0, S = 0, k = 0, k_tot = 0, E_router = 0, E_probs = 0;
+    int tokens_per_cta = 0;
+    // expert range held by this handle ([0,E) unless expert-parallel)
+    int e_lo = 0, e_hi = 0;
+
+    // weights in the compute dtype, [E_local][out][in]
+    void* w1 = nullptr;
+    void* w3 = nullptr;
+    void* w2 = nullptr;
+    float* router_w = nullptr;   // [E_router][D]
+    float* router_bias = nullptr;
+    bool has_bias = false, router_set = false;
+    std::vector<char> expert_set;
+    void* stage_w = nullptr;     // device staging for host-side weight sources
+    size_t stage_w_bytes = 0;
+
+    // workspace (sized for T_cap tokens)
+    int64_t T_cap = 0;
+    int64_t P_cap = 0;
+    int32_t* idx = nullptr;
+    float* gate = nullptr;
+    int32_t* pair_pos = nullptr;
+    int32_t* row_token = nullptr;
+    int32_t* cta_counts = nullptr;
+    float* cta_psum = nullptr;
+    double* cta_entropy = nullptr;
+    int32_t* expert_count = nullptr;
+    int32_t* expert_offset = nullptr;
+    int32_t* tile_prefix = nullptr;
+    float* loss_dev = nullptr;
+    void* xp = nullptr;
+    void* h = nullptr;
+    void* y = nullptr;
+    int32_t* status = nullptr;
+    TcGemmPlan* plan = nullptr;
+    bool plan_dirty = true;
+
+    // host-call staging
+    cudaStream_t stream = nullptr;
+    void* hx = nullptr;
+    size_t hx_bytes = 0;
+    float* hout = nullptr;
+    size_t hout_bytes = 0;
+    void* hopt = nullptr;
+    size_t hopt_bytes = 0;
+
+    // profiling
+    bool profiling = false;
+    cudaEvent_t ev[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool ev_valid = false;
+    int64_t launches = 0;
+
+    EpState* ep = nullptr;
+};
+
+namespace {
+
+int validate_config(const moe_config_t& c) {
+    if (c.num_experts < 1 || c.num_experts > MAX_EXPERTS)
+        return fail(MOE_ERR_INVALID, "num_experts must be in 1..%d (got %d)", MAX_EXPERTS, c.num_experts);
+    if (c.input_dim < 1 || c.hidden_dim < 1 || c.output_dim < 1)
+        return fail(MOE_ERR_INVALID, "input_dim, hidden_dim and output_dim must be positive");
+    if (c.gate_kind < MOE_GATE_TOPK || c.gate_kind > MOE_GATE_SHARED_TOPK)
+        return fail(MOE_ERR_INVALID, "unknown gate_kind %d", c.gate_kind);
+    if (c.activation < MOE_ACT_SILU || c.activation > MOE_ACT_IDENTITY)
+        return fail(MOE_ERR_INVALID, "unknown activation %d", c.activation);
+    if (c.compute_dtype != MOE_DTYPE_F32 && c.compute_dtype != MOE_DTYPE_BF16)
+        return fail(MOE_ERR_INVALID, "unknown compute_dtype %d", c.compute_dtype);
+    if (c.shared_mode < MOE_SHARED_NONE || c.shared_mode > MOE_SHARED_LAYER_BLEND)
+        return fail(MOE_ERR_INVALID, "unknown shared_mode %d", c.shared_mode);
+    if (c.index_base != 0 && c.index_base != 1) return fail(MOE_ERR_INVALID, "index_base must be 0 or 1");
+    if ((c.gate_kind == MOE_GATE_SHARED_TOPK) != (c.shared_mode == MOE_SHARED_GATING))
+        return fail(MOE_ERR_INVALID, "gate_kind SHARED_TOPK and shared_mode GATING go together");
+    if (c.shared_mode == MOE_SHARED_NONE && c.num_shared != 0)
+        return fail(MOE_ERR_INVALID, "num_shared must be 0 when shared_mode is NONE");
+    if (c.shared_mode != MOE_SHARED_NONE && (c.num_shared < 1 || c.num_shared >= c.num_experts))
+        return fail(MOE_ERR_INVALID, "num_shared must be in 1..num_experts-1 for this shared_mode");
+    const int k = (c.gate_kind == MOE_GATE_SWITCH) ? 1 : c.top_k;
+    const int e_router = c.shared_mode == MOE_SHARED_LAYER_BLEND ? c.num_experts - c.num_shared : c.num_experts;
+    const int routed = c.shared_mode == MOE_SHARED_GATING ? c.num_experts - c.num_shared : e_router;
+    if (k < 1 || k > routed) return fail(MOE_ERR_INVALID, "top_k must be in 1..%d (got %d)", routed, k);
+    if (k + c.num_shared > MAX_KTOT)
+        return fail(MOE_ERR_UNSUPPORTED, "more than %d selected experts per token", MAX_KTOT);
+    if (e_router > MAX_ROUTER_EXPERTS)
+        return fail(MOE_ERR_UNSUPPORTED, "more than %d router rows", MAX_ROUTER_EXPERTS);
+    if (c.compute_dtype == MOE_DTYPE_BF16 && (c.input_dim % 8 || c.hidden_dim % 8))
+        return fail(MOE_ERR_UNSUPPORTED,
+                    "the BF16 tensor-core path needs input_dim and hidden_dim to be multiples of 8");
+    return MOE_OK;
+}
+
+int ensure_weights(moe_layer* L) {
+    if (L->w1) return MOE_OK;
+    const size_t el = dtype_size(L->cfg.compute_dtype);
+    const size_t n_local = (size_t)(L->e_hi - L->e_lo);
+    const size_t D = L->cfg.input_dim, H = L->cfg.hidden_dim, O = L->cfg.output_dim;
+    CUDA_TRY(cudaMalloc(&L->w1, n_local * H * D * el));
+    CUDA_TRY(cudaMalloc(&L->w3, n_local * H * D * el));
+    CUDA_TRY(cudaMalloc(&L->w2, n_local * O * H * el));
+    L->expert_set.assign(n_local, 0);
+    L->plan_dirty = true;
+    return MOE_OK;
+}
+
+void free_workspace(moe_layer* L) {
+    dev_free(L->idx);
+    dev_free(L->gate);
+    dev_free(L->pair_pos);
+    dev_free(L->row_token);
+    dev_free(L->cta_counts);
+    dev_free(L->cta_psum);
+    dev_free(L->cta_entropy);
+    dev_free(L->xp);
+    dev_free(L->h);
+    dev_free(L->y);
+    L->T_cap = 0;
+    L->P_cap = 0;
+}
+
+// Buffers whose size follows the number of local tokens.
+int ensure_workspace(moe_layer* L, int64_t T) {
+    if (T <= L->T_cap) return MOE_OK;
+    CUDA_TRY(cudaDeviceSynchronize());
+    free_workspace(L);
+    const int64_t P = T * L->k_tot;
+    const int64_t num_cta = (T + L->tokens_per_cta - 1) / L->tokens_per_cta;
+    const size_t el = dtype_size(L->cfg.compute_dtype);
+    int rc;
+    if ((rc = dev_alloc(&L->idx, (size_t)P))) return rc;
+    if ((rc = dev_alloc(&L->gate, (size_t)P))) return rc;
+    if ((rc = dev_alloc(&L->pair_pos, (size_t)P))) return rc;
+    if ((rc = dev_alloc(&L->row_token, (size_t)P))) return rc;
+    if ((rc = dev_alloc(&L->cta_counts, (size_t)num_cta * L->E))) return rc;
+    if ((rc = dev_alloc(&L->cta_psum, (size_t)num_cta * (L->E_probs + 1)))) return rc;
+    if ((rc = dev_alloc(&L->cta_entropy, (size_t)num_cta))) return rc;
+    CUDA_TRY(cudaMalloc(&L->xp, (size_t)P * L->cfg.input_dim * el));
+    if (!L->ep) {
+        // with expert parallelism the GEMMs run on the receive buffers owned by the EP state
+        CUDA_TRY(cudaMalloc(&L->h, (size_t)P * L->cfg.hidden_dim * el));
+    }
+    CUDA_TRY(cudaMalloc(&L->y, (size_t)P * L->cfg.output_dim * el));
+    L->T_cap = T;
+    L->P_cap = P;
+    L->plan_dirty = true;
+    return MOE_OK;
+}
+
+int ensure_plan(moe_layer* L, const void* a1, const void* a2, int64_t rows) {
+    if (L->cfg.compute_dtype != MOE_DTYPE_BF16) return MOE_OK;
+    if (!L->plan) L->plan = tc_plan_create();
+    const char* msg = "";
+    const int rc = tc_plan_encode(L->plan, a1, a2, rows, L->cfg.input_dim, L->cfg.hidden_dim, L->cfg.output_dim,
+                                  L->e_hi - L->e_lo, L->w1, L->w3, L->w2, &msg);
+    if (rc != MOE_OK) return fail(rc, "%s", msg);
+    L->plan_dirty = false;
+    return MOE_OK;
+}
+
+inline void stage_mark(moe_layer* L, int i, cudaStream_t s) {
+    if (L->profiling && L->ev_valid) cudaEventRecord(L->ev[i], s);
+}
+
+int check_ready(moe_layer* L) {
+    if (!L->router_set) return fail(MOE_ERR_STATE, "router weights have not been set (moe_layer_set_router)");
+    if (!L->w1) return fail(MOE_ERR_STATE, "no expert weights have been set (moe_layer_set_expert)");
+    for (size_t i = 0; i < L->expert_set.size(); ++i)
+        if (!L->expert_set[i])
+            return fail(MOE_ERR_STATE, "expert %d has no weights (moe_layer_set_expert)", (int)i + L->e_lo);
+    return MOE_OK;
+}
+
+// The grouped GEMM pair on `rows_cap` rows described by (expert_offset, tile_prefix).
+int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const int32_t* expert_offset,
+                const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base) {
+    const moe_config_t& c = L->cfg;
+    GroupGemmParams g;
+    g.E = n_experts;
+    g.activation = c.activation;
+    g.expert_offset = expert_offset;
+    g.tile_prefix = tile_prefix;
+    g.status = L->status;
+    const bool tc = c.compute_dtype == MOE_DTYPE_BF16;
+    const int tile_m = tc ? TC_TILE_M : F32_TILE_M;
+    const int64_t max_mtiles64 = (rows + tile_m - 1) / tile_m + n_experts;
+    if (max_mtiles64 > 0x7fffffff / 256) return fail(MOE_ERR_UNSUPPORTED, "too many row tiles");
+    const int max_mtiles = (int)max_mtiles64;
+    int n;
+    // GEMM 1: h = act(a W1^T) .* (a W3^T)
+    g.A = a_in;
+    g.B0 = L->w1;
+    g.B1 = L->w3;
+    g.C = h_buf;
+    g.N = c.hidden_dim;
+    g.K = c.input_dim;
+    if (tc) n = launch_group_gemm_tc(L->plan, 1, g, max_mtiles * ((c.hidden_dim + 127) / 128), L->num_sms, s);
+    else n = launch_group_gemm_f32(g, 1, max_mtiles, s);
+    if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 1 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n;
+    stage_mark(L, ev_base, s);
+    // GEMM 2: y = h W2^T
+    g.A = h_buf;
+    g.B0 = L->w2;
+    g.B1 = nullptr;
+    g.C = y_buf;
+    g.N = c.output_dim;
+    g.K = c.hidden_dim;
+    if (tc) n = launch_group_gemm_tc(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
+    else n = launch_group_gemm_f32(g, 2, max_mtiles, s);
+    if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 2 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n;
+    stage_mark(L, ev_base + 1, s);
+    return MOE_OK;
+}
+
+int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int training, float* out,
+                   const moe_forward_outputs_t* opt, cudaStream_t s) {
+    const moe_config_t& c = L->cfg;
+    static const moe_forward_outputs_t none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    if (!opt) opt = &none;
+    if (T < 0) return fail(MOE_ERR_INVALID, "T must be non-negative");
+    if (x_dtype != MOE_DTYPE_F32 && x_dtype != MOE_DTYPE_BF16) return fail(MOE_ERR_INVALID, "unknown x_dtype");
+    if (T > 0 && (!x || !out)) return fail(MOE_ERR_INVALID, "x and out must not be null");
+    if (T * (int64_t)L->k_tot > 0x7fffffffLL) return fail(MOE_ERR_UNSUPPORTED, "T*k exceeds 2^31-1 rows");
+    int rc = check_ready(L);
+    if (rc) return rc;
+    CUDA_TRY(cudaSetDevice(L->device));
+    if (T == 0 && !L->ep) {
+        if (opt->loss) CUDA_TRY(cudaMemsetAsync(opt->loss, 0, sizeof(float), s));
+        if (opt->routing_entropy) CUDA_TRY(cudaMemsetAsync(opt->routing_entropy, 0, sizeof(float), s));
+        if (opt->tokens_per_expert) CUDA_TRY(cudaMemsetAsync(opt->tokens_per_expert, 0, sizeof(int64_t) * L->E, s));
+        return MOE_OK;
+    }
+    if ((rc = ensure_workspace(L, T > 0 ? T : 1))) return rc;
+    if (!L->ep && L->plan_dirty && (rc = ensure_plan(L, L->xp, L->h, L->P_cap))) return rc;
+
+    const int num_cta = (int)((T + L->tokens_per_cta - 1) / L->tokens_per_cta);
+    stage_mark(L, 0, s);
+
+    RouterParams r;
+    r.x = x;
+    r.w = L->router_w;
+    r.bias = L->has_bias ? L->router_bias : nullptr;
+    r.T = T;
+    r.D = c.input_dim;
+    r.E = L->E;
+    r.E_router = L->E_router;
+    r.E_probs = L->E_probs;
+    r.S = L->S;
+    r.k = L->k;
+    r.k_tot = L->k_tot;
+    r.shared_mode = c.shared_mode;
+    r.bias_gates_only = c.bias_gates_only;
+    r.index_base = c.index_base;
+    r.tokens_per_cta = L->tokens_per_cta;
+    r.want_entropy = opt->routing_entropy != nullptr;
+    r.idx = L->idx;
+    r.gate = L->gate;
+    r.cta_counts = L->cta_counts;
+    r.cta_psum = L->cta_psum;
+    r.cta_entropy = L->cta_entropy;
+    r.u_idx = opt->indices;
+    r.u_gate = opt->gates;
+    r.u_probs = opt->probs;
+    r.u_logits = opt->logits;
+    int n = 0;
+    if (num_cta > 0) {
+        n = launch_router(r, x_dtype, num_cta, s);
+        if (n < 0) return fail(MOE_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n;
+    }
+    stage_mark(L, 1, s);
+
+    ScanParams sp;
+    sp.T = T;
+    sp.E = L->E;
+    sp.E_probs = L->E_probs;
+    sp.S = L->S;
+    sp.k = L->k;
+    sp.k_tot = L->k_tot;
+    sp.shared_mode = c.shared_mode;
+    sp.num_cta = num_cta;
+    sp.tile_m = c.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M;
+    sp.training = training;
+    sp.alpha = c.balance_alpha;
+    sp.z_weight = c.z_loss_weight;
+    sp.cta_counts = L->cta_counts;
+    sp.cta_psum = L->cta_psum;
+    sp.cta_entropy = L->cta_entropy;
+    sp.expert_count = L->expert_count;
+    sp.expert_offset = L->expert_offset;
+    sp.tile_prefix = L->tile_prefix;
+    sp.loss_internal = L->loss_dev;
+    sp.u_loss = L->ep ? nullptr : opt->loss;
+    sp.u_tokens_per_expert = opt->tokens_per_expert;
+    sp.u_entropy = L->ep ? nullptr : opt->routing_entropy;
+    sp.ep_sums = L->ep ? ep_sums_buffer(L->ep) : nullptr;
+    n = launch_scan(sp, s);
+    if (n < 0) return fail(MOE_ERR_CUDA, "scan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n;
+    stage_mark(L, 2, s);
+
+    PermuteParams pp;
+    pp.x = x;
+    pp.xp = L->xp;
+    pp.T = T;
+    pp.D = c.input_dim;
+    pp.E = L->E;
+    pp.k_tot = L->k_tot;
+    pp.tokens_per_cta = L->tokens_per_cta;
+    pp.idx = L->idx;
+    pp.cta_base = L->cta_counts;
+    pp.expert_offset = L->expert_offset;
+    pp.pair_pos = L->pair_pos;
+    pp.row_token = L->row_token;
+    pp.status = L->status;
+    pp.P_cap = L->P_cap;
+    if (num_cta > 0) {
+        n = launch_permute(pp, x_dtype, c.compute_dtype, num_cta, s);
+        if (n < 0) return fail(MOE_ERR_CUDA, "permute launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n;
+    }
+    stage_mark(L, 3, s);
+
+    if (!L->ep) {
+        if ((rc = run_experts(L, L->xp, L->h, L->y, L->expert_offset, L->tile_prefix, T * L->k_tot, L->E, s, 4)))
+            return rc;
+    } else {
+        EpCall call;
+        call.T = T;
+        call.training = training;
+        call.u_loss = opt->loss;
+        call.u_entropy = opt->routing_entropy;
+        call.xs = L->xp;
+        call.y_back = L->y;
+        call.expert_count = L->expert_count;
+        call.expert_offset = L->expert_offset;
+        call.stream = s;
+        int64_t ep_launches = 0;
+        rc = ep_exchange_and_run(
+            L->ep, call,
+            [](void* self, const void* a_in, void* h_buf, void* y_buf, const int32_t* eo, const int32_t* tp,
+               int64_t rows, int n_exp, int64_t cap_rows, cudaStream_t st) -> int {
+                moe_layer* M = reinterpret_cast<moe_layer*>(self);
+                int rc2 = ensure_plan(M, a_in, h_buf, cap_rows);
+                if (rc2) return rc2;
+                return run_experts(M, a_in, h_buf, y_buf, eo, tp, rows, n_exp, st, 4);
+            },
+            L, &ep_launches, g_err, sizeof(g_err));
+        L->launches += ep_launches;
+        if (rc) return rc;
+    }
+
+    CombineParams cp;
+    cp.y = L->y;
+    cp.out = out;
+    cp.T = T;
+    cp.O = c.output_dim;
+    cp.k_tot = L->k_tot;
+    cp.idx = L->idx;
+    cp.gate = L->gate;
+    cp.pair_pos = L->pair_pos;
+    n = launch_combine(cp, c.compute_dtype, s);
+    if (n < 0) return fail(MOE_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n;
+    stage_mark(L, 6, s);
+    return MOE_OK;
+}
+
+int grow(void** p, size_t* cap, size_t need) {
+    if (need <= *cap) return MOE_OK;
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+    CUDA_TRY(cudaMalloc(p, need));
+    *cap = need;
+    return MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* moe_last_error(void) { return g_err; }
+const char* moe_version(void) { return "moe_b200 0.1 (sm_100a)"; }
+
+int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
+    if (!cfg || !out) return fail(MOE_ERR_INVALID, "cfg and out must not be null");
+    *out = nullptr;
+    int rc = validate_config(*cfg);
+    if (rc) return rc;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+        return fail(MOE_ERR_CUDA, "no CUDA device is available (this library has no CPU path)");
+    if (device < 0 || device >= ndev) return fail(MOE_ERR_INVALID, "device %d out of range (0..%d)", device, ndev - 1);
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(MOE_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                    prop.major, prop.minor);
+    moe_layer* L = new (std::nothrow) moe_layer();
+    if (!L) return fail(MOE_ERR_INVALID, "out of host memory");
+    L->cfg = *cfg;
+    L->device = device;
+    L->num_sms = prop.multiProcessorCount;
+    L->E = cfg->num_experts;
+    L->S = cfg->shared_mode == MOE_SHARED_NONE ? 0 : cfg->num_shared;
+    L->k = cfg->gate_kind == MOE_GATE_SWITCH ? 1 : cfg->top_k;
+    L->k_tot = L->k + L->S;
+    L->E_router = cfg->shared_mode == MOE_SHARED_LAYER_BLEND ? L->E - L->S : L->E;
+    L->E_probs = L->E_router;
+    L->tokens_per_cta = router_tokens_per_cta(L->E_router);
+    L->e_lo = 0;
+    L->e_hi = L->E;
+    auto cleanup = [&](int code) {
+        moe_layer_destroy(L);
+        return code;
+    };
+    if ((rc = dev_alloc(&L->router_w, (size_t)L->E_router * cfg->input_dim))) return cleanup(rc);
+    if ((rc = dev_alloc(&L->router_bias, (size_t)L->E_router))) return cleanup(rc);
+    if ((rc = dev_alloc(&L->expert_count, (size_t)L->E))) return cleanup(rc);
+    if ((rc = dev_alloc(&L->expert_offset, (size_t)L->E + 1))) return cleanup(rc);
+    if ((rc = dev_alloc(&L->tile_prefix, (size_t)L->E + 1))) return cleanup(rc);
+    if ((rc = dev_alloc(&L->loss_dev, 1))) return cleanup(rc);
+    if ((rc = dev_alloc(&L->status, 1))) return cleanup(rc);
+    if (cudaMemset(L->status, 0, sizeof(int32_t)) != cudaSuccess) return cleanup(fail(MOE_ERR_CUDA, "cudaMemset failed"));
+    if (cudaStreamCreateWithFlags(&L->stream, cudaStreamNonBlocking) != cudaSuccess)
+        return cleanup(fail(MOE_ERR_CUDA, "cudaStreamCreate failed"));
+    *out = L;
+    return MOE_OK;
+}
+
+int moe_layer_destroy(moe_layer_t* L) {
+    if (!L) return MOE_OK;
+    cudaSetDevice(L->device);
+    cudaDeviceSynchronize();
+    if (L->ep) ep_destroy(L->ep);
+    free_workspace(L);
+    dev_free(L->w1);
+    dev_free(L->w3);
+    dev_free(L->w2);
+    dev_free(L->router_w);
+    dev_free(L->router_bias);
+    dev_free(L->stage_w);
+    dev_free(L->expert_count);
+    dev_free(L->expert_offset);
+    dev_free(L->tile_prefix);
+    dev_free(L->loss_dev);
+    dev_free(L->status);
+    dev_free(L->hx);
+    dev_free(L->hout);
+    dev_free(L->hopt);
+    if (L->plan) tc_plan_destroy(L->plan);
+    if (L->ev_valid)
+        for (auto& e : L->ev) cudaEventDestroy(e);
+    if (L->stream) cudaStreamDestroy(L->stream);
+    delete L;
+    return MOE_OK;
+}
+
+int moe_layer_dims(const moe_layer_t* L, int32_t* k_tot, int32_t* e_probs, int32_t* e_router) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    // indices/gates hold k routed entries per token in LAYER_BLEND mode (the reference's
+    // expert_indices there are the routed ones shifted by S), else k_tot.
+    if (k_tot) *k_tot = L->cfg.shared_mode == MOE_SHARED_LAYER_BLEND ? L->k : L->k_tot;
+    if (e_probs) *e_probs = L->E_probs;
+    if (e_router) *e_router = L->E_router;
+    return MOE_OK;
+}
+
+int moe_layer_set_expert(moe_layer_t* L, int expert, const void* w1, const void* w2, const void* w3, int src_dtype,
+                         int layout, int src_is_device) {
+    if (!L || !w1 || !w2 || !w3) return fail(MOE_ERR_INVALID, "null argument");
+    if (src_dtype != MOE_DTYPE_F32 && src_dtype != MOE_DTYPE_BF16) return fail(MOE_ERR_INVALID, "unknown src_dtype");
+    if (layout != MOE_LAYOUT_IN_CONTIG && layout != MOE_LAYOUT_OUT_CONTIG) return fail(MOE_ERR_INVALID, "unknown layout");
+    if (expert < 0 || expert >= L->E) return fail(MOE_ERR_INVALID, "expert %d out of range 0..%d", expert, L->E - 1);
+    if (expert < L->e_lo || expert >= L->e_hi)
+        return fail(MOE_ERR_INVALID, "expert %d is not held by this rank (it holds %d..%d)", expert, L->e_lo, L->e_hi - 1);
+    CUDA_TRY(cudaSetDevice(L->device));
+    int rc = ensure_weights(L);
+    if (rc) return rc;
+    const size_t D = L->cfg.input_dim, H = L->cfg.hidden_dim, O = L->cfg.output_dim;
+    const size_t el = dtype_size(L->cfg.compute_dtype), sel = dtype_size(src_dtype);
+    const size_t slot = (size_t)(expert - L->e_lo);
+    struct Item { const void* src; void* dst; int rows, cols; };
+    const Item items[3] = {
+        {w1, (char*)L->w1 + slot * H * D * el, (int)H, (int)D},
+        {w3, (char*)L->w3 + slot * H * D * el, (int)H, (int)D},
+        {w2, (char*)L->w2 + slot * O * H * el, (int)O, (int)H},
+    };
+    for (const Item& it : items) {
+        const void* src = it.src;
+        const size_t bytes = (size_t)it.rows * it.cols * sel;
+        if (!src_is_device) {
+            if ((rc = grow(&L->stage_w, &L->stage_w_bytes, bytes))) return rc;
+            CUDA_TRY(cudaMemcpyAsync(L->stage_w, it.src, bytes, cudaMemcpyHostToDevice, L->stream));
+            src = L->stage_w;
+        }
+        const int n = launch_transpose_convert(src, src_dtype, it.dst, L->cfg.compute_dtype, it.rows, it.cols,
+                                               layout == MOE_LAYOUT_OUT_CONTIG, L->stream);
+        if (n < 0) return fail(MOE_ERR_CUDA, "weight repack launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n;
+        CUDA_TRY(cudaStreamSynchronize(L->stream));
+    }
+    L->expert_set[slot] = 1;
+    return MOE_OK;
+}
+
+int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias, int layout, int src_is_device) {
+    if (!L || !w) return fail(MOE_ERR_INVALID, "null argument");
+    if (layout != MOE_LAYOUT_IN_CONTIG && layout != MOE_LAYOUT_OUT_CONTIG) return fail(MOE_ERR_INVALID, "unknown layout");
+    CUDA_TRY(cudaSetDevice(L->device));
+    const size_t bytes = (size_t)L->E_router * L->cfg.input_dim * sizeof(float);
+    const void* src = w;
+    int rc;
+    if (!src_is_device) {
+        if ((rc = grow(&L->stage_w, &L->stage_w_bytes, bytes))) return rc;
+        CUDA_TRY(cudaMemcpyAsync(L->stage_w, w, bytes, cudaMemcpyHostToDevice, L->stream));
+        src = L->stage_w;
+    }
+    const int n = launch_transpose_convert(src, MOE_DTYPE_F32, L->router_w, MOE_DTYPE_F32, L->E_router,
+                                           L->cfg.input_dim, layout == MOE_LAYOUT_OUT_CONTIG, L->stream);
+    if (n < 0) return fail(MOE_ERR_CUDA, "router repack launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n;
+    if (logit_bias) {
+        CUDA_TRY(cudaMemcpyAsync(L->router_bias, logit_bias, sizeof(float) * L->E_router,
+                                 src_is_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, L->stream));
+        L->has_bias = true;
+    } else {
+        L->has_bias = false;
+    }
+    CUDA_TRY(cudaStreamSynchronize(L->stream));
+    L->router_set = true;
+    return MOE_OK;
+}
+
+int moe_layer_forward(moe_layer_t* L, const void* x, int x_dtype, int64_t T, int training, float* out,
+                      const moe_forward_outputs_t* opt, void* cuda_stream) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    return forward_device(L, x, x_dtype, T, training, out, opt, reinterpret_cast<cudaStream_t>(cuda_stream));
+}
+
+int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T, int training, float* out,
+                           const moe_forward_outputs_t* opt) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    if (T < 0) return fail(MOE_ERR_INVALID, "T must be non-negative");
+    if (x_dtype != MOE_DTYPE_F32 && x_dtype != MOE_DTYPE_BF16) return fail(MOE_ERR_INVALID, "unknown x_dtype");
+    if (T > 0 && (!x || !out)) return fail(MOE_ERR_INVALID, "x and out must not be null");
+    CUDA_TRY(cudaSetDevice(L->device));
+    static const moe_forward_outputs_t none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    if (!opt) opt = &none;
+    int32_t ku = 0, ep = 0, er = 0;
+    moe_layer_dims(L, &ku, &ep, &er);
+    const size_t xb = (size_t)T * L->cfg.input_dim * dtype_size(x_dtype);
+    const size_t ob = (size_t)T * L->cfg.output_dim * sizeof(float);
+    // one device block for the optional outputs
+    size_t off = 0;
+    auto take = [&](bool want, size_t bytes) {
+        const size_t o = off;
+        if (want) off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t o_loss = take(opt->loss, 4), o_idx = take(opt->indices, (size_t)T * ku * 4),
+                 o_gate = take(opt->gates, (size_t)T * ku * 4), o_probs = take(opt->probs, (size_t)T * ep * 4),
+                 o_logits = take(opt->logits, (size_t)T * er * 4), o_tpe = take(opt->tokens_per_expert, (size_t)L->E * 8),
+                 o_ent = take(opt->routing_entropy, 4);
+    int rc;
+    if ((rc = grow(&L->hx, &L->hx_bytes, xb))) return rc;
+    if ((rc = grow(reinterpret_cast<void**>(&L->hout), &L->hout_bytes, ob))) return rc;
+    if ((rc = grow(&L->hopt, &L->hopt_bytes, off))) return rc;
+    char* ob_dev = reinterpret_cast<char*>(L->hopt);
+    moe_forward_outputs_t d;
+    d.loss = opt->loss ? reinterpret_cast<float*>(ob_dev + o_loss) : nullptr;
+    d.indices = opt->indices ? reinterpret_cast<int32_t*>(ob_dev + o_idx) : nullptr;
+    d.gates = opt->gates ? reinterpret_cast<float*>(ob_dev + o_gate) : nullptr;
+    d.probs = opt->probs ? reinterpret_cast<float*>(ob_dev + o_probs) : nullptr;
+    d.logits = opt->logits ? reinterpret_cast<float*>(ob_dev + o_logits) : nullptr;
+    d.tokens_per_expert = opt->tokens_per_expert ? reinterpret_cast<int64_t*>(ob_dev + o_tpe) : nullptr;
+    d.routing_entropy = opt->routing_entropy ? reinterpret_cast<float*>(ob_dev + o_ent) : nullptr;
+    cudaStream_t s = L->stream;
+    if (xb) CUDA_TRY(cudaMemcpyAsync(L->hx, x, xb, cudaMemcpyHostToDevice, s));
+    if ((rc = forward_device(L, L->hx, x_dtype, T, training, L->hout, &d, s))) return rc;
+    if (ob) CUDA_TRY(cudaMemcpyAsync(out, L->hout, ob, cudaMemcpyDeviceToHost, s));
+    if (d.loss) CUDA_TRY(cudaMemcpyAsync(opt->loss, d.loss, 4, cudaMemcpyDeviceToHost, s));
+    if (d.indices && T) CUDA_TRY(cudaMemcpyAsync(opt->indices, d.indices, (size_t)T * ku * 4, cudaMemcpyDeviceToHost, s));
+    if (d.gates && T) CUDA_TRY(cudaMemcpyAsync(opt->gates, d.gates, (size_t)T * ku * 4, cudaMemcpyDeviceToHost, s));
+    if (d.probs && T) CUDA_TRY(cudaMemcpyAsync(opt->probs, d.probs, (size_t)T * ep * 4, cudaMemcpyDeviceToHost, s));
+    if (d.logits && T) CUDA_TRY(cudaMemcpyAsync(opt->logits, d.logits, (size_t)T * er * 4, cudaMemcpyDeviceToHost, s));
+    if (d.tokens_per_expert)
+        CUDA_TRY(cudaMemcpyAsync(opt->tokens_per_expert, d.tokens_per_expert, (size_t)L->E * 8, cudaMemcpyDeviceToHost, s));
+    if (d.routing_entropy) CUDA_TRY(cudaMemcpyAsync(opt->routing_entropy, d.routing_entropy, 4, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    int32_t st = 0;
+    CUDA_TRY(cudaMemcpy(&st, L->status, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st != DEV_OK) {
+        cudaMemset(L->status, 0, sizeof(int32_t));
+        return fail(st == DEV_BAD_INDEX ? MOE_ERR_INVALID : MOE_ERR_TIMEOUT, "device status %d after forward", st);
+    }
+    return MOE_OK;
+}
+
+int moe_compute_gates(int gate_kind, int num_experts, int num_shared, int top_k, int index_base, const float* logits,
+                      int64_t T, int32_t* indices, float* gates, float* probs, void* cuda_stream) {
+    if (gate_kind < MOE_GATE_TOPK || gate_kind > MOE_GATE_SHARED_TOPK) return fail(MOE_ERR_INVALID, "unknown gate_kind");
+    if (num_experts < 1 || num_experts > MAX_ROUTER_EXPERTS)
+        return fail(MOE_ERR_UNSUPPORTED, "num_experts must be in 1..%d", MAX_ROUTER_EXPERTS);
+    const int S = gate_kind == MOE_GATE_SHARED_TOPK ? num_shared : 0;
+    const int k = gate_kind == MOE_GATE_SWITCH ? 1 : top_k;
+    if (S < 0 || S >= num_experts) return fail(MOE_ERR_INVALID, "num_shared out of range");
+    if (k < 1 || k > num_experts - S) return fail(MOE_ERR_INVALID, "top_k out of range");
+    if (k + S > MAX_KTOT) return fail(MOE_ERR_UNSUPPORTED, "more than %d selected experts per token", MAX_KTOT);
+    if (index_base != 0 && index_base != 1) return fail(MOE_ERR_INVALID, "index_base must be 0 or 1");
+    if (T < 0 || (T > 0 && !logits)) return fail(MOE_ERR_INVALID, "bad logits/T");
+    if (T == 0) return MOE_OK;
+    if (launch_gates_only(gate_kind, num_experts, S, k, index_base, logits, T, indices, gates, probs,
+                          reinterpret_cast<cudaStream_t>(cuda_stream)) < 0)
+        return fail(MOE_ERR_CUDA, "compute_gates launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return MOE_OK;
+}
+
+int moe_compute_loss(float alpha, float z_weight, int n_probs, int k, int index_base, const int32_t* indices,
+                     const float* probs, const float* logits, int n_logits, int64_t T, float* loss, void* cuda_stream) {
+    if (n_probs < 1 || n_probs > MAX_EXPERTS) return fail(MOE_ERR_UNSUPPORTED, "n_probs must be in 1..%d", MAX_EXPERTS);
+    if (k < 1 || T < 1 || !indices || !probs || !loss) return fail(MOE_ERR_INVALID, "bad argument");
+    if (logits && n_logits < 1) return fail(MOE_ERR_INVALID, "n_logits must be positive");
+    if (launch_loss_only(alpha, z_weight, n_probs, k, index_base, indices, probs, logits, n_logits, T, loss,
+                         reinterpret_cast<cudaStream_t>(cuda_stream)) < 0)
+        return fail(MOE_ERR_CUDA, "compute_loss launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return MOE_OK;
+}
+
+int moe_layer_set_profiling(moe_layer_t* L, int enabled) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    CUDA_TRY(cudaSetDevice(L->device));
+    if (enabled && !L->ev_valid) {
+        for (auto& e : L->ev) CUDA_TRY(cudaEventCreate(&e));
+        L->ev_valid = true;
+    }
+    L->profiling = enabled != 0;
+    return MOE_OK;
+}
+
+int moe_layer_last_stage_ms(moe_layer_t* L, float ms[7]) {
+    if (!L || !ms) return fail(MOE_ERR_INVALID, "null argument");
+    if (!L->profiling || !L->ev_valid) return fail(MOE_ERR_STATE, "profiling is not enabled");
+    CUDA_TRY(cudaSetDevice(L->device));
+    CUDA_TRY(cudaEventSynchronize(L->ev[6]));
+    // events: 0 start, 1 router, 2 scan, 3 permute, 4 gemm1, 5 gemm2, 6 combine; 7 = end of exchange
+    for (int i = 0; i < 7; ++i) ms[i] = 0.f;
+    for (int i = 0; i < 6; ++i) {
+        float v = 0.f;
+        if (cudaEventElapsedTime(&v, L->ev[i], L->ev[i + 1]) == cudaSuccess) ms[i] = v;
+    }
+    if (L->ep) ms[6] = ep_last_exchange_ms(L->ep);
+    return MOE_OK;
+}
+
+int64_t moe_layer_launch_count(const moe_layer_t* L) { return L ? L->launches : 0; }
+
+int moe_layer_device_status(moe_layer_t* L, int32_t* status) {
+    if (!L || !status) return fail(MOE_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(L->device));
+    CUDA_TRY(cudaMemcpy(status, L->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    return MOE_OK;
+}
+
+int moe_ep_unique_id(void* id128) { return ep_unique_id(id128, g_err, sizeof(g_err)); }
+
+int moe_ep_init(moe_layer_t* L, const void* id128, int rank, int world) {
+    if (!L || !id128) return fail(MOE_ERR_INVALID, "null argument");
+    if (world < 1 || rank < 0 || rank >= world) return fail(MOE_ERR_INVALID, "bad rank/world");
+    if (L->E % world) return fail(MOE_ERR_INVALID, "num_experts (%d) must be divisible by the world size (%d)", L->E, world);
+    if (L->cfg.shared_mode != MOE_SHARED_NONE)
+        return fail(MOE_ERR_UNSUPPORTED, "expert parallelism with shared experts is not implemented");
+    if (L->w1) return fail(MOE_ERR_STATE, "moe_ep_init must come before moe_layer_set_expert");
+    if (L->ep) return fail(MOE_ERR_STATE, "expert parallelism is already initialised");
+    CUDA_TRY(cudaSetDevice(L->device));
+    EpConfig ec;
+    ec.rank = rank;
+    ec.world = world;
+    ec.E = L->E;
+    ec.E_probs = L->E_probs;
+    ec.k_tot = L->k_tot;
+    ec.D = L->cfg.input_dim;
+    ec.H = L->cfg.hidden_dim;
+    ec.O = L->cfg.output_dim;
+    ec.elt = (int)dtype_size(L->cfg.compute_dtype);
+    ec.tile_m = L->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M;
+    ec.alpha = L->cfg.balance_alpha;
+    ec.z_weight = L->cfg.z_loss_weight;
+    const int rc = ep_create(&L->ep, ec, id128, g_err, sizeof(g_err));
+    if (rc) return rc;
+    const int per = L->E / world;
+    L->e_lo = rank * per;
+    L->e_hi = L->e_lo + per;
+    free_workspace(L);
+    return MOE_OK;
+}
+
+}  // extern "C"

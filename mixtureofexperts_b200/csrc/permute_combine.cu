@@ -1,0 +1,236 @@
+// Token permute (dispatch) and weighted un-permute (combine).
+//
+// permute: every (token, slot) pair gets row  expert_offset[e] + (pairs of e in earlier CTAs) +
+// (rank inside this CTA's token tile)  -- the ascending-token order of the reference's bucket
+// pass (process_expert_forward!, src/core/moe_layer.jl:195-203) -- and the token's D-vector is
+// copied there with 16-byte loads/stores: each token row is read once and written k_tot times.
+// HBM bound: T*D*sizeof(x) read + pairs*D*sizeof(xp) written.
+//
+// combine: out[t] = sum over the token's slots, in ascending expert id (the order in which
+// the reference's expert loop adds into a token, moe_layer.jl:205-218), of gate * y[row].
+// Gather-style: every output element is written exactly once, no atomics, no memset
+// (replaces apply_gates_kernel!, src/cuda/kernels.jl:60-81, launched E times with a device
+// sync after each, and the zero fill of src/cuda/experts.jl:36).
+// HBM bound: pairs*O*sizeof(y) read + T*O*4 written.
+#include "common.cuh"
+
+namespace moe {
+namespace {
+
+constexpr int PERM_THREADS = 256;
+constexpr int PERM_MAX_PAIRS = 64 * MAX_KTOT;  // tokens_per_cta <= 64
+
+template <typename T>
+struct Vec16 {
+    static constexpr int N = 16 / sizeof(T);
+};
+
+__device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+
+template <typename XT, typename PT>
+__device__ __forceinline__ void copy_row(const XT* src, PT* const* dst, int ndst, int D, int lane, bool vec);
+
+// same type: straight 16-byte copies
+template <typename T>
+__device__ __forceinline__ void copy_row_same(const T* src, T* const* dst, int ndst, int D, int lane, bool vec) {
+    constexpr int N = 16 / sizeof(T);
+    if (vec) {
+        for (int c = lane * N; c < D; c += 32 * N) {
+            const uint4 v = ld16(src + c);
+            for (int j = 0; j < ndst; ++j) st16(dst[j] + c, v);
+        }
+    } else {
+        for (int c = lane; c < D; c += 32) {
+            const T v = src[c];
+            for (int j = 0; j < ndst; ++j) dst[j][c] = v;
+        }
+    }
+}
+
+template <>
+__device__ __forceinline__ void copy_row<float, float>(const float* s, float* const* d, int n, int D, int lane,
+                                                       bool vec) {
+    copy_row_same<float>(s, d, n, D, lane, vec);
+}
+template <>
+__device__ __forceinline__ void copy_row<__nv_bfloat16, __nv_bfloat16>(const __nv_bfloat16* s,
+                                                                       __nv_bfloat16* const* d, int n, int D,
+                                                                       int lane, bool vec) {
+    copy_row_same<__nv_bfloat16>(s, d, n, D, lane, vec);
+}
+template <>
+__device__ __forceinline__ void copy_row<float, __nv_bfloat16>(const float* s, __nv_bfloat16* const* d, int n,
+                                                               int D, int lane, bool) {
+    for (int c = lane; c < D; c += 32) {
+        const __nv_bfloat16 v = __float2bfloat16_rn(s[c]);
+        for (int j = 0; j < n; ++j) d[j][c] = v;
+    }
+}
+template <>
+__device__ __forceinline__ void copy_row<__nv_bfloat16, float>(const __nv_bfloat16* s, float* const* d, int n,
+                                                               int D, int lane, bool) {
+    for (int c = lane; c < D; c += 32) {
+        const float v = __bfloat162float(s[c]);
+        for (int j = 0; j < n; ++j) d[j][c] = v;
+    }
+}
+
+template <typename XT, typename PT>
+__global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermuteParams p) {
+    __shared__ int s_base[MAX_EXPERTS];
+    __shared__ int s_pos[PERM_MAX_PAIRS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t tok0 = (int64_t)blockIdx.x * p.tokens_per_cta;
+    const int ntok = (int)min((int64_t)p.tokens_per_cta, p.T - tok0);
+    const int npairs = ntok * p.k_tot;
+
+    for (int e = threadIdx.x; e < p.E; e += PERM_THREADS)
+        s_base[e] = p.expert_offset[e] + p.cta_base[(size_t)blockIdx.x * p.E + e];
+    __syncthreads();
+
+    if (warp == 0) {
+        // rank of each pair among the tile's pairs of the same expert, in (token, slot) order
+        for (int q0 = 0; q0 < npairs; q0 += 32) {
+            const int q = q0 + lane;
+            const bool act = q < npairs;
+            const int e = act ? p.idx[tok0 * p.k_tot + q] : -1 - lane;  // inactive lanes never match
+            const unsigned m = __match_any_sync(0xffffffffu, e);
+            const int rank = __popc(m & ((1u << lane) - 1u));
+            int pos = -1;
+            if (act && e >= 0 && e < p.E) {
+                pos = s_base[e] + rank;
+            }
+            __syncwarp();
+            if (act && e >= 0 && e < p.E && rank == 0) s_base[e] += __popc(m);
+            __syncwarp();
+            if (act) {
+                if (pos < 0 || (int64_t)pos >= p.P_cap) {
+                    if (p.status) atomicCAS(p.status, DEV_OK, DEV_BAD_INDEX);
+                    pos = -1;
+                }
+                s_pos[q] = pos;
+                p.pair_pos[tok0 * p.k_tot + q] = pos;
+                if (pos >= 0) p.row_token[pos] = (int)(tok0 + q / p.k_tot);
+            }
+        }
+    }
+    __syncthreads();
+
+    const XT* x = reinterpret_cast<const XT*>(p.x);
+    PT* xp = reinterpret_cast<PT*>(p.xp);
+    const bool vec = (p.D * sizeof(XT)) % 16 == 0 && (p.D * sizeof(PT)) % 16 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.xp)) & 15) == 0;
+    for (int tl = warp; tl < ntok; tl += PERM_THREADS / 32) {
+        PT* dst[MAX_KTOT];
+        int nd = 0;
+        for (int j = 0; j < p.k_tot; ++j) {
+            const int pos = s_pos[tl * p.k_tot + j];
+            if (pos >= 0) dst[nd++] = xp + (size_t)pos * p.D;
+        }
+        copy_row<XT, PT>(x + (size_t)(tok0 + tl) * p.D, dst, nd, p.D, lane, vec);
+    }
+}
+
+template <typename YT>
+__device__ __forceinline__ float4 ld_y4(const YT* p);
+template <>
+__device__ __forceinline__ float4 ld_y4<float>(const float* p) {
+    return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 ld_y4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+template <typename YT>
+__device__ __forceinline__ float ld_y1(const YT* p);
+template <>
+__device__ __forceinline__ float ld_y1<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ld_y1<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+constexpr int COMB_THREADS = 256;
+
+// One CTA per token; threads stride the O columns four at a time.
+template <typename YT>
+__global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombineParams p) {
+    __shared__ int s_row[MAX_KTOT];
+    __shared__ float s_gate[MAX_KTOT];
+    __shared__ int s_n;
+    const int64_t t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        // insertion sort of the token's slots by expert id (k_tot <= 16)
+        int ids[MAX_KTOT];
+        int n = 0;
+        for (int j = 0; j < p.k_tot; ++j) {
+            const int e = p.idx[t * p.k_tot + j];
+            const int r = p.pair_pos[t * p.k_tot + j];
+            const float g = p.gate[t * p.k_tot + j];
+            if (r < 0) continue;
+            int i = n++;
+            while (i > 0 && ids[i - 1] > e) {
+                ids[i] = ids[i - 1];
+                s_row[i] = s_row[i - 1];
+                s_gate[i] = s_gate[i - 1];
+                --i;
+            }
+            ids[i] = e;
+            s_row[i] = r;
+            s_gate[i] = g;
+        }
+        s_n = n;
+    }
+    __syncthreads();
+    const int n = s_n;
+    const YT* y = reinterpret_cast<const YT*>(p.y);
+    float* out = p.out + (size_t)t * p.O;
+    const bool vec = (p.O % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < p.O; c += COMB_THREADS * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < n; ++j) {
+                const float4 v = ld_y4<YT>(y + (size_t)s_row[j] * p.O + c);
+                const float g = s_gate[j];
+                acc.x += g * v.x;
+                acc.y += g * v.y;
+                acc.z += g * v.z;
+                acc.w += g * v.w;
+            }
+            *reinterpret_cast<float4*>(out + c) = acc;
+        }
+    } else {
+        for (int c = threadIdx.x; c < p.O; c += COMB_THREADS) {
+            float acc = 0.f;
+            for (int j = 0; j < n; ++j) acc += s_gate[j] * ld_y1<YT>(y + (size_t)s_row[j] * p.O + c);
+            out[c] = acc;
+        }
+    }
+}
+
+}  // namespace
+
+int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s) {
+    if (x_dtype == MOE_DTYPE_F32 && xp_dtype == MOE_DTYPE_F32)
+        permute_kernel<float, float><<<num_cta, PERM_THREADS, 0, s>>>(p);
+    else if (x_dtype == MOE_DTYPE_BF16 && xp_dtype == MOE_DTYPE_BF16)
+        permute_kernel<__nv_bfloat16, __nv_bfloat16><<<num_cta, PERM_THREADS, 0, s>>>(p);
+    else if (x_dtype == MOE_DTYPE_F32 && xp_dtype == MOE_DTYPE_BF16)
+        permute_kernel<float, __nv_bfloat16><<<num_cta, PERM_THREADS, 0, s>>>(p);
+    else
+        permute_kernel<__nv_bfloat16, float><<<num_cta, PERM_THREADS, 0, s>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s) {
+    if (p.T == 0) return 0;
+    if (y_dtype == MOE_DTYPE_F32)
+        combine_kernel<float><<<(unsigned)p.T, COMB_THREADS, 0, s>>>(p);
+    else
+        combine_kernel<__nv_bfloat16><<<(unsigned)p.T, COMB_THREADS, 0, s>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+}  // namespace moe

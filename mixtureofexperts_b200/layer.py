@@ -1,0 +1,398 @@
+"""MoEConfig / Router / MoELayer with the reference's call API (src/core/), running on
+libmoe_b200's CUDA kernels.
+
+    config = create_moe_config(num_experts=8, expert_type="gated", input_dim=512, hidden_dim=2048,
+                               output_dim=512, activation=silu, gate_type=TopKGating(2),
+                               balance_loss=SwitchTransformerLoss(0.01))
+    moe = MoELayer(config)
+    output, balance_loss = moe(x, training=True)        # x: (input_dim, T), output: (output_dim, T)
+
+Matrices keep the reference's shapes.  Julia stores (input_dim x T) column-major, i.e. T
+contiguous token vectors; pass ``x_TD.t()`` (torch) or an F-ordered NumPy array to avoid a copy.
+CUDA tensors run in place on torch's current stream; NumPy arrays go through the host entry
+point (copy in, compute, copy out).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import numpy as np
+
+from . import _lib
+from . import experts as _experts
+from .experts import GatedExpert
+from .gating import GatingMechanism, SharedExpertGating, SwitchGating, TopKGating, gate_kind_of
+from .losses import AuxiliaryFreeLoss, LoadBalancingLoss, SwitchTransformerLoss
+
+
+@dataclass
+class MoEConfig:
+    """Base.@kwdef struct MoEConfig (src/core/moe_layer.jl:4-29), same fields and defaults."""
+    num_experts: int = 8
+    expert_type: str = "standard"
+    input_dim: int = 768
+    hidden_dim: int = 3072
+    output_dim: int = 768
+    activation: Callable = _experts.gelu
+    expert_dropout: float = 0.0
+    gate_type: GatingMechanism = field(default_factory=lambda: TopKGating(2))
+    top_k: int = 2                      # not read by the forward pass (k comes from gate_type)
+    noise_scale: float = 0.0
+    use_noise_network: bool = False
+    use_fp32_router: bool = True
+    balance_loss: LoadBalancingLoss = field(default_factory=lambda: SwitchTransformerLoss(0.01))
+    z_loss_weight: float = 0.001
+    capacity_factor: float = 1.25
+    drop_tokens: bool = False
+    use_cur: bool = False
+    cur_rank: Optional[int] = None
+    num_shared_experts: int = 0
+
+
+def create_moe_config(**kwargs) -> MoEConfig:
+    """create_moe_config(; kwargs...) (src/core/moe_layer.jl:281-283)."""
+    return MoEConfig(**kwargs)
+
+
+_ACT_PROBE = np.array([-3.0, -1.0, -0.25, 0.0, 0.5, 2.0], dtype=np.float64)
+
+
+def activation_enum(fn) -> int:
+    """Map MoEConfig.activation (any callable in the reference) to the C ABI's enum: by
+    identity for the functions this package exports, else by probing the callable on a few
+    points.  Anything else is refused - there is no CPU path to run an arbitrary function."""
+    if isinstance(fn, str):
+        table = {"silu": _lib.ACT_SILU, "swish": _lib.ACT_SILU, "gelu": _lib.ACT_GELU_TANH,
+                 "relu": _lib.ACT_RELU, "identity": _lib.ACT_IDENTITY}
+        if fn in table:
+            return table[fn]
+        raise _lib.MoEError(_lib.ERR_UNSUPPORTED, f"unknown activation '{fn}'")
+    known = [(_experts.silu, _lib.ACT_SILU), (_experts.gelu, _lib.ACT_GELU_TANH),
+             (_experts.relu, _lib.ACT_RELU), (_experts.identity, _lib.ACT_IDENTITY)]
+    for f, e in known:
+        if fn is f:
+            return e
+    try:
+        got = np.array([float(fn(float(v))) for v in _ACT_PROBE])
+    except Exception as exc:  # noqa: BLE001
+        raise _lib.MoEError(_lib.ERR_UNSUPPORTED, f"activation {fn!r} cannot be probed: {exc}") from exc
+    for f, e in known:
+        if np.allclose(got, f(_ACT_PROBE), rtol=1e-5, atol=1e-6):
+            return e
+    raise _lib.MoEError(_lib.ERR_UNSUPPORTED, f"activation {fn!r} is not one of silu/gelu/relu/identity")
+
+
+class Router:
+    """Router (src/core/router.jl:4-23): a bias-free (num_experts x input_dim) projection with
+    Flux's default Glorot-uniform init, plus the gate that turns logits into assignments."""
+
+    def __init__(self, input_dim: int, num_experts: int, gate_type: GatingMechanism, *, noise_scale: float = 0.0,
+                 use_noise_network: bool = False, use_fp32: bool = True, rng=None):
+        g = rng if isinstance(rng, np.random.Generator) else np.random.default_rng(rng)
+        lim = math.sqrt(6.0 / (input_dim + num_experts))
+        self.weight = g.uniform(-lim, lim, size=(num_experts, input_dim)).astype(np.float32)
+        self.noise_weight = None
+        self.gate_type = gate_type
+        self.noise_scale = float(noise_scale)
+        self.use_fp32 = bool(use_fp32)
+        if use_noise_network or noise_scale > 0:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "training-time router noise is not accelerated (noise_scale must be 0)")
+
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+def _weight_ptr_layout(w):
+    """(pointer, dtype enum, layout enum, is_device, keepalive) of an (out, in) weight."""
+    if _is_torch(w):
+        import torch
+
+        if w.dtype == torch.float32:
+            dt = _lib.DTYPE_F32
+        elif w.dtype == torch.bfloat16:
+            dt = _lib.DTYPE_BF16
+        else:
+            raise _lib.MoEError(_lib.ERR_INVALID, f"unsupported weight dtype {w.dtype}")
+        if w.is_contiguous():
+            return w.data_ptr(), dt, _lib.LAYOUT_IN_CONTIG, int(w.is_cuda), w
+        if w.t().is_contiguous():
+            return w.data_ptr(), dt, _lib.LAYOUT_OUT_CONTIG, int(w.is_cuda), w
+        wc = w.contiguous()
+        return wc.data_ptr(), dt, _lib.LAYOUT_IN_CONTIG, int(wc.is_cuda), wc
+    a = np.asarray(w)
+    if a.dtype != np.float32:
+        a = a.astype(np.float32)
+    if a.flags.c_contiguous:
+        return a.ctypes.data, _lib.DTYPE_F32, _lib.LAYOUT_IN_CONTIG, 0, a
+    if a.flags.f_contiguous:
+        return a.ctypes.data, _lib.DTYPE_F32, _lib.LAYOUT_OUT_CONTIG, 0, a
+    a = np.ascontiguousarray(a)
+    return a.ctypes.data, _lib.DTYPE_F32, _lib.LAYOUT_IN_CONTIG, 0, a
+
+
+class MoELayer:
+    """MoELayer(config) (src/core/moe_layer.jl:34-63) and its call
+    ``moe(x; training=false, return_stats=false) -> (output, balance_loss[, training_stats])``
+    (:107-128).
+
+    Extra keywords (no counterpart in the reference): ``device`` (CUDA ordinal),
+    ``compute_dtype`` ("f32": FP32 FMA path, 1e-5 parity class; "bf16": tcgen05 tensor cores),
+    ``experts`` / ``router`` to inject pre-built weights, ``rng`` to seed the default init,
+    ``weights_on_device`` to draw the default expert weights on the GPU."""
+
+    def __init__(self, config: MoEConfig, *, device: int = 0, compute_dtype: str = "f32", experts=None, router=None,
+                 rng=None, weights_on_device: bool = False, expert_parallel=None):
+        self.config = config
+        self.device = int(device)
+        self.compute_dtype = compute_dtype
+        self._handle = C.c_void_p()
+        if config.expert_type != "gated" and str(config.expert_type) != ":gated":
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "only expert_type='gated' (GatedExpert) is accelerated")
+        if config.use_cur:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "CUR experts are not accelerated")
+        if config.drop_tokens:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "drop_tokens (capacity constraint) is not accelerated")
+        kind, k, gate_shared = gate_kind_of(config.gate_type)
+        if gate_shared and config.num_shared_experts:
+            raise _lib.MoEError(_lib.ERR_INVALID, "use either SharedExpertGating or num_shared_experts, not both")
+        shared_mode = _lib.SHARED_GATING if gate_shared else (
+            _lib.SHARED_LAYER_BLEND if config.num_shared_experts > 0 else _lib.SHARED_NONE)
+        num_shared = gate_shared or config.num_shared_experts
+        self.balance_loss = config.balance_loss
+        if isinstance(self.balance_loss, AuxiliaryFreeLoss):
+            alpha = self.balance_loss.complementary_weight if self.balance_loss.use_complementary_loss else 0.0
+        elif isinstance(self.balance_loss, SwitchTransformerLoss):
+            alpha = self.balance_loss.alpha
+        else:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, f"balance_loss {type(self.balance_loss).__name__} is not accelerated")
+        self._cfg = _lib.MoeConfig(
+            num_experts=config.num_experts, num_shared=num_shared, top_k=k, input_dim=config.input_dim,
+            hidden_dim=config.hidden_dim, output_dim=config.output_dim, gate_kind=kind,
+            activation=activation_enum(config.activation),
+            compute_dtype={"f32": _lib.DTYPE_F32, "bf16": _lib.DTYPE_BF16}[compute_dtype],
+            shared_mode=shared_mode, balance_alpha=float(alpha), z_loss_weight=float(config.z_loss_weight),
+            index_base=1, bias_gates_only=1 if isinstance(self.balance_loss, AuxiliaryFreeLoss) else 0)
+        _lib.check(_lib.lib.moe_layer_create(C.byref(self._cfg), self.device, C.byref(self._handle)))
+        kt, ep, er = C.c_int32(), C.c_int32(), C.c_int32()
+        _lib.check(_lib.lib.moe_layer_dims(self._handle, C.byref(kt), C.byref(ep), C.byref(er)))
+        self.k_out, self.e_probs, self.e_router = kt.value, ep.value, er.value
+
+        self.expert_range = range(config.num_experts)
+        if expert_parallel is not None:
+            rank, world, uid = expert_parallel
+            _lib.check(_lib.lib.moe_ep_init(self._handle, uid, int(rank), int(world)))
+            per = config.num_experts // world
+            self.expert_range = range(rank * per, (rank + 1) * per)
+
+        if experts is None:
+            dev = f"cuda:{self.device}" if weights_on_device else None
+            experts = [GatedExpert(config.input_dim, config.hidden_dim, config.output_dim, config.activation,
+                                   rng=rng, device=dev) if e in self.expert_range else None
+                       for e in range(config.num_experts)]
+        self.experts = list(experts)
+        self.router = router if router is not None else Router(
+            config.input_dim, self.e_router, config.gate_type, noise_scale=config.noise_scale,
+            use_noise_network=config.use_noise_network, use_fp32=config.use_fp32_router, rng=rng)
+        self.training_stats = {"tokens_per_expert": np.zeros(config.num_experts, dtype=np.int64),
+                               "routing_entropy": [], "capacity_overflow": 0}
+        self.sync_weights()
+
+    # -- weights ---------------------------------------------------------------------------
+    def sync_weights(self) -> None:
+        """Copy (and repack) the experts' and the router's current weights into the device
+        handle; call again after mutating them."""
+        for e in self.expert_range:
+            ex = self.experts[e]
+            p1, d1, l1, dev1, k1 = _weight_ptr_layout(ex.w1)
+            p2, d2, l2, dev2, k2 = _weight_ptr_layout(ex.w2)
+            p3, d3, l3, dev3, k3 = _weight_ptr_layout(ex.w3)
+            if not (d1 == d2 == d3 and l1 == l2 == l3 and dev1 == dev2 == dev3):
+                raise _lib.MoEError(_lib.ERR_INVALID, "w1, w2, w3 of an expert must share dtype, layout and device")
+            _lib.check(_lib.lib.moe_layer_set_expert(self._handle, e, p1, p2, p3, d1, l1, dev1))
+        self.sync_router()
+
+    def sync_router(self) -> None:
+        w = self.router.weight
+        p, d, lay, dev, keep = _weight_ptr_layout(w)
+        if d != _lib.DTYPE_F32:
+            raise _lib.MoEError(_lib.ERR_INVALID, "router weights must be float32")
+        bias_ptr, keep_b = None, None
+        bias = getattr(self.router, "bias", None)
+        if isinstance(self.balance_loss, AuxiliaryFreeLoss):
+            bias = self.balance_loss.bias
+        if bias is not None:
+            if _is_torch(bias):
+                import torch
+
+                keep_b = bias.to(dtype=torch.float32).contiguous()
+                if bool(keep_b.is_cuda) != bool(dev):
+                    keep_b = keep_b.cuda(self.device) if dev else keep_b.cpu()
+                bias_ptr = keep_b.data_ptr()
+            else:
+                if dev:
+                    import torch
+
+                    keep_b = torch.as_tensor(np.asarray(bias, dtype=np.float32)).cuda(self.device)
+                    bias_ptr = keep_b.data_ptr()
+                else:
+                    keep_b = np.ascontiguousarray(bias, dtype=np.float32)
+                    bias_ptr = keep_b.ctypes.data
+            n = keep_b.numel() if _is_torch(keep_b) else keep_b.size
+            if n != self.e_router:
+                raise _lib.MoEError(_lib.ERR_INVALID, f"router bias must have {self.e_router} entries")
+        _lib.check(_lib.lib.moe_layer_set_router(self._handle, p, bias_ptr, lay, dev))
+
+    # -- forward ---------------------------------------------------------------------------
+    def __call__(self, x, training: bool = False, return_stats: bool = False, return_routing: bool = False):
+        cfg = self.config
+        if x.ndim != 2 or x.shape[0] != cfg.input_dim:
+            raise _lib.MoEError(_lib.ERR_INVALID, f"x must have shape (input_dim={cfg.input_dim}, T), got {tuple(x.shape)}")
+        T = int(x.shape[1])
+        want_stats = return_stats or cfg.num_shared_experts == 0
+        if _is_torch(x) and x.is_cuda:
+            out, loss, extra = self._forward_torch(x, T, training, want_stats, return_routing)
+        else:
+            out, loss, extra = self._forward_numpy(np.asarray(x) if not _is_torch(x) else x.numpy(), T, training,
+                                                   want_stats, return_routing)
+        if cfg.num_shared_experts == 0:
+            # update_stats! (src/core/moe_layer.jl:250-264) runs in forward_standard only
+            self.training_stats["tokens_per_expert"] += extra["tokens_per_expert"]
+            self.training_stats["routing_entropy"].append(float(extra["routing_entropy"]))
+        if isinstance(self.balance_loss, AuxiliaryFreeLoss) and training:
+            # compute_loss(::AuxiliaryFreeLoss) updates the bias first (auxiliary_free.jl:73-83)
+            self.balance_loss.update_bias(extra["tokens_per_expert"])
+            self.sync_router()
+        ret = (out, loss)
+        if return_stats:
+            ret = ret + (self.training_stats,)
+        if return_routing:
+            ret = ret + ({k: extra[k] for k in ("indices", "gates", "probs", "logits")},)
+        return ret
+
+    def _forward_torch(self, x, T, training, want_stats, want_routing):
+        import torch
+
+        cfg = self.config
+        xt = x.t()
+        if not xt.is_contiguous():
+            xt = xt.contiguous()
+        if xt.dtype == torch.float32:
+            xd = _lib.DTYPE_F32
+        elif xt.dtype == torch.bfloat16:
+            xd = _lib.DTYPE_BF16
+        else:
+            xt = xt.float()
+            xd = _lib.DTYPE_F32
+        dev = xt.device
+        out = torch.empty((T, cfg.output_dim), dtype=torch.float32, device=dev)
+        loss = torch.zeros((), dtype=torch.float32, device=dev)
+        o = _lib.ForwardOutputs()
+        o.loss = loss.data_ptr()
+        extra = {}
+        if want_stats:
+            tpe = torch.zeros(cfg.num_experts, dtype=torch.int64, device=dev)
+            ent = torch.zeros((), dtype=torch.float32, device=dev)
+            o.tokens_per_expert, o.routing_entropy = tpe.data_ptr(), ent.data_ptr()
+        if want_routing:
+            idx = torch.empty((T, self.k_out), dtype=torch.int32, device=dev)
+            gates = torch.empty((T, self.k_out), dtype=torch.float32, device=dev)
+            probs = torch.empty((T, self.e_probs), dtype=torch.float32, device=dev)
+            logits = torch.empty((T, self.e_router), dtype=torch.float32, device=dev)
+            o.indices, o.gates, o.probs, o.logits = idx.data_ptr(), gates.data_ptr(), probs.data_ptr(), logits.data_ptr()
+            extra.update(indices=idx.t(), gates=gates.t(), probs=probs.t(), logits=logits.t())
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(_lib.lib.moe_layer_forward(self._handle, xt.data_ptr(), xd, T, int(training), out.data_ptr(),
+                                                  C.byref(o), stream))
+        if want_stats:
+            extra["tokens_per_expert"] = tpe.cpu().numpy()
+            extra["routing_entropy"] = float(ent.item())
+        return out.t(), loss, extra
+
+    def _forward_numpy(self, x, T, training, want_stats, want_routing):
+        cfg = self.config
+        if x.dtype != np.float32:
+            x = x.astype(np.float32)
+        xt = np.ascontiguousarray(x.T)
+        out = np.empty((T, cfg.output_dim), dtype=np.float32)
+        loss = np.zeros(1, dtype=np.float32)
+        o = _lib.ForwardOutputs()
+        o.loss = loss.ctypes.data
+        extra = {}
+        keep = []
+        if want_stats:
+            tpe = np.zeros(cfg.num_experts, dtype=np.int64)
+            ent = np.zeros(1, dtype=np.float32)
+            o.tokens_per_expert, o.routing_entropy = tpe.ctypes.data, ent.ctypes.data
+        if want_routing:
+            idx = np.empty((T, self.k_out), dtype=np.int32)
+            gates = np.empty((T, self.k_out), dtype=np.float32)
+            probs = np.empty((T, self.e_probs), dtype=np.float32)
+            logits = np.empty((T, self.e_router), dtype=np.float32)
+            o.indices, o.gates, o.probs, o.logits = idx.ctypes.data, gates.ctypes.data, probs.ctypes.data, logits.ctypes.data
+            extra.update(indices=idx.T, gates=gates.T, probs=probs.T, logits=logits.T)
+        _lib.check(_lib.lib.moe_layer_forward_host(self._handle, xt.ctypes.data, _lib.DTYPE_F32, T, int(training),
+                                                   out.ctypes.data, C.byref(o)))
+        if want_stats:
+            extra["tokens_per_expert"] = tpe
+            extra["routing_entropy"] = float(ent[0])
+        return out.T, np.float32(loss[0]), extra
+
+    # -- helpers ---------------------------------------------------------------------------
+    def set_profiling(self, enabled: bool = True) -> None:
+        _lib.check(_lib.lib.moe_layer_set_profiling(self._handle, int(enabled)))
+
+    def last_stage_ms(self) -> dict:
+        ms = (C.c_float * 7)()
+        _lib.check(_lib.lib.moe_layer_last_stage_ms(self._handle, ms))
+        names = ["router", "scan_loss", "permute", "gemm1", "gemm2", "combine", "exchange"]
+        return dict(zip(names, [float(v) for v in ms]))
+
+    def launch_count(self) -> int:
+        return int(_lib.lib.moe_layer_launch_count(self._handle))
+
+    def device_status(self) -> int:
+        st = C.c_int32()
+        _lib.check(_lib.lib.moe_layer_device_status(self._handle, C.byref(st)))
+        return st.value
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            _lib.lib.moe_layer_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+def create_moe_layer(input_dim: int, hidden_dim: int, output_dim: int, **kwargs) -> MoELayer:
+    """create_moe_layer(input_dim, hidden_dim, output_dim; kwargs...) (src/core/moe_layer.jl:285-293).
+    Keywords that MoEConfig does not know (device, compute_dtype, rng, ...) go to MoELayer."""
+    cfg_fields = set(MoEConfig.__dataclass_fields__)
+    cfg_kw = {k: v for k, v in kwargs.items() if k in cfg_fields}
+    layer_kw = {k: v for k, v in kwargs.items() if k not in cfg_fields}
+    return MoELayer(MoEConfig(input_dim=input_dim, hidden_dim=hidden_dim, output_dim=output_dim, **cfg_kw), **layer_kw)
+
+
+def reset_stats(moe: MoELayer) -> None:
+    """reset_stats!(moe) (src/core/moe_layer.jl:271-276)."""
+    moe.training_stats["tokens_per_expert"][:] = 0
+    moe.training_stats["routing_entropy"].clear()
+    moe.training_stats["capacity_overflow"] = 0
+
+
+def load_balance_score(expert_counts) -> float:
+    """load_balance_score(expert_counts) (src/core/utils.jl:40-52)."""
+    c = np.asarray(expert_counts, dtype=np.float64)
+    total = c.sum()
+    if total == 0:
+        return 1.0
+    ideal = total / c.size
+    return float(1.0 - math.sqrt(((c - ideal) ** 2).sum() / c.size) / ideal)

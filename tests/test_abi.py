@@ -1,0 +1,92 @@
+"""CPU tests of the boundary: the shared library loads, exports every symbol that
+include/moe_b200.h declares, rejects bad arguments on the host, and refuses to compute
+without a CUDA device (there is no CPU fallback)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "moe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib_built):
+    lib = C.CDLL(str(lib_built))
+    names = declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in moe_b200.h but not exported"
+
+
+def test_binding_lists_every_declared_symbol(lib_built):
+    from mixtureofexperts_b200 import _lib
+
+    assert sorted(_lib.EXPORTS) == declared_symbols()
+
+
+def test_config_struct_matches_header(lib_built):
+    from mixtureofexperts_b200 import _lib
+
+    assert C.sizeof(_lib.MoeConfig) == 14 * 4
+    assert C.sizeof(_lib.ForwardOutputs) == 7 * C.sizeof(C.c_void_p)
+
+
+def test_invalid_configs_are_rejected_on_the_host(lib_built):
+    from mixtureofexperts_b200 import _lib
+
+    def create(**kw):
+        base = dict(num_experts=8, num_shared=0, top_k=2, input_dim=64, hidden_dim=128, output_dim=64,
+                    gate_kind=_lib.GATE_TOPK, activation=_lib.ACT_SILU, compute_dtype=_lib.DTYPE_F32,
+                    shared_mode=_lib.SHARED_NONE, balance_alpha=0.01, z_loss_weight=0.001, index_base=1,
+                    bias_gates_only=0)
+        base.update(kw)
+        cfg = _lib.MoeConfig(**base)
+        h = C.c_void_p()
+        return _lib.lib.moe_layer_create(C.byref(cfg), 0, C.byref(h)), _lib.lib.moe_last_error().decode()
+
+    for kw in (dict(num_experts=0), dict(top_k=9), dict(top_k=0), dict(input_dim=0), dict(activation=9),
+               dict(index_base=2), dict(gate_kind=_lib.GATE_SHARED_TOPK), dict(num_shared=1),
+               dict(shared_mode=_lib.SHARED_LAYER_BLEND, num_shared=8)):
+        code, msg = create(**kw)
+        assert code == _lib.ERR_INVALID and msg, kw
+    code, msg = create(compute_dtype=_lib.DTYPE_BF16, input_dim=60)
+    assert code == _lib.ERR_UNSUPPORTED and "multiples of 8" in msg
+    code, msg = create(num_experts=200, top_k=2)
+    assert code == _lib.ERR_UNSUPPORTED
+
+
+def test_no_device_means_loud_failure_not_fallback(lib_built):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    import mixtureofexperts_b200 as m
+
+    with pytest.raises(m.MoEError) as ei:
+        m.MoELayer(m.create_moe_config(expert_type="gated", activation=m.silu, input_dim=64, hidden_dim=128,
+                                       output_dim=64))
+    assert ei.value.code == -2 and "no CPU path" in str(ei.value)
+
+
+def test_null_handles_are_rejected(lib_built):
+    from mixtureofexperts_b200 import _lib
+
+    assert _lib.lib.moe_layer_forward(None, None, 0, 1, 0, None, None, None) == _lib.ERR_INVALID
+    assert _lib.lib.moe_layer_forward_host(None, None, 0, 1, 0, None, None) == _lib.ERR_INVALID
+    assert _lib.lib.moe_layer_destroy(None) == _lib.OK
+    assert _lib.lib.moe_compute_gates(_lib.GATE_TOPK, 8, 0, 9, 1, None, 4, None, None, None, None) == _lib.ERR_INVALID
+
+
+def test_product_package_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "mixtureofexperts_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower() or f == "ep.h" or "the oracle for this path" in text.lower(), f

@@ -1,0 +1,290 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (via the ctypes host mirror),
+against the CPU oracle on the same seeded inputs.
+
+Tolerances (from the task statement): expert indices bit-exact except gate-logit ties within
+1e-6; FP32 outputs and loss within 1e-5 relative (||a-b||_inf/||b||_inf per tensor); the BF16
+tensor-core path within 2e-2 relative, the oracle being evaluated in FP32 on the BF16-rounded
+weights and activations."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden  # noqa: E402
+from helpers import check_indices, device_gate, make_device_layer, oracle_gate, rel_inf  # noqa: E402
+from oracle import moe_oracle as orc  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+F32_TOL = 1e-5
+BF16_TOL = 2e-2
+
+
+def logits64(x, w, bias=None):
+    lg = x.astype(np.float64) @ w.router.astype(np.float64).T
+    if bias is not None:
+        lg = lg + bias.astype(np.float64)
+    return lg
+
+
+def run_case(T, D, H, O, E, gate_kind, k, S=0, *, seed=0, activation="silu", compute="f32", z=0.001,
+             num_shared_experts=0, init="normal", std=0.25, host=False, training=True, tol=None, x_bf16=None):
+    bf16 = compute == "bf16"
+    e_router = E - num_shared_experts
+    x, w = orc.make_layer_inputs(seed, T, D, H, O, E, e_router=e_router, init=init, std=std, bf16=bf16)
+    ogate = oracle_gate(gate_kind, k, S, E)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation=activation,
+                        gate_type=ogate, balance_alpha=0.01, z_loss_weight=z, num_shared_experts=num_shared_experts)
+    o_out, o_loss, aux = orc.moe_layer_forward(cfg, w, x, training=training)
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=device_gate(gate_kind, k, S, E), activation=activation, z=z,
+                              compute_dtype=compute, num_shared_experts=num_shared_experts)
+    if host:
+        xin = np.asfortranarray(x.T)
+    else:
+        xt = torch.from_numpy(x).cuda()
+        if x_bf16 if x_bf16 is not None else bf16:
+            xt = xt.to(torch.bfloat16)
+        xin = xt.t()
+    out, loss, stats, routing = layer(xin, training=training, return_stats=True, return_routing=True)
+    if not host:
+        torch.cuda.synchronize()
+        out = out.cpu().numpy()
+        loss = float(loss.item())
+        routing = {k_: v.cpu().numpy() for k_, v in routing.items()}
+    assert layer.device_status() == 0
+    tol = tol or (BF16_TOL if bf16 else F32_TOL)
+    r0 = S if gate_kind == "shared" else 0
+    kk = 1 if gate_kind == "switch" else k
+    excused = check_indices(routing["indices"].T, aux["indices"], logits64(x, w), kk, r0)
+    assert rel_inf(routing["logits"].T, aux["logits"]) < F32_TOL
+    if excused == 0:
+        assert rel_inf(routing["gates"].T, aux["gates"]) < F32_TOL
+        assert rel_inf(out.T, o_out) < tol, f"output rel err {rel_inf(out.T, o_out):.3e}"
+    assert rel_inf(routing["probs"].T, aux["probs"]) < F32_TOL
+    assert abs(float(loss) - float(o_loss)) <= F32_TOL * max(abs(float(o_loss)), 1e-30) + (1e-4 if excused else 0)
+    if num_shared_experts == 0:
+        assert np.array_equal(stats["tokens_per_expert"], aux["stats"]["tokens_per_expert"]) or excused
+        assert abs(stats["routing_entropy"][-1] - float(aux["stats"]["routing_entropy"])) < 1e-5
+    layer.close()
+    return rel_inf(out.T, o_out)
+
+
+# ---- golden fixtures (BASELINE config 1 and the small gate/shared-expert variants) -------------
+
+@pytest.mark.parametrize("case", list(make_golden.CASES))
+@pytest.mark.parametrize("host", [False, True])
+def test_golden_fixture(case, host):
+    c, cfg, x, w = make_golden.build(case)
+    ref = np.load(os.path.join(GOLDEN, f"{case}.npz"))
+    g = c["gate"]
+    S = g[2] if g[0] == "shared" else 0
+    k = 1 if g[0] == "switch" else g[1]
+    nsh = c.get("num_shared_experts", 0)
+    layer = make_device_layer(w, D=c["D"], H=c["H"], O=c["O"], gate=device_gate(g[0], k, S, c["E"]),
+                              activation=c.get("activation", "silu"), z=c["z"], num_shared_experts=nsh)
+    xin = np.asfortranarray(x.T) if host else torch.from_numpy(x).cuda().t()
+    out, loss, routing = layer(xin, training=True, return_routing=True)
+    if not host:
+        out, loss = out.cpu().numpy(), float(loss.item())
+        routing = {k_: v.cpu().numpy() for k_, v in routing.items()}
+    assert np.array_equal(routing["indices"].T, ref["indices"])
+    assert rel_inf(out.T, ref["out"]) < F32_TOL
+    assert rel_inf(routing["gates"].T, ref["gates"]) < F32_TOL
+    assert rel_inf(routing["probs"].T, ref["probs"]) < F32_TOL
+    assert rel_inf(routing["logits"].T, ref["logits"]) < F32_TOL
+    assert abs(float(loss) - float(ref["loss"])) < F32_TOL * abs(float(ref["loss"]))
+    layer.close()
+
+
+# ---- FP32 path: shape sweep with ragged sizes ---------------------------------------------------
+
+@pytest.mark.parametrize("T", [1, 2, 31, 32, 33, 257])
+@pytest.mark.parametrize("E,k", [(2, 1), (8, 2), (8, 8), (66, 6)])
+def test_f32_shape_sweep(T, E, k):
+    run_case(T, 72, 100, 52, E, "topk", k, seed=T * 100 + E)
+
+
+@pytest.mark.parametrize("dims", [(512, 1376, 512), (36, 44, 20), (7, 9, 5), (128, 128, 128)])
+def test_f32_odd_dims(dims):
+    D, H, O = dims
+    run_case(50, D, H, O, 8, "topk", 2, seed=D)
+
+
+@pytest.mark.parametrize("activation", ["silu", "gelu", "relu", "identity"])
+def test_f32_activations(activation):
+    run_case(40, 64, 96, 64, 4, "topk", 2, activation=activation, seed=3)
+
+
+def test_f32_switch_gate_and_inference_mode():
+    run_case(100, 64, 96, 64, 8, "switch", 1, seed=5)
+    run_case(100, 64, 96, 64, 8, "topk", 2, seed=6, training=False)
+
+
+def test_f32_shared_expert_gating_and_layer_blend():
+    run_case(130, 64, 96, 64, 10, "shared", 3, 2, seed=7)
+    run_case(90, 64, 96, 48, 6, "topk", 2, seed=8, num_shared_experts=2)
+
+
+def test_f32_bf16_input_is_cast_like_the_router():
+    run_case(64, 64, 96, 64, 8, "topk", 2, seed=9, compute="f32", x_bf16=False)
+
+
+def test_aux_free_bias_selects_but_does_not_change_probs():
+    import mixtureofexperts_b200 as m
+
+    T, D, H, O, E = 64, 64, 96, 64, 8
+    x, w = orc.make_layer_inputs(11, T, D, H, O, E, init="normal", std=0.25)
+    bias = np.random.default_rng(3).normal(0, 1.5, E).astype(np.float32)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(2), balance_alpha=0.001, z_loss_weight=0.0, aux_free_bias=bias)
+    o_out, _, aux = orc.moe_layer_forward(cfg, w, x, training=False)
+    bl = m.AuxiliaryFreeLoss(E)
+    bl.bias = bias.copy()
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=m.TopKGating(2), z=0.0, balance_loss=bl)
+    out, _, routing = layer(torch.from_numpy(x).cuda().t(), training=False, return_routing=True)
+    assert np.array_equal(routing["indices"].cpu().numpy().T, aux["indices"])
+    assert rel_inf(routing["gates"].cpu().numpy().T, aux["gates"]) < F32_TOL
+    assert rel_inf(routing["probs"].cpu().numpy().T, aux["probs"]) < F32_TOL
+    assert rel_inf(out.cpu().numpy().T, o_out) < F32_TOL
+    layer.close()
+
+
+def test_router_bias_skews_routing_like_config4():
+    """A per-expert logit bias N(0,1.5) that is part of the logits (BASELINE config 4's skew)."""
+    T, D, H, O, E, S, k = 300, 64, 96, 64, 18, 2, 6
+    x, w = orc.make_layer_inputs(12, T, D, H, O, E, init="normal", std=0.25)
+    bias = np.concatenate([np.zeros(S), np.random.default_rng(4).normal(0, 1.5, E - S)]).astype(np.float32)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.SharedExpertGating(S, orc.TopKGating(k), E), z_loss_weight=0.001,
+                        router_bias=bias)
+    o_out, o_loss, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=device_gate("shared", k, S, E), router_bias=bias)
+    out, loss, routing = layer(torch.from_numpy(x).cuda().t(), training=True, return_routing=True)
+    check_indices(routing["indices"].cpu().numpy().T, aux["indices"], logits64(x, w, bias), k, S)
+    assert rel_inf(out.cpu().numpy().T, o_out) < F32_TOL
+    assert abs(float(loss.item()) - float(o_loss)) < F32_TOL * abs(float(o_loss))
+    counts = np.bincount(aux["indices"].ravel() - 1, minlength=E)
+    assert counts[S:].max() > 3 * max(counts[S:].min(), 1)  # routing is strongly skewed
+    layer.close()
+
+
+def test_empty_batch():
+    x, w = orc.make_layer_inputs(1, 1, 64, 96, 64, 4, init="normal", std=0.25)
+    layer = make_device_layer(w, D=64, H=96, O=64, gate=device_gate("topk", 2))
+    out, loss = layer(torch.empty((64, 0), device="cuda"), training=True)
+    assert tuple(out.shape) == (64, 0) and float(loss.item()) == 0.0
+    out, loss = layer(np.zeros((64, 0), dtype=np.float32, order="F"), training=True)
+    assert out.shape == (64, 0) and float(loss) == 0.0
+    layer.close()
+
+
+def test_two_runs_are_bit_identical_and_workspace_grows():
+    x, w = orc.make_layer_inputs(2, 700, 64, 96, 64, 8, init="normal", std=0.25)
+    layer = make_device_layer(w, D=64, H=96, O=64, gate=device_gate("topk", 2))
+    xt = torch.from_numpy(x).cuda()
+    small = layer(xt[:10].t(), training=True)[0].clone()
+    a, la = layer(xt.t(), training=True)
+    a = a.clone()
+    b, lb = layer(xt.t(), training=True)
+    assert torch.equal(a, b) and float(la.item()) == float(lb.item())
+    assert torch.equal(small, a[:, :10])
+    layer.close()
+
+
+def test_token_permutation_equivariance():
+    """Each token's output depends on that token only: permuting the batch permutes the output."""
+    x, w = orc.make_layer_inputs(3, 500, 64, 96, 64, 8, init="normal", std=0.25)
+    layer = make_device_layer(w, D=64, H=96, O=64, gate=device_gate("topk", 2))
+    xt = torch.from_numpy(x).cuda()
+    perm = torch.randperm(500, generator=torch.Generator().manual_seed(0)).cuda()
+    a = layer(xt.t(), training=False)[0].clone()
+    b = layer(xt[perm].t(), training=False)[0]
+    assert torch.equal(a[:, perm], b)
+    layer.close()
+
+
+# ---- stand-alone operators ----------------------------------------------------------------------
+
+def test_compute_gates_and_compute_loss_operators():
+    import mixtureofexperts_b200 as m
+
+    rng = np.random.default_rng(5)
+    logits = rng.standard_normal((333, 16)).astype(np.float32)
+    oi, og, op = orc.compute_gates(orc.TopKGating(4), logits)
+    lt = torch.from_numpy(logits).cuda()
+    di, dg, dp = m.compute_gates(m.TopKGating(4), lt.t())
+    assert np.array_equal(di.cpu().numpy().T, oi)
+    assert rel_inf(dg.cpu().numpy().T, og) < F32_TOL and rel_inf(dp.cpu().numpy().T, op) < F32_TOL
+    # the reference's own property: gates of a token sum to 1 within 1e-6
+    assert np.abs(dg.cpu().numpy().sum(axis=0) - 1).max() < 1e-6
+    oi2, og2, op2 = orc.compute_gates(orc.SharedExpertGating(2, orc.TopKGating(3), 16), logits)
+    di2, dg2, dp2 = m.compute_gates(m.SharedExpertGating(2, m.TopKGating(3), 16), lt.t())
+    assert np.array_equal(di2.cpu().numpy().T, oi2)
+    assert rel_inf(dg2.cpu().numpy().T, og2) < F32_TOL and rel_inf(dp2.cpu().numpy().T, op2) < F32_TOL
+    want = orc.switch_transformer_loss(0.01, oi, op)
+    got = m.compute_loss(m.SwitchTransformerLoss(0.01), di, dp)
+    assert abs(float(got.item()) - float(want)) < F32_TOL * float(want)
+    wz = orc.z_loss(0.001, logits)
+    gz = m.compute_loss(m.ZLoss(0.001), lt.t())
+    assert abs(float(gz.item()) - float(wz)) < F32_TOL * float(wz)
+
+
+def test_exact_ties_go_to_the_lowest_index():
+    import mixtureofexperts_b200 as m
+
+    logits = np.array([[0.5, 2.0, 2.0, 2.0, -1.0], [1.0, 1.0, 1.0, 1.0, 1.0]], dtype=np.float32)
+    di, dg, _ = m.compute_gates(m.TopKGating(2), torch.from_numpy(logits).cuda().t())
+    assert di.cpu().numpy().T.tolist() == [[2, 3], [1, 2]]
+
+
+# ---- BF16 tensor-core path ----------------------------------------------------------------------
+
+@pytest.mark.parametrize("T,E,k,D,H,O", [
+    (1000, 8, 2, 512, 1024, 512),     # several m-tiles per expert, ragged last tiles
+    (64, 8, 2, 256, 384, 256),        # fewer rows than one tile per expert
+    (300, 4, 1, 136, 200, 104),       # D, H, O not multiples of the 64/128/256 tile edges
+    (257, 66, 6, 128, 256, 128),      # many small experts, some empty
+    (1, 8, 2, 128, 256, 128),         # a single token
+])
+def test_bf16_tensor_core_path(T, E, k, D, H, O):
+    err = run_case(T, D, H, O, E, "topk", k, seed=T + E, compute="bf16", std=0.05)
+    assert err < BF16_TOL
+
+
+def test_bf16_shared_gating_and_f32_input():
+    run_case(400, 128, 256, 128, 10, "shared", 3, 2, seed=21, compute="bf16", std=0.05)
+    run_case(200, 128, 256, 120, 8, "topk", 2, seed=22, compute="bf16", std=0.05, x_bf16=False)
+
+
+def test_bf16_mixtral_shaped_slice_sampled_against_oracle():
+    """Mixtral-shaped widths (d_model 4096, ffn 14336) at a reduced expert/token count; the
+    oracle checks a sample of tokens (the dense oracle on all tokens would take minutes)."""
+    import mixtureofexperts_b200 as m
+
+    T, D, H, O, E = 2048, 4096, 14336, 4096, 2
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((T, D), device="cuda", generator=g).to(torch.bfloat16)
+    router = (torch.randn((E, D), device="cuda", generator=g) * 0.02)
+    ws = [[(torch.randn(s, device="cuda", generator=g) * 0.02).to(torch.bfloat16) for s in ((H, D), (O, H), (H, D))]
+          for _ in range(E)]
+    weights = orc.MoEWeights(router=router.cpu().numpy(),
+                             experts=[orc.GatedExpertWeights(w1=a, w2=b, w3=c) for a, b, c in ws])
+    layer = make_device_layer(weights, D=D, H=H, O=O, gate=m.TopKGating(1), compute_dtype="bf16", z=0.0)
+    out, loss, routing = layer(x.t(), training=True, return_routing=True)
+    torch.cuda.synchronize()
+    assert layer.device_status() == 0
+    sample = np.arange(0, T, 97)
+    xs = x[sample].float().cpu().numpy()
+    cpu_w = orc.MoEWeights(router=weights.router, experts=[
+        orc.GatedExpertWeights(w1=a.float().cpu().numpy(), w2=b.float().cpu().numpy(), w3=c.float().cpu().numpy())
+        for a, b, c in ws])
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(1), z_loss_weight=0.0)
+    o_out, _, aux = orc.moe_layer_forward(cfg, cpu_w, xs, training=False)
+    assert np.array_equal(routing["indices"].cpu().numpy().T[sample], aux["indices"])
+    err = rel_inf(out.cpu().numpy().T[sample], o_out)
+    assert err < BF16_TOL, err
+    layer.close()
