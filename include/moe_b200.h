@@ -121,6 +121,7 @@ int moe_layer_set_expert(moe_layer_t*, int expert, const void* w1, const void* w
                          int src_dtype, int layout, int src_is_device);
 
 /* Router.weight (src/core/router.jl:14-23): FP32 (E_router x D), E_router = E - S.
+ * (E_router = E in GATING mode: the first S rows are present but unused by the gate.)
  * logit_bias: optional FP32 [E_router] added to the logits (see bias_gates_only). */
 int moe_layer_set_router(moe_layer_t*, const float* w, const float* logit_bias,
                          int layout, int src_is_device);
@@ -153,11 +154,14 @@ int moe_compute_loss(float alpha, float z_weight, int n_probs, int k, int index_
                      const int32_t* indices, const float* probs, const float* logits,
                      int n_logits, int64_t T, float* loss, void* cuda_stream);
 
-/* Device time in milliseconds of each stage of the handle's last forward call, in order
- * {router, scan+loss, permute, gemm1, gemm2, combine, exchange}; only recorded after
- * moe_layer_set_profiling(h, 1).  Synchronises on the recorded events. */
-int moe_layer_set_profiling(moe_layer_t*, int enabled);
-int moe_layer_last_stage_ms(moe_layer_t*, float ms[7]);
+/* Stage timing.  moe_layer_set_profiling(h, slots) keeps CUDA events for the last `slots`
+ * forward calls (0 switches it off; it synchronises the device).  moe_layer_stage_ms gives the
+ * device time in milliseconds of each stage of the call made `calls_back` calls ago (0 = the
+ * last one), in order {router, scan+loss, permute, gemm1, gemm2, combine, exchange}; with
+ * expert parallelism gemm1 includes the dispatch and `exchange` is dispatch + combine of the
+ * last call.  It synchronises on that call's events. */
+int moe_layer_set_profiling(moe_layer_t*, int slots);
+int moe_layer_stage_ms(moe_layer_t*, int calls_back, float ms[7]);
 
 /* Number of kernel launches of this library issued through the handle since creation. */
 int64_t moe_layer_launch_count(const moe_layer_t*);

@@ -3,18 +3,35 @@
 The names mirror the reference package (create_moe_config, MoELayer, TopKGating, SwitchGating,
 GatedExpert, SwitchTransformerLoss, convert_to_moe, sample_moe, ...); the arithmetic runs in
 hand-written CUDA kernels behind the C ABI of ``lib/libmoe_b200.so`` (include/moe_b200.h).
-Importing the package requires that library; there is no CPU or PyTorch fallback.
+Using any of these names requires that library; there is no CPU or PyTorch fallback.  Names
+are resolved on first use so that ``python -m mixtureofexperts_b200.build`` can (re)build the
+library before it is loaded.
 """
-from ._lib import LIB_PATH, MoEError, version
-from .experts import Expert, GatedExpert, gelu, identity, relu, silu, swish
-from .gating import GatingMechanism, SharedExpertGating, SwitchGating, TopKGating, compute_gates
-from .layer import (MoEConfig, MoELayer, Router, create_moe_config, create_moe_layer, load_balance_score,
-                    reset_stats)
-from .losses import AuxiliaryFreeLoss, LoadBalancingLoss, SwitchTransformerLoss, ZLoss, compute_loss
+import importlib
 
-__all__ = [
-    "LIB_PATH", "MoEError", "version", "Expert", "GatedExpert", "gelu", "identity", "relu", "silu", "swish",
-    "GatingMechanism", "SharedExpertGating", "SwitchGating", "TopKGating", "compute_gates", "MoEConfig",
-    "MoELayer", "Router", "create_moe_config", "create_moe_layer", "load_balance_score", "reset_stats",
-    "AuxiliaryFreeLoss", "LoadBalancingLoss", "SwitchTransformerLoss", "ZLoss", "compute_loss",
-]
+_EXPORTS = {
+    "LIB_PATH": "_lib", "MoEError": "_lib", "version": "_lib",
+    "Expert": "experts", "GatedExpert": "experts", "gelu": "experts", "identity": "experts", "relu": "experts",
+    "silu": "experts", "swish": "experts",
+    "GatingMechanism": "gating", "SharedExpertGating": "gating", "SwitchGating": "gating", "TopKGating": "gating",
+    "compute_gates": "gating",
+    "MoEConfig": "layer", "MoELayer": "layer", "Router": "layer", "create_moe_config": "layer",
+    "create_moe_layer": "layer", "load_balance_score": "layer", "reset_stats": "layer",
+    "AuxiliaryFreeLoss": "losses", "LoadBalancingLoss": "losses", "SwitchTransformerLoss": "losses",
+    "ZLoss": "losses", "compute_loss": "losses",
+}
+
+__all__ = sorted(_EXPORTS)
+
+
+def __getattr__(name):
+    mod = _EXPORTS.get(name)
+    if mod is None:
+        raise AttributeError(f"module 'mixtureofexperts_b200' has no attribute '{name}'")
+    value = getattr(importlib.import_module(f".{mod}", __name__), name)
+    globals()[name] = value
+    return value
+
+
+def __dir__():
+    return __all__

@@ -22,7 +22,7 @@ LAYOUT_IN_CONTIG, LAYOUT_OUT_CONTIG = 0, 1
 EXPORTS = [
     "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_router", "moe_layer_dims",
     "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_loss",
-    "moe_layer_set_profiling", "moe_layer_last_stage_ms", "moe_layer_launch_count",
+    "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_launch_count",
     "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_layer_destroy",
     "moe_last_error", "moe_version",
 ]
@@ -69,7 +69,7 @@ def _load():
     lib.moe_compute_gates.argtypes = [i32, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
     lib.moe_compute_loss.argtypes = [f32, f32, i32, i32, i32, vp, vp, vp, i32, i64, vp, vp]
     lib.moe_layer_set_profiling.argtypes = [vp, i32]
-    lib.moe_layer_last_stage_ms.argtypes = [vp, C.POINTER(C.c_float)]
+    lib.moe_layer_stage_ms.argtypes = [vp, i32, C.POINTER(C.c_float)]
     lib.moe_layer_launch_count.argtypes = [vp]
     lib.moe_layer_launch_count.restype = C.c_int64
     lib.moe_layer_device_status.argtypes = [vp, C.POINTER(C.c_int32)]

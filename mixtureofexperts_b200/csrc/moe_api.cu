@@ -101,10 +101,11 @@ struct moe_layer {
     void* hopt = nullptr;
     size_t hopt_bytes = 0;
 
-    // profiling
-    bool profiling = false;
-    cudaEvent_t ev[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-    bool ev_valid = false;
+    // profiling: a ring of event sets, one set per forward call
+    int prof_slots = 0;
+    std::vector<cudaEvent_t> ev;   // [prof_slots][8]
+    int64_t prof_calls = 0;
+    int prof_cur = 0;
     int64_t launches = 0;
 
     EpState* ep = nullptr;
@@ -214,7 +215,7 @@ int ensure_plan(moe_layer* L, const void* a1, const void* a2, int64_t rows) {
 }
 
 inline void stage_mark(moe_layer* L, int i, cudaStream_t s) {
-    if (L->profiling && L->ev_valid) cudaEventRecord(L->ev[i], s);
+    if (L->prof_slots > 0) cudaEventRecord(L->ev[(size_t)L->prof_cur * 8 + i], s);
 }
 
 int check_ready(moe_layer* L) {
@@ -291,6 +292,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     if (!L->ep && L->plan_dirty && (rc = ensure_plan(L, L->xp, L->h, L->P_cap))) return rc;
 
     const int num_cta = (int)((T + L->tokens_per_cta - 1) / L->tokens_per_cta);
+    if (L->prof_slots > 0) L->prof_cur = (int)(L->prof_calls++ % L->prof_slots);
     stage_mark(L, 0, s);
 
     RouterParams r;
@@ -508,8 +510,7 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->hout);
     dev_free(L->hopt);
     if (L->plan) tc_plan_destroy(L->plan);
-    if (L->ev_valid)
-        for (auto& e : L->ev) cudaEventDestroy(e);
+    for (auto& e : L->ev) cudaEventDestroy(e);
     if (L->stream) cudaStreamDestroy(L->stream);
     delete L;
     return MOE_OK;
@@ -686,27 +687,38 @@ int moe_compute_loss(float alpha, float z_weight, int n_probs, int k, int index_
     return MOE_OK;
 }
 
-int moe_layer_set_profiling(moe_layer_t* L, int enabled) {
+int moe_layer_set_profiling(moe_layer_t* L, int slots) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    if (slots < 0 || slots > 1024) return fail(MOE_ERR_INVALID, "slots must be in 0..1024");
     CUDA_TRY(cudaSetDevice(L->device));
-    if (enabled && !L->ev_valid) {
+    CUDA_TRY(cudaDeviceSynchronize());
+    for (auto& e : L->ev) cudaEventDestroy(e);
+    L->ev.clear();
+    L->prof_slots = 0;
+    L->prof_calls = 0;
+    L->prof_cur = 0;
+    if (slots > 0) {
+        L->ev.resize((size_t)slots * 8, nullptr);
         for (auto& e : L->ev) CUDA_TRY(cudaEventCreate(&e));
-        L->ev_valid = true;
+        L->prof_slots = slots;
     }
-    L->profiling = enabled != 0;
     return MOE_OK;
 }
 
-int moe_layer_last_stage_ms(moe_layer_t* L, float ms[7]) {
+int moe_layer_stage_ms(moe_layer_t* L, int calls_back, float ms[7]) {
     if (!L || !ms) return fail(MOE_ERR_INVALID, "null argument");
-    if (!L->profiling || !L->ev_valid) return fail(MOE_ERR_STATE, "profiling is not enabled");
+    if (L->prof_slots <= 0) return fail(MOE_ERR_STATE, "profiling is not enabled");
+    if (calls_back < 0 || calls_back >= L->prof_slots || calls_back >= L->prof_calls)
+        return fail(MOE_ERR_INVALID, "that call is not in the profiling ring");
     CUDA_TRY(cudaSetDevice(L->device));
-    CUDA_TRY(cudaEventSynchronize(L->ev[6]));
-    // events: 0 start, 1 router, 2 scan, 3 permute, 4 gemm1, 5 gemm2, 6 combine; 7 = end of exchange
+    const int slot = (int)((L->prof_calls - 1 - calls_back) % L->prof_slots);
+    cudaEvent_t* ev = &L->ev[(size_t)slot * 8];
+    CUDA_TRY(cudaEventSynchronize(ev[6]));
+    // events: 0 start, 1 router, 2 scan, 3 permute, 4 gemm1, 5 gemm2, 6 combine
     for (int i = 0; i < 7; ++i) ms[i] = 0.f;
     for (int i = 0; i < 6; ++i) {
         float v = 0.f;
-        if (cudaEventElapsedTime(&v, L->ev[i], L->ev[i + 1]) == cudaSuccess) ms[i] = v;
+        if (cudaEventElapsedTime(&v, ev[i], ev[i + 1]) == cudaSuccess) ms[i] = v;
     }
     if (L->ep) ms[6] = ep_last_exchange_ms(L->ep);
     return MOE_OK;

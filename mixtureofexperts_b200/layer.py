@@ -134,6 +134,22 @@ def _weight_ptr_layout(w):
     return a.ctypes.data, _lib.DTYPE_F32, _lib.LAYOUT_IN_CONTIG, 0, a
 
 
+class _HostValue:
+    """A host result with the two accessors the lazy statistics use on device tensors."""
+
+    def __init__(self, v):
+        self.v = v
+
+    def cpu(self):
+        return self
+
+    def numpy(self):
+        return np.asarray(self.v)
+
+    def item(self):
+        return float(self.v)
+
+
 class MoELayer:
     """MoELayer(config) (src/core/moe_layer.jl:34-63) and its call
     ``moe(x; training=false, return_stats=false) -> (output, balance_loss[, training_stats])``
@@ -193,20 +209,35 @@ class MoELayer:
             experts = [GatedExpert(config.input_dim, config.hidden_dim, config.output_dim, config.activation,
                                    rng=rng, device=dev) if e in self.expert_range else None
                        for e in range(config.num_experts)]
-        self.experts = list(experts)
+        # `experts` may be a callable e -> GatedExpert: each expert is then built, copied to the
+        # device and dropped, so the host (or torch) copy of a large layer never exists at once
+        self._expert_factory = experts if callable(experts) else None
+        self.experts = [None] * config.num_experts if callable(experts) else list(experts)
         self.router = router if router is not None else Router(
             config.input_dim, self.e_router, config.gate_type, noise_scale=config.noise_scale,
             use_noise_network=config.use_noise_network, use_fp32=config.use_fp32_router, rng=rng)
-        self.training_stats = {"tokens_per_expert": np.zeros(config.num_experts, dtype=np.int64),
-                               "routing_entropy": [], "capacity_overflow": 0}
+        self._stats = {"tokens_per_expert": np.zeros(config.num_experts, dtype=np.int64),
+                       "routing_entropy": [], "capacity_overflow": 0}
+        self._pending = []          # device-side (tokens_per_expert, entropy) of calls not yet folded in
         self.sync_weights()
+
+    @property
+    def training_stats(self) -> dict:
+        """moe.training_stats (src/core/moe_layer.jl:56-60): cumulative tokens_per_expert, the
+        routing entropy of every call, capacity_overflow.  Device-side results of earlier
+        calls are folded in here, so a forward on CUDA tensors never waits for the GPU."""
+        for tpe, ent in self._pending:
+            self._stats["tokens_per_expert"] += tpe.cpu().numpy()
+            self._stats["routing_entropy"].append(float(ent.item()))
+        self._pending.clear()
+        return self._stats
 
     # -- weights ---------------------------------------------------------------------------
     def sync_weights(self) -> None:
         """Copy (and repack) the experts' and the router's current weights into the device
         handle; call again after mutating them."""
         for e in self.expert_range:
-            ex = self.experts[e]
+            ex = self._expert_factory(e) if self._expert_factory else self.experts[e]
             p1, d1, l1, dev1, k1 = _weight_ptr_layout(ex.w1)
             p2, d2, l2, dev2, k2 = _weight_ptr_layout(ex.w2)
             p3, d3, l3, dev3, k3 = _weight_ptr_layout(ex.w3)
@@ -247,24 +278,30 @@ class MoELayer:
         _lib.check(_lib.lib.moe_layer_set_router(self._handle, p, bias_ptr, lay, dev))
 
     # -- forward ---------------------------------------------------------------------------
-    def __call__(self, x, training: bool = False, return_stats: bool = False, return_routing: bool = False):
+    def __call__(self, x, training: bool = False, return_stats: bool = False, return_routing: bool = False,
+                 out=None):
+        """``out`` (optional, no counterpart in the reference): a preallocated float32 (T, output_dim)
+        C-ordered buffer of the same kind as x (CUDA tensor / NumPy array, e.g. pinned) that
+        receives the result; the returned output is its (output_dim, T) view."""
         cfg = self.config
         if x.ndim != 2 or x.shape[0] != cfg.input_dim:
             raise _lib.MoEError(_lib.ERR_INVALID, f"x must have shape (input_dim={cfg.input_dim}, T), got {tuple(x.shape)}")
         T = int(x.shape[1])
-        want_stats = return_stats or cfg.num_shared_experts == 0
+        aux_free = isinstance(self.balance_loss, AuxiliaryFreeLoss) and training
+        want_stats = cfg.num_shared_experts == 0 or aux_free
         if _is_torch(x) and x.is_cuda:
-            out, loss, extra = self._forward_torch(x, T, training, want_stats, return_routing)
+            out, loss, extra = self._forward_torch(x, T, training, want_stats, return_routing, out)
         else:
-            out, loss, extra = self._forward_numpy(np.asarray(x) if not _is_torch(x) else x.numpy(), T, training,
-                                                   want_stats, return_routing)
+            out, loss, extra = self._forward_host(x if _is_torch(x) else np.asarray(x), T, training, want_stats,
+                                                  return_routing, out)
         if cfg.num_shared_experts == 0:
             # update_stats! (src/core/moe_layer.jl:250-264) runs in forward_standard only
-            self.training_stats["tokens_per_expert"] += extra["tokens_per_expert"]
-            self.training_stats["routing_entropy"].append(float(extra["routing_entropy"]))
-        if isinstance(self.balance_loss, AuxiliaryFreeLoss) and training:
+            self._pending.append((extra["tokens_per_expert"], extra["routing_entropy"]))
+            if len(self._pending) > 256:
+                _ = self.training_stats
+        if aux_free:
             # compute_loss(::AuxiliaryFreeLoss) updates the bias first (auxiliary_free.jl:73-83)
-            self.balance_loss.update_bias(extra["tokens_per_expert"])
+            self.balance_loss.update_bias(extra["tokens_per_expert"].cpu().numpy())
             self.sync_router()
         ret = (out, loss)
         if return_stats:
@@ -273,7 +310,7 @@ class MoELayer:
             ret = ret + ({k: extra[k] for k in ("indices", "gates", "probs", "logits")},)
         return ret
 
-    def _forward_torch(self, x, T, training, want_stats, want_routing):
+    def _forward_torch(self, x, T, training, want_stats, want_routing, out=None):
         import torch
 
         cfg = self.config
@@ -288,7 +325,11 @@ class MoELayer:
             xt = xt.float()
             xd = _lib.DTYPE_F32
         dev = xt.device
-        out = torch.empty((T, cfg.output_dim), dtype=torch.float32, device=dev)
+        if out is None:
+            out = torch.empty((T, cfg.output_dim), dtype=torch.float32, device=dev)
+        elif (tuple(out.shape) != (T, cfg.output_dim) or out.dtype != torch.float32 or not out.is_contiguous()
+              or out.device != dev):
+            raise _lib.MoEError(_lib.ERR_INVALID, "out must be a contiguous float32 (T, output_dim) tensor on x's device")
         loss = torch.zeros((), dtype=torch.float32, device=dev)
         o = _lib.ForwardOutputs()
         o.loss = loss.data_ptr()
@@ -309,21 +350,48 @@ class MoELayer:
             _lib.check(_lib.lib.moe_layer_forward(self._handle, xt.data_ptr(), xd, T, int(training), out.data_ptr(),
                                                   C.byref(o), stream))
         if want_stats:
-            extra["tokens_per_expert"] = tpe.cpu().numpy()
-            extra["routing_entropy"] = float(ent.item())
+            extra["tokens_per_expert"] = tpe
+            extra["routing_entropy"] = ent
         return out.t(), loss, extra
 
-    def _forward_numpy(self, x, T, training, want_stats, want_routing):
+    def _forward_host(self, x, T, training, want_stats, want_routing, out=None):
+        """Host buffers (NumPy arrays or torch CPU tensors, pinned or not) through
+        moe_layer_forward_host: copy in, compute, copy out, synchronise."""
         cfg = self.config
-        if x.dtype != np.float32:
-            x = x.astype(np.float32)
-        xt = np.ascontiguousarray(x.T)
-        out = np.empty((T, cfg.output_dim), dtype=np.float32)
+        use_torch = _is_torch(x)
+        if use_torch:
+            import torch
+
+            xt = x.t()
+            if xt.dtype not in (torch.float32, torch.bfloat16):
+                xt = xt.float()
+            if not xt.is_contiguous():
+                xt = xt.contiguous()
+            xd = _lib.DTYPE_BF16 if xt.dtype == torch.bfloat16 else _lib.DTYPE_F32
+            x_ptr = xt.data_ptr()
+            if out is None:
+                out = torch.empty((T, cfg.output_dim), dtype=torch.float32)
+            elif (tuple(out.shape) != (T, cfg.output_dim) or out.dtype != torch.float32 or not out.is_contiguous()
+                  or out.is_cuda):
+                raise _lib.MoEError(_lib.ERR_INVALID, "out must be a contiguous float32 (T, output_dim) CPU tensor")
+            out_ptr = out.data_ptr()
+            out_view = out.t()
+        else:
+            if x.dtype != np.float32:
+                x = x.astype(np.float32)
+            xt = np.ascontiguousarray(x.T)
+            xd = _lib.DTYPE_F32
+            x_ptr = xt.ctypes.data
+            if out is None:
+                out = np.empty((T, cfg.output_dim), dtype=np.float32)
+            elif out.shape != (T, cfg.output_dim) or out.dtype != np.float32 or not out.flags.c_contiguous:
+                raise _lib.MoEError(_lib.ERR_INVALID, "out must be a C-ordered float32 (T, output_dim) array")
+            out_ptr = out.ctypes.data
+            out_view = out.T
         loss = np.zeros(1, dtype=np.float32)
         o = _lib.ForwardOutputs()
         o.loss = loss.ctypes.data
         extra = {}
-        keep = []
         if want_stats:
             tpe = np.zeros(cfg.num_experts, dtype=np.int64)
             ent = np.zeros(1, dtype=np.float32)
@@ -335,20 +403,21 @@ class MoELayer:
             logits = np.empty((T, self.e_router), dtype=np.float32)
             o.indices, o.gates, o.probs, o.logits = idx.ctypes.data, gates.ctypes.data, probs.ctypes.data, logits.ctypes.data
             extra.update(indices=idx.T, gates=gates.T, probs=probs.T, logits=logits.T)
-        _lib.check(_lib.lib.moe_layer_forward_host(self._handle, xt.ctypes.data, _lib.DTYPE_F32, T, int(training),
-                                                   out.ctypes.data, C.byref(o)))
+        _lib.check(_lib.lib.moe_layer_forward_host(self._handle, x_ptr, xd, T, int(training), out_ptr, C.byref(o)))
         if want_stats:
-            extra["tokens_per_expert"] = tpe
-            extra["routing_entropy"] = float(ent[0])
-        return out.T, np.float32(loss[0]), extra
+            extra["tokens_per_expert"] = _HostValue(tpe)
+            extra["routing_entropy"] = _HostValue(ent[0])
+        return out_view, np.float32(loss[0]), extra
 
     # -- helpers ---------------------------------------------------------------------------
-    def set_profiling(self, enabled: bool = True) -> None:
-        _lib.check(_lib.lib.moe_layer_set_profiling(self._handle, int(enabled)))
+    def set_profiling(self, slots: int = 1) -> None:
+        """Keep per-stage CUDA events for the last ``slots`` forward calls (0 = off)."""
+        _lib.check(_lib.lib.moe_layer_set_profiling(self._handle, int(slots)))
 
-    def last_stage_ms(self) -> dict:
+    def stage_ms(self, calls_back: int = 0) -> dict:
+        """Device milliseconds per stage of the forward made ``calls_back`` calls ago."""
         ms = (C.c_float * 7)()
-        _lib.check(_lib.lib.moe_layer_last_stage_ms(self._handle, ms))
+        _lib.check(_lib.lib.moe_layer_stage_ms(self._handle, int(calls_back), ms))
         names = ["router", "scan_loss", "permute", "gemm1", "gemm2", "combine", "exchange"]
         return dict(zip(names, [float(v) for v in ms]))
 
@@ -383,9 +452,10 @@ def create_moe_layer(input_dim: int, hidden_dim: int, output_dim: int, **kwargs)
 
 def reset_stats(moe: MoELayer) -> None:
     """reset_stats!(moe) (src/core/moe_layer.jl:271-276)."""
-    moe.training_stats["tokens_per_expert"][:] = 0
-    moe.training_stats["routing_entropy"].clear()
-    moe.training_stats["capacity_overflow"] = 0
+    st = moe.training_stats
+    st["tokens_per_expert"][:] = 0
+    st["routing_entropy"].clear()
+    st["capacity_overflow"] = 0
 
 
 def load_balance_score(expert_counts) -> float:
