@@ -59,58 +59,65 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock, power and throttle reasons of one GPU through NVML from a thread while
+    the timed region runs (the same quantities `nvidia-smi --query-gpu=clocks.sm,...` prints)."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
+    def __init__(self, uuid: str):
+        self.uuid = uuid
+        self.samples = []
+        self.stop_flag = threading.Event()
+        self.thread = None
+        self.err = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            pynvml.nvmlInit()
+            u = self.uuid if self.uuid.startswith("GPU-") else "GPU-" + self.uuid
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(u.encode() if hasattr(u, "encode") else u)
+            self.nv = pynvml
+        except Exception as exc:  # noqa: BLE001
+            self.err = f"NVML unavailable: {exc}"
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
-    def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, power = [], [], []
-        reasons = set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 9:
-                continue
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-                power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                mx = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((time.perf_counter(), sm, mx, pw, rs))
+            except Exception as exc:  # noqa: BLE001
+                self.err = str(exc)
+                return
+            time.sleep(0.002)
+
+    def mark(self):
+        return time.perf_counter()
+
+    def stop(self, t0=None, t1=None):
+        self.stop_flag.set()
+        if self.thread:
+            self.thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.err or "no samples"]}
+        sel = [s for s in self.samples if (t0 is None or s[0] >= t0) and (t1 is None or s[0] <= t1)] or self.samples
+        sm = sorted(s[1] for s in sel)
+        bits = 0
+        for s in sel:
+            bits |= int(s[4])
+        # NVML clocks-event-reason bits
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+                 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting"}
+        reasons = sorted(n for b, n in names.items() if bits & b)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(s[2] for s in sel), "power_w_max": max(s[3] for s in sel),
+                "samples": len(sel), "reasons": reasons}
 
 
 def make_expert_factory(w, torch, device):
@@ -223,6 +230,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override the tokens per GPU (profiling of small cases)")
+    ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -233,6 +241,9 @@ def main():
     w = dict(WORKLOADS[name])
     if args.tokens > 0:
         w["T"] = args.tokens
+    if args.experts > 0:
+        w["E"] = args.experts
+        w["desc"] += f" [experts overridden to {args.experts}]"
     if args.impl == "reference":
         run_reference_arm(args, w, name)
         return
@@ -276,19 +287,21 @@ def main():
         step()
     barrier()
     layer.set_profiling(min(args.steps, 1024))
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(local_rank).uuid))
     if rank == 0:
         sampler.start()
     launches0 = layer.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_mark0 = sampler.mark()
     ev0.record()
     for _ in range(args.steps):
         _, loss = step()
     ev1.record()
     barrier()
+    t_mark1 = sampler.mark()
     ms_total = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_mark0, t_mark1) if rank == 0 else None
     launches = layer.launch_count() - launches0
     status = layer.device_status()
     if world > 1:
