@@ -183,6 +183,17 @@ int moe_ep_unique_id(void* id128);
  * the balance loss is reduced over all ranks' tokens. */
 int moe_ep_init(moe_layer_t*, const void* id128, int rank, int world);
 
+/* Host-only helper (no CUDA, no NCCL): the row layout one rank uses for the dispatch and the
+ * combine, from the all-gathered pair counts counts[world][num_experts].  send_off[E+1]: first
+ * row, in the rank's permuted buffer, of its pairs for expert e; recv_off[E/world][world]:
+ * first received row of the pairs rank r sends to local expert el; local_off[E/world+1] and
+ * tile_prefix[E/world+1]: received rows grouped by local expert and their tile_m-row tile
+ * prefix.  Returns the number of rows the rank receives, or a negative MOE_ERR_*.  A forward
+ * call computes exactly this internally; it is exported so the exchange can be checked without
+ * GPUs. */
+int64_t moe_ep_layout(const int32_t* counts, int world, int num_experts, int rank, int tile_m,
+                      int64_t* send_off, int64_t* recv_off, int32_t* local_off, int32_t* tile_prefix);
+
 int moe_layer_destroy(moe_layer_t*);
 
 const char* moe_last_error(void);     /* thread-local message of the last failure */

@@ -23,7 +23,7 @@ EXPORTS = [
     "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_router", "moe_layer_dims",
     "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_loss",
     "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_launch_count",
-    "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_layer_destroy",
+    "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_ep_layout", "moe_layer_destroy",
     "moe_last_error", "moe_version",
 ]
 
@@ -75,12 +75,15 @@ def _load():
     lib.moe_layer_device_status.argtypes = [vp, C.POINTER(C.c_int32)]
     lib.moe_ep_unique_id.argtypes = [vp]
     lib.moe_ep_init.argtypes = [vp, vp, i32, i32]
+    lib.moe_ep_layout.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    lib.moe_ep_layout.restype = C.c_int64
     lib.moe_layer_destroy.argtypes = [vp]
     lib.moe_last_error.restype = C.c_char_p
     lib.moe_version.restype = C.c_char_p
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name not in ("moe_last_error", "moe_version", "moe_layer_launch_count"):
+        if name not in ("moe_last_error", "moe_version", "moe_layer_launch_count", "moe_route_static_error",
+                        "moe_route_static_scratch_bytes", "moe_ep_layout"):
             fn.restype = C.c_int
     return lib
 

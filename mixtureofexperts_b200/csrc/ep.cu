@@ -115,6 +115,30 @@ struct EpState {
     bool timed = false;
 };
 
+// Pure host arithmetic (no CUDA, no NCCL): see ep.h.
+int64_t ep_plan_layout(const int32_t* cnt, int W, int E, int me, int tile_m, int64_t* send_off, int64_t* recv_off,
+                       int32_t* local_off, int32_t* tile_prefix) {
+    const int per = E / W;
+    send_off[0] = 0;
+    for (int e = 0; e < E; ++e) send_off[e + 1] = send_off[e] + cnt[(size_t)me * E + e];
+    int64_t rows = 0;
+    int64_t tiles = 0;
+    for (int el = 0; el < per; ++el) {
+        local_off[el] = (int32_t)rows;
+        tile_prefix[el] = (int32_t)tiles;
+        int64_t n_e = 0;
+        for (int r = 0; r < W; ++r) {
+            recv_off[(size_t)el * W + r] = rows + n_e;
+            n_e += cnt[(size_t)r * E + me * per + el];
+        }
+        rows += n_e;
+        tiles += (n_e + tile_m - 1) / tile_m;
+    }
+    local_off[per] = (int32_t)rows;
+    tile_prefix[per] = (int32_t)tiles;
+    return rows;
+}
+
 int ep_unique_id(void* id128, char* err, size_t errlen) {
     int rc = load_nccl(err, errlen);
     if (rc) return rc;
@@ -206,28 +230,12 @@ int ep_exchange_and_run(EpState* ep, const EpCall& c, EpRunFn run, void* self, i
     EP_CUDA(cudaStreamSynchronize(s));
     const int32_t* cnt = ep->h_all_counts;  // cnt[r*E + e]
 
-    // send layout: my rows grouped by global expert
+    // send layout (my rows grouped by global expert) and receive layout ([local expert][source])
     std::vector<int64_t> send_off((size_t)E + 1, 0);
-    for (int e = 0; e < E; ++e) send_off[e + 1] = send_off[e] + cnt[(size_t)me * E + e];
-    // receive layout: [local expert][source rank]
-    std::vector<int64_t> recv_off((size_t)per * W + 1, 0);
+    std::vector<int64_t> recv_off((size_t)per * W, 0);
     int32_t* h_off = ep->h_tables;
     int32_t* h_tp = ep->h_tables + (per + 1);
-    int64_t rows = 0;
-    int tiles = 0;
-    for (int el = 0; el < per; ++el) {
-        h_off[el] = (int32_t)rows;
-        h_tp[el] = tiles;
-        int64_t n_e = 0;
-        for (int r = 0; r < W; ++r) {
-            recv_off[(size_t)el * W + r] = rows + n_e;
-            n_e += cnt[(size_t)r * E + me * per + el];
-        }
-        rows += n_e;
-        tiles += (int)((n_e + g.tile_m - 1) / g.tile_m);
-    }
-    h_off[per] = (int32_t)rows;
-    h_tp[per] = tiles;
+    const int64_t rows = ep_plan_layout(cnt, W, E, me, g.tile_m, send_off.data(), recv_off.data(), h_off, h_tp);
     if (rows > 0x7fffffffLL) return set_err(err, errlen, MOE_ERR_UNSUPPORTED, "more than 2^31-1 received rows");
 
     if (rows > ep->rows_cap) {

@@ -34,6 +34,13 @@ struct EpCall {
 typedef int (*EpRunFn)(void* self, const void* a_in, void* h_buf, void* y_buf, const int32_t* expert_offset,
                        const int32_t* tile_prefix, int64_t rows, int n_experts, int64_t cap_rows, cudaStream_t s);
 
+// Row layout of one rank's exchange from the all-gathered pair counts cnt[W][E] (host only).
+// send_off[E+1]: first row, in this rank's permuted buffer, of the pairs routed to expert e.
+// recv_off[per][W]: first received row of the pairs rank r sends to local expert el.
+// local_off[per+1], tile_prefix[per+1]: the received rows grouped by local expert and their
+// m-tile prefix (tile_m rows per tile).  Returns the number of rows this rank receives.
+int64_t ep_plan_layout(const int32_t* cnt, int W, int E, int me, int tile_m, int64_t* send_off, int64_t* recv_off,
+                       int32_t* local_off, int32_t* tile_prefix);
 int ep_unique_id(void* id128, char* err, size_t errlen);
 int ep_create(EpState** out, const EpConfig& cfg, const void* id128, char* err, size_t errlen);
 void ep_destroy(EpState*);

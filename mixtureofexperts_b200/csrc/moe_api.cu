@@ -735,6 +735,15 @@ int moe_layer_device_status(moe_layer_t* L, int32_t* status) {
 
 int moe_ep_unique_id(void* id128) { return ep_unique_id(id128, g_err, sizeof(g_err)); }
 
+int64_t moe_ep_layout(const int32_t* counts, int world, int num_experts, int rank, int tile_m, int64_t* send_off,
+                      int64_t* recv_off, int32_t* local_off, int32_t* tile_prefix) {
+    if (!counts || !send_off || !recv_off || !local_off || !tile_prefix)
+        return fail(MOE_ERR_INVALID, "null argument");
+    if (world < 1 || rank < 0 || rank >= world || num_experts < 1 || num_experts % world || tile_m < 1)
+        return fail(MOE_ERR_INVALID, "bad world/rank/num_experts/tile_m");
+    return ep_plan_layout(counts, world, num_experts, rank, tile_m, send_off, recv_off, local_off, tile_prefix);
+}
+
 int moe_ep_init(moe_layer_t* L, const void* id128, int rank, int world) {
     if (!L || !id128) return fail(MOE_ERR_INVALID, "null argument");
     if (world < 1 || rank < 0 || rank >= world) return fail(MOE_ERR_INVALID, "bad rank/world");

@@ -38,31 +38,21 @@ def broadcast_unique_id(dist, rank: int, device=None, make_id=new_unique_id) -> 
 
 def exchange_layout(counts, rank: int, tile_m: int):
     """Row layout of one rank's dispatch/combine, from the all-gathered pair counts
-    ``counts[world][E]`` (the same arithmetic libmoe_b200 runs on the host inside a forward).
+    ``counts[world][E]`` -- the host arithmetic a forward call runs (moe_ep_layout of the C ABI).
 
-    Returns (send_off[E+1], recv_off[per][world], local_off[per+1], tile_prefix[per+1]):
+    Returns (send_off[E+1], recv_off[per][world], local_off[per+1], tile_prefix[per+1], rows):
     rows this rank sends to expert e start at send_off[e] of its permuted buffer; rows it
     receives from rank r for its local expert el land at recv_off[el][r]; local_off/tile_prefix
     describe the received rows grouped by local expert for the grouped GEMM."""
-    counts = np.asarray(counts, dtype=np.int64)
+    counts = np.ascontiguousarray(counts, dtype=np.int32)
     world, E = counts.shape
     per = E // world
     send_off = np.zeros(E + 1, dtype=np.int64)
-    send_off[1:] = np.cumsum(counts[rank])
     recv_off = np.zeros((per, world), dtype=np.int64)
-    local_off = np.zeros(per + 1, dtype=np.int64)
-    tile_prefix = np.zeros(per + 1, dtype=np.int64)
-    rows = 0
-    tiles = 0
-    for el in range(per):
-        local_off[el] = rows
-        tile_prefix[el] = tiles
-        n_e = 0
-        for r in range(world):
-            recv_off[el, r] = rows + n_e
-            n_e += counts[r, rank * per + el]
-        rows += n_e
-        tiles += (n_e + tile_m - 1) // tile_m
-    local_off[per] = rows
-    tile_prefix[per] = tiles
-    return send_off, recv_off, local_off, tile_prefix
+    local_off = np.zeros(per + 1, dtype=np.int32)
+    tile_prefix = np.zeros(per + 1, dtype=np.int32)
+    rows = _lib.lib.moe_ep_layout(counts.ctypes.data, world, E, int(rank), int(tile_m), send_off.ctypes.data,
+                                  recv_off.ctypes.data, local_off.ctypes.data, tile_prefix.ctypes.data)
+    if rows < 0:
+        _lib.check(int(rows))
+    return send_off, recv_off, local_off, tile_prefix, int(rows)
