@@ -196,6 +196,34 @@ int64_t moe_ep_layout(const int32_t* counts, int world, int num_experts, int ran
 
 int moe_layer_destroy(moe_layer_t*);
 
+/* ---- routing without any allocation -------------------------------------------------------
+ * No counterpart in the reference.  For callers that cannot allocate device memory -- a
+ * process that gives all of HBM to its own pools at start-up so that a later cudaMalloc fails,
+ * or a latency-critical loop that cannot take the device-wide synchronisation an allocation or
+ * free implies -- this runs the layer's fused router (gate GEMM, softmax, top-k, renormalised
+ * gates) and its Switch + z loss with the kernels' scratch held in a file-scope device array
+ * of moe_route_static_scratch_bytes() bytes (8 MiB, held by every GPU that loads the library
+ * until the process exits).  It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   x [T][input_dim] (x_dtype), router_w FP32 [num_experts][input_dim] (input contiguous),
+ *   logit_bias FP32 [num_experts] or NULL: device pointers owned by the caller.
+ *   indices/gates [T][k_tot] (k_tot = top_k, + num_shared for MOE_GATE_SHARED_TOPK), probs
+ *   [T][num_experts] (nullable), loss [1] (nullable; 0 is written when training == 0): device.
+ * Sizes whose scratch does not fit the array are rejected with MOE_ERR_INVALID (the message
+ * says how much was needed); MoEConfig.num_shared_experts (LAYER_BLEND) is not offered here.
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress) with
+ * that device current; make that first call outside any stream capture.  All calls share the
+ * one array, which keeps the previous call's contents (nothing in it needs clearing: every
+ * region is rewritten before it is read); two calls whose kernels overlap on the GPU -- from
+ * two streams or two threads -- race on it, so serialise them.  Errors of this entry point
+ * are reported by moe_route_static_error(). */
+int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, int index_base,
+                     const void* x, int x_dtype, int64_t T, int input_dim,
+                     const float* router_w, const float* logit_bias,
+                     float balance_alpha, float z_loss_weight, int training,
+                     int32_t* indices, float* gates, float* probs, float* loss, void* cuda_stream);
+int64_t moe_route_static_scratch_bytes(void);
+const char* moe_route_static_error(void);
+
 const char* moe_last_error(void);     /* thread-local message of the last failure */
 const char* moe_version(void);
 

@@ -24,7 +24,8 @@ EXPORTS = [
     "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_loss",
     "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_launch_count",
     "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_ep_layout", "moe_layer_destroy",
-    "moe_last_error", "moe_version",
+    "moe_last_error", "moe_version", "moe_route_static", "moe_route_static_scratch_bytes",
+    "moe_route_static_error",
 ]
 
 
@@ -78,6 +79,9 @@ def _load():
     lib.moe_ep_layout.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     lib.moe_ep_layout.restype = C.c_int64
     lib.moe_layer_destroy.argtypes = [vp]
+    lib.moe_route_static.argtypes = [i32, i32, i32, i32, i32, vp, i32, i64, i32, vp, vp, f32, f32, i32, vp, vp, vp, vp, vp]
+    lib.moe_route_static_scratch_bytes.restype = C.c_int64
+    lib.moe_route_static_error.restype = C.c_char_p
     lib.moe_last_error.restype = C.c_char_p
     lib.moe_version.restype = C.c_char_p
     for name in EXPORTS:
