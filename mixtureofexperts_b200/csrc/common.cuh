@@ -23,7 +23,7 @@ enum : int32_t {
 
 constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
-constexpr int ROUTER_KC = 128;          // K chunk: one float4 per lane
+constexpr int ROUTER_TOKENS_PER_CTA = 64;
 constexpr int MAX_ROUTER_EXPERTS = 128; // upper bound on router rows
 constexpr int MAX_EXPERTS = 256;        // upper bound on experts per layer
 constexpr int MAX_KTOT = 16;            // upper bound on selected experts per token
@@ -35,6 +35,7 @@ constexpr int F32_TILE_M = 16;   // FP32 SIMT path
 struct RouterParams {
     const void* x;            // [T][D]
     const float* w;           // [E_router][D]
+    const float* wt;          // [D_pad][E_pad] K-major zero-padded copy (launch_router_transpose)
     const float* bias;        // [E_router] or null
     int64_t T;
     int D;
@@ -47,7 +48,7 @@ struct RouterParams {
     int shared_mode;
     int bias_gates_only;
     int index_base;
-    int tokens_per_cta;       // 8 warps * tokens per warp pass
+    int tokens_per_cta;       // ROUTER_TOKENS_PER_CTA
     int want_entropy;
     // internal results
     int32_t* idx;             // [T][k_tot] layer expert id, 0-based
@@ -125,6 +126,9 @@ struct GroupGemmParams {
 // ---- launchers (each returns the number of kernels it launched, or <0 on a launch error) ---
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s);
 int router_tokens_per_cta(int e_router);
+int router_e_pad(int e_router);          // router rows padded to 8, 16, 32, 64 or 128
+int router_d_pad(int D);                 // K rows of the K-major copy (multiple of 128)
+int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_t s);
 int launch_scan(const ScanParams& p, cudaStream_t s);
 int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s);
 int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s);

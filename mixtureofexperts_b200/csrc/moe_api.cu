@@ -65,6 +65,7 @@ struct moe_layer {
     void* w3 = nullptr;
     void* w2 = nullptr;
     float* router_w = nullptr;   // [E_router][D]
+    float* router_wt = nullptr;  // [D_pad][E_pad] K-major zero-padded copy read by the router kernel
     float* router_bias = nullptr;
     bool has_bias = false, router_set = false;
     std::vector<char> expert_set;
@@ -298,6 +299,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     RouterParams r;
     r.x = x;
     r.w = L->router_w;
+    r.wt = L->router_wt;
     r.bias = L->has_bias ? L->router_bias : nullptr;
     r.T = T;
     r.D = c.input_dim;
@@ -476,6 +478,7 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
         return code;
     };
     if ((rc = dev_alloc(&L->router_w, (size_t)L->E_router * cfg->input_dim))) return cleanup(rc);
+    if ((rc = dev_alloc(&L->router_wt, (size_t)router_e_pad(L->E_router) * router_d_pad(cfg->input_dim)))) return cleanup(rc);
     if ((rc = dev_alloc(&L->router_bias, (size_t)L->E_router))) return cleanup(rc);
     if ((rc = dev_alloc(&L->expert_count, (size_t)L->E))) return cleanup(rc);
     if ((rc = dev_alloc(&L->expert_offset, (size_t)L->E + 1))) return cleanup(rc);
@@ -500,6 +503,7 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->w2);
     dev_free(L->router_w);
     dev_free(L->router_bias);
+    dev_free(L->router_wt);
     dev_free(L->stage_w);
     dev_free(L->expert_count);
     dev_free(L->expert_offset);
@@ -580,6 +584,9 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
                                            L->cfg.input_dim, layout == MOE_LAYOUT_OUT_CONTIG, L->stream);
     if (n < 0) return fail(MOE_ERR_CUDA, "router repack launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
+    const int n2 = launch_router_transpose(L->router_w, L->router_wt, L->E_router, L->cfg.input_dim, L->stream);
+    if (n2 < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n2;
     if (logit_bias) {
         CUDA_TRY(cudaMemcpyAsync(L->router_bias, logit_bias, sizeof(float) * L->E_router,
                                  src_is_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, L->stream));

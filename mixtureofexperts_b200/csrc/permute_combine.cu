@@ -36,7 +36,19 @@ template <typename T>
 __device__ __forceinline__ void copy_row_same(const T* src, T* const* dst, int ndst, int D, int lane, bool vec) {
     constexpr int N = 16 / sizeof(T);
     if (vec) {
-        for (int c = lane * N; c < D; c += 32 * N) {
+        // four 16-byte loads in flight per lane before the first store
+        int c = lane * N;
+        for (; c + 3 * 32 * N < D; c += 4 * 32 * N) {
+            const uint4 v0 = ld16(src + c), v1 = ld16(src + c + 32 * N), v2 = ld16(src + c + 2 * 32 * N),
+                        v3 = ld16(src + c + 3 * 32 * N);
+            for (int j = 0; j < ndst; ++j) {
+                st16(dst[j] + c, v0);
+                st16(dst[j] + c + 32 * N, v1);
+                st16(dst[j] + c + 2 * 32 * N, v2);
+                st16(dst[j] + c + 3 * 32 * N, v3);
+            }
+        }
+        for (; c < D; c += 32 * N) {
             const uint4 v = ld16(src + c);
             for (int j = 0; j < ndst; ++j) st16(dst[j] + c, v);
         }

@@ -62,7 +62,8 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
     const size_t b_psum = align256((size_t)num_cta64 * (num_experts + 1) * sizeof(float));
     const size_t b_ent = align256((size_t)num_cta64 * sizeof(double));
     const size_t b_tab = align256((size_t)(num_experts + 1) * sizeof(int32_t));
-    const size_t need = b_counts + b_psum + b_ent + 3 * b_tab + 256;
+    const size_t b_wt = align256((size_t)router_e_pad(num_experts) * router_d_pad(input_dim) * sizeof(float));
+    const size_t need = b_counts + b_psum + b_ent + 3 * b_tab + 256 + b_wt;
     if (need > SCRATCH_BYTES) {
         snprintf(g_static_err, sizeof(g_static_err),
                  "T=%lld with %d experts needs %zu bytes of scratch; the static array holds %zu "
@@ -92,13 +93,22 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
     int32_t* expert_offset = reinterpret_cast<int32_t*>(base + b_counts + b_psum + b_ent + b_tab);
     int32_t* tile_prefix = reinterpret_cast<int32_t*>(base + b_counts + b_psum + b_ent + 2 * b_tab);
     float* loss_internal = reinterpret_cast<float*>(base + b_counts + b_psum + b_ent + 3 * b_tab);
-    // Nothing here has to start at zero: the router kernel writes every per-CTA row before the
-    // scan kernel reads it, and the scan kernel writes the tables and the loss it produces.
+    float* wt = reinterpret_cast<float*>(base + b_counts + b_psum + b_ent + 3 * b_tab + 256);
+    // Nothing here has to start at zero: the transpose kernel writes the whole padded matrix,
+    // the router kernel writes every per-CTA row before the scan kernel reads it, and the scan
+    // kernel writes the tables and the loss it produces.
 
     cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+    // the router kernel reads a K-major, zero-padded copy of the router matrix: build it in the array
+    if (launch_router_transpose(router_w, wt, num_experts, input_dim, s) < 0) {
+        snprintf(g_static_err, sizeof(g_static_err), "router transpose launch failed: %s",
+                 cudaGetErrorString(cudaGetLastError()));
+        return MOE_ERR_CUDA;
+    }
     RouterParams r;
     r.x = x;
     r.w = router_w;
+    r.wt = wt;
     r.bias = logit_bias;
     r.T = T;
     r.D = input_dim;

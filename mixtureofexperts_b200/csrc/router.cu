@@ -1,4 +1,4 @@
-// Fused router: gate GEMM (FP32, lane-split K for a short rounding chain) -> softmax -> top-k
+// Fused router: gate GEMM (FP32 FMA, split-K + two-level summation for a short rounding chain) -> softmax -> top-k
 // (k arg-max passes, ties to the lowest index) -> renormalised gates -> per-CTA expert
 // histogram and per-CTA partial sums for the Switch loss, the z-loss and the routing entropy.
 //
@@ -206,37 +206,6 @@ __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const fl
     if (c.want_entropy) ent_acc += warp_sum_d(ent);
 }
 
-template <typename XT>
-__device__ __forceinline__ float4 load_x4(const XT* row, int kk, int D, bool vec);
-
-template <>
-__device__ __forceinline__ float4 load_x4<float>(const float* row, int kk, int D, bool vec) {
-    if (vec && kk + 3 < D) return *reinterpret_cast<const float4*>(row + kk);
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (kk + 0 < D) v.x = row[kk + 0];
-    if (kk + 1 < D) v.y = row[kk + 1];
-    if (kk + 2 < D) v.z = row[kk + 2];
-    if (kk + 3 < D) v.w = row[kk + 3];
-    return v;
-}
-template <>
-__device__ __forceinline__ float4 load_x4<__nv_bfloat16>(const __nv_bfloat16* row, int kk, int D, bool vec) {
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (vec && kk + 3 < D) {
-        const uint2 u = *reinterpret_cast<const uint2*>(row + kk);
-        v.x = __uint_as_float(u.x << 16);
-        v.y = __uint_as_float(u.x & 0xffff0000u);
-        v.z = __uint_as_float(u.y << 16);
-        v.w = __uint_as_float(u.y & 0xffff0000u);
-        return v;
-    }
-    if (kk + 0 < D) v.x = __bfloat162float(row[kk + 0]);
-    if (kk + 1 < D) v.y = __bfloat162float(row[kk + 1]);
-    if (kk + 2 < D) v.z = __bfloat162float(row[kk + 2]);
-    if (kk + 3 < D) v.w = __bfloat162float(row[kk + 3]);
-    return v;
-}
-
 __device__ __forceinline__ GateCtx make_ctx(const RouterParams& p) {
     GateCtx c;
     c.E_router = p.E_router;
@@ -261,103 +230,227 @@ __device__ __forceinline__ GateCtx make_ctx(const RouterParams& p) {
     return c;
 }
 
-// E_MAX: compile-time bound on router rows; TP: tokens a warp carries through the K loop.
-template <int E_MAX, int TP, typename XT>
-__global__ void __launch_bounds__(ROUTER_THREADS) router_kernel(const RouterParams p) {
-    extern __shared__ float4 s_w[];  // [E_router][KC/4]
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// 16-byte async copy that reads only `src_bytes` (0..16) and zero-fills the rest.
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gmem_src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gmem_src), "r"(src_bytes)
+                 : "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int RT_BT = ROUTER_TOKENS_PER_CTA;  // 64 tokens per CTA
+constexpr int RT_STAGES = 3;
+
+template <typename XT> struct XElt;
+template <> struct XElt<float> { static constexpr int PER16 = 4; };
+template <> struct XElt<__nv_bfloat16> { static constexpr int PER16 = 8; };
+
+// One pipeline stage: a [64 tokens][BK (+16 bytes pad)] tile of x in its own dtype and the
+// [BK][E_PAD] block of the K-major router matrix.
+template <int E_PAD, int BK, typename XT>
+struct RouterStage {
+    static constexpr int ROW_ELTS = BK + XElt<XT>::PER16;   // padded row, stays 16-byte aligned
+    XT x[RT_BT][ROW_ELTS];
+    float w[BK][E_PAD];
+};
+
+template <int E_PAD, int BK, typename XT>
+union RouterSmem {
+    RouterStage<E_PAD, BK, XT> st[RT_STAGES];
+    float red[(ROUTER_THREADS / (16 * (E_PAD / 8))) * RT_BT * E_PAD];  // [KS][64][E_PAD] = 8192 floats
+};
+
+// Gate GEMM as a register-tiled FP32 FMA kernel: a CTA owns 64 tokens x E_PAD router rows; a
+// thread owns 4 tokens x 8 rows and 1/KS of every K chunk, KS = 256/(16*E_PAD/8), so the
+// per-thread FP32 chain stays short; an inner accumulator is folded into an outer one every
+// ~256 products (two-level summation) and the KS partials are added in a fixed order.  x (in
+// its own dtype) and the K-major router matrix ([K][E_PAD], built once per set_router) stream
+// through a 3-stage cp.async ring; every token row contributes BK contiguous elements per chunk.
+template <int E_PAD, int BK, typename XT>
+__global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterParams p) {
+    constexpr int EG = E_PAD / 8;
+    constexpr int TG = 16;
+    constexpr int KS = ROUTER_THREADS / (TG * EG);
+    constexpr int KPT = BK / KS;
+    constexpr int FOLD = (256 / KPT) > 0 ? (256 / KPT) : 1;
+    constexpr int PER16 = XElt<XT>::PER16;
+    constexpr int UPR = BK / PER16;                    // 16-byte units per token row per chunk
+    constexpr int XUNITS = RT_BT * UPR;
+    using Stage = RouterStage<E_PAD, BK, XT>;
+    static_assert(KPT >= 2 && KPT % 2 == 0, "tile configuration");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    RouterSmem<E_PAD, BK, XT>& sm = *reinterpret_cast<RouterSmem<E_PAD, BK, XT>*>(smem_raw);
     __shared__ int s_cnt[MAX_EXPERTS];
     __shared__ float s_psum[ROUTER_WARPS][MAX_EXPERTS];
     __shared__ float s_lse2[ROUTER_WARPS];
     __shared__ double s_ent[ROUTER_WARPS];
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < MAX_EXPERTS; i += ROUTER_THREADS) s_cnt[i] = 0;
-    for (int i = threadIdx.x; i < ROUTER_WARPS * MAX_EXPERTS; i += ROUTER_THREADS) (&s_psum[0][0])[i] = 0.f;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int eg = tid % EG, tg = (tid / EG) % TG, ks = tid / (EG * TG);
+    for (int i = tid; i < MAX_EXPERTS; i += ROUTER_THREADS) s_cnt[i] = 0;
+    for (int i = tid; i < ROUTER_WARPS * MAX_EXPERTS; i += ROUTER_THREADS) (&s_psum[0][0])[i] = 0.f;
 
-    const int64_t tok0 = (int64_t)blockIdx.x * p.tokens_per_cta + (int64_t)warp * TP;
+    const int64_t tok0 = (int64_t)blockIdx.x * RT_BT;
     const XT* x = reinterpret_cast<const XT*>(p.x);
-    const bool vec_x = (p.D % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
-    const bool vec_w = (p.D % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.w) & 15) == 0);
+    const bool vec_x = (p.D % PER16 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15) == 0);
+    const int nchunks = (p.D + BK - 1) / BK;
 
-    float acc[TP][E_MAX];
-#pragma unroll
-    for (int a = 0; a < TP; ++a)
-#pragma unroll
-        for (int e = 0; e < E_MAX; ++e) acc[a][e] = 0.f;
-
-    for (int kc = 0; kc < p.D; kc += ROUTER_KC) {
-        __syncthreads();
-        for (int i = threadIdx.x; i < p.E_router * (ROUTER_KC / 4); i += ROUTER_THREADS) {
-            const int e = i / (ROUTER_KC / 4), c4 = i % (ROUTER_KC / 4);
-            s_w[i] = load_x4<float>(p.w + (size_t)e * p.D, kc + c4 * 4, p.D, vec_w);
-        }
-        __syncthreads();
-        float4 xv[TP];
-#pragma unroll
-        for (int a = 0; a < TP; ++a) {
-            const int64_t t = tok0 + a;
-            xv[a] = (t < p.T) ? load_x4<XT>(x + (size_t)t * p.D, kc + lane * 4, p.D, vec_x)
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int e = 0; e < E_MAX; ++e) {
-            if (e < p.E_router) {
-                const float4 wv = s_w[e * (ROUTER_KC / 4) + lane];
-#pragma unroll
-                for (int a = 0; a < TP; ++a) {
-                    float s = acc[a][e];
-                    s = fmaf(xv[a].x, wv.x, s);
-                    s = fmaf(xv[a].y, wv.y, s);
-                    s = fmaf(xv[a].z, wv.z, s);
-                    s = fmaf(xv[a].w, wv.w, s);
-                    acc[a][e] = s;
+    auto issue_chunk = [&](int c) {
+        if (c < nchunks) {
+            Stage& st = sm.st[c % RT_STAGES];
+            const int kbase = c * BK;
+            if (vec_x) {
+                for (int u = tid; u < XUNITS; u += ROUTER_THREADS) {
+                    const int tok = u / UPR, q = u % UPR;
+                    const int64_t t = tok0 + tok;
+                    const int k0 = kbase + q * PER16;
+                    int bytes = (t < p.T && k0 < p.D) ? 16 : 0;   // D % PER16 == 0: a unit is all in or all out
+                    const XT* src = bytes ? x + (size_t)t * p.D + k0 : x;
+                    cp_async16_zfill(&st.x[tok][q * PER16], src, bytes);
+                }
+            } else {
+                for (int i = tid; i < RT_BT * BK; i += ROUTER_THREADS) {
+                    const int tok = i / BK, kk = i % BK;
+                    const int64_t t = tok0 + tok;
+                    XT v = XT(0.f);
+                    if (t < p.T && kbase + kk < p.D) v = x[(size_t)t * p.D + kbase + kk];
+                    st.x[tok][kk] = v;
                 }
             }
+            // rows [kbase, kbase+BK) of the K-major router matrix: one contiguous block (rows past D are zero)
+            const float* src = p.wt + (size_t)kbase * E_PAD;
+            float* dst = &st.w[0][0];
+            for (int u = tid; u < BK * E_PAD / 4; u += ROUTER_THREADS) cp_async16(dst + u * 4, src + u * 4);
         }
-    }
-    // butterfly all-reduce: every lane ends with the same full dot products
+        cp_async_commit();   // always commit, so that group counting stays uniform
+    };
+
+    float acc[4][8], outer[4][8];
 #pragma unroll
-    for (int a = 0; a < TP; ++a)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int e = 0; e < E_MAX; ++e) {
-            if (e < p.E_router) {
-                float v = acc[a][e];
-#pragma unroll
-                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                acc[a][e] = v;
-            }
+        for (int j = 0; j < 8; ++j) {
+            acc[i][j] = 0.f;
+            outer[i][j] = 0.f;
         }
 
+#pragma unroll
+    for (int s = 0; s < RT_STAGES - 1; ++s) issue_chunk(s);
+    for (int c = 0; c < nchunks; ++c) {
+        cp_async_wait<RT_STAGES - 2>();   // chunk c has landed (this thread's copies)
+        __syncthreads();                  // ... and everybody's; everybody is also done with chunk c-1
+        issue_chunk(c + RT_STAGES - 1);
+        const Stage& st = sm.st[c % RT_STAGES];
+#pragma unroll
+        for (int kk = 0; kk < KPT; kk += 2) {
+            const int k = ks * KPT + kk;
+            float x0[4], x1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if constexpr (sizeof(XT) == 2) {
+                    const uint32_t w2 = *reinterpret_cast<const uint32_t*>(&st.x[i * 16 + tg][k]);
+                    x0[i] = __uint_as_float(w2 << 16);
+                    x1[i] = __uint_as_float(w2 & 0xffff0000u);
+                } else {
+                    const float2 w2 = *reinterpret_cast<const float2*>(&st.x[i * 16 + tg][k]);
+                    x0[i] = w2.x;
+                    x1[i] = w2.y;
+                }
+            }
+            const float4 a0 = *reinterpret_cast<const float4*>(&st.w[k][eg * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&st.w[k][E_PAD / 2 + eg * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&st.w[k + 1][eg * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&st.w[k + 1][E_PAD / 2 + eg * 4]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[i][0] = fmaf(x0[i], a0.x, acc[i][0]);
+                acc[i][1] = fmaf(x0[i], a0.y, acc[i][1]);
+                acc[i][2] = fmaf(x0[i], a0.z, acc[i][2]);
+                acc[i][3] = fmaf(x0[i], a0.w, acc[i][3]);
+                acc[i][4] = fmaf(x0[i], a1.x, acc[i][4]);
+                acc[i][5] = fmaf(x0[i], a1.y, acc[i][5]);
+                acc[i][6] = fmaf(x0[i], a1.z, acc[i][6]);
+                acc[i][7] = fmaf(x0[i], a1.w, acc[i][7]);
+                acc[i][0] = fmaf(x1[i], b0.x, acc[i][0]);
+                acc[i][1] = fmaf(x1[i], b0.y, acc[i][1]);
+                acc[i][2] = fmaf(x1[i], b0.z, acc[i][2]);
+                acc[i][3] = fmaf(x1[i], b0.w, acc[i][3]);
+                acc[i][4] = fmaf(x1[i], b1.x, acc[i][4]);
+                acc[i][5] = fmaf(x1[i], b1.y, acc[i][5]);
+                acc[i][6] = fmaf(x1[i], b1.z, acc[i][6]);
+                acc[i][7] = fmaf(x1[i], b1.w, acc[i][7]);
+            }
+        }
+        if ((c % FOLD) == FOLD - 1) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    outer[i][j] += acc[i][j];
+                    acc[i][j] = 0.f;
+                }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();   // the ring is dead from here on; its memory becomes the reduction buffer
+    // partial sums of this thread's K slices -> shared [ks][token][row]
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int tok = i * 16 + tg;
+        float* dst = &sm.red[((size_t)ks * RT_BT + tok) * E_PAD];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            dst[eg * 4 + j] = outer[i][j] + acc[i][j];
+            dst[E_PAD / 2 + eg * 4 + j] = outer[i][4 + j] + acc[i][4 + j];
+        }
+    }
+    __syncthreads();
+
     const GateCtx c = make_ctx(p);
-    constexpr int NJ = (E_MAX + 31) / 32;
+    constexpr int NJ = (E_PAD + 31) / 32;
     float lse2 = 0.f;
     double ent = 0.0;
+    for (int a = 0; a < RT_BT / ROUTER_WARPS; ++a) {
+        const int tok = warp * (RT_BT / ROUTER_WARPS) + a;
+        const int64_t t = tok0 + tok;
+        if (t >= p.T) break;
+        float lg[NJ];
 #pragma unroll
-    for (int a = 0; a < TP; ++a) {
-        const int64_t t = tok0 + a;
-        if (t < p.T) {
-            float lg[NJ];
+        for (int j = 0; j < NJ; ++j) {
+            const int e = lane + 32 * j;
+            float s = 0.f;
+            if (e < E_PAD) {
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) lg[j] = 0.f;
-#pragma unroll
-            for (int e = 0; e < E_MAX; ++e)
-                if ((e & 31) == lane) lg[e >> 5] = acc[a][e];
-            gate_token<NJ>(c, t, lg, lane, s_cnt, s_psum[warp], lse2, ent);
+                for (int q = 0; q < KS; ++q) s += sm.red[((size_t)q * RT_BT + tok) * E_PAD + e];
+            }
+            lg[j] = s;
         }
+        gate_token<NJ>(c, t, lg, lane, s_cnt, s_psum[warp], lse2, ent);
     }
     if (lane == 0) {
         s_lse2[warp] = lse2;
         s_ent[warp] = ent;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < p.E; e += ROUTER_THREADS) p.cta_counts[(size_t)blockIdx.x * p.E + e] = s_cnt[e];
-    for (int e = threadIdx.x; e < p.E_probs; e += ROUTER_THREADS) {
+    for (int e = tid; e < p.E; e += ROUTER_THREADS) p.cta_counts[(size_t)blockIdx.x * p.E + e] = s_cnt[e];
+    for (int e = tid; e < p.E_probs; e += ROUTER_THREADS) {
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < ROUTER_WARPS; ++w) s += s_psum[w][e];
         p.cta_psum[(size_t)blockIdx.x * (p.E_probs + 1) + e] = s;
     }
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         float s = 0.f;
         double d = 0.0;
         for (int w = 0; w < ROUTER_WARPS; ++w) {
@@ -366,6 +459,15 @@ __global__ void __launch_bounds__(ROUTER_THREADS) router_kernel(const RouterPara
         }
         p.cta_psum[(size_t)blockIdx.x * (p.E_probs + 1) + p.E_probs] = s;
         p.cta_entropy[blockIdx.x] = d;
+    }
+}
+
+// wt[k][e] = w[e][k] for k < D, e < E; zero elsewhere (k < D_pad, e < E_pad)
+__global__ void router_transpose_kernel(const float* w, float* wt, int E, int D, int E_pad, int D_pad) {
+    const size_t n = (size_t)E_pad * D_pad;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int k = (int)(i / E_pad), e = (int)(i % E_pad);
+        wt[i] = (k < D && e < E) ? w[(size_t)e * D + k] : 0.f;
     }
 }
 
@@ -388,47 +490,54 @@ __global__ void __launch_bounds__(ROUTER_THREADS) gates_only_kernel(GateCtx c, c
     gate_token<NJ>(c, t, lg, lane, s_cnt, s_psum[warp], lse2, ent);
 }
 
-template <int E_MAX, int TP>
-int launch_router_t(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s) {
-    const size_t smem = (size_t)p.E_router * ROUTER_KC * sizeof(float);
-    cudaError_t err;
-    if (x_dtype == MOE_DTYPE_F32) {
-        auto kern = router_kernel<E_MAX, TP, float>;
-        if (smem > 32 * 1024) {
-            err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (err != cudaSuccess) return -1;
-        }
-        kern<<<num_cta, ROUTER_THREADS, smem, s>>>(p);
-    } else {
-        auto kern = router_kernel<E_MAX, TP, __nv_bfloat16>;
-        if (smem > 32 * 1024) {
-            err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (err != cudaSuccess) return -1;
-        }
-        kern<<<num_cta, ROUTER_THREADS, smem, s>>>(p);
+template <int E_PAD, int BK, typename XT>
+int launch_router_t(const RouterParams& p, int num_cta, cudaStream_t s) {
+    auto kern = router_kernel<E_PAD, BK, XT>;
+    const size_t smem = sizeof(RouterSmem<E_PAD, BK, XT>);
+    static bool attr_done = false;   // per instantiation
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
+        attr_done = true;
     }
+    kern<<<num_cta, ROUTER_THREADS, smem, s>>>(p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
-int tokens_per_pass(int e_router) {
-    if (e_router <= 16) return 8;
-    if (e_router <= 32) return 4;
-    if (e_router <= 72) return 2;
-    return 1;
+template <int E_PAD, int BK>
+int launch_router_e(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s) {
+    if (x_dtype == MOE_DTYPE_F32) return launch_router_t<E_PAD, BK, float>(p, num_cta, s);
+    return launch_router_t<E_PAD, BK, __nv_bfloat16>(p, num_cta, s);
 }
 
 }  // namespace
 
-int router_tokens_per_cta(int e_router) { return ROUTER_WARPS * tokens_per_pass(e_router); }
+int router_tokens_per_cta(int) { return ROUTER_TOKENS_PER_CTA; }
+
+int router_e_pad(int e_router) {
+    int e = 8;
+    while (e < e_router) e <<= 1;
+    return e;
+}
+
+int router_d_pad(int D) { return (D + 127) / 128 * 128; }
+
+int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_t s) {
+    const int e_pad = router_e_pad(E), d_pad = router_d_pad(D);
+    const size_t n = (size_t)e_pad * d_pad;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    router_transpose_kernel<<<blocks, 256, 0, s>>>(w, wt, E, D, e_pad, d_pad);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
 
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s) {
-    const int e = p.E_router;
-    if (e <= 8) return launch_router_t<8, 8>(p, x_dtype, num_cta, s);
-    if (e <= 16) return launch_router_t<16, 8>(p, x_dtype, num_cta, s);
-    if (e <= 32) return launch_router_t<32, 4>(p, x_dtype, num_cta, s);
-    if (e <= 64) return launch_router_t<64, 2>(p, x_dtype, num_cta, s);
-    if (e <= 72) return launch_router_t<72, 2>(p, x_dtype, num_cta, s);
-    return launch_router_t<128, 1>(p, x_dtype, num_cta, s);
+    switch (router_e_pad(p.E_router)) {
+        case 8: return launch_router_e<8, 128>(p, x_dtype, num_cta, s);
+        case 16: return launch_router_e<16, 128>(p, x_dtype, num_cta, s);
+        case 32: return launch_router_e<32, 128>(p, x_dtype, num_cta, s);
+        case 64: return launch_router_e<64, 64>(p, x_dtype, num_cta, s);
+        case 128: return launch_router_e<128, 32>(p, x_dtype, num_cta, s);
+        default: return -1;
+    }
 }
 
 int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const float* logits, int64_t T,
