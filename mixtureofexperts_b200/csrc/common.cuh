@@ -98,6 +98,9 @@ struct PermuteParams {
     int32_t* row_token;           // [P]
     int32_t* status;
     int64_t P_cap;
+    // expert-parallel peer mode (else null): expert_dst[e] is where this rank's rows for expert e
+    // start, possibly in another GPU's memory; row (pos - expert_offset[e]) of that segment is written
+    void* const* expert_dst;
 };
 
 struct CombineParams {
@@ -108,6 +111,10 @@ struct CombineParams {
     const int32_t* idx;
     const float* gate;
     const int32_t* pair_pos;
+    // expert-parallel peer mode (else null): outputs of expert e for this rank's rows start at
+    // expert_src[e] (possibly another GPU's memory); expert_offset is this rank's send layout
+    const void* const* expert_src;
+    const int32_t* expert_offset;
 };
 
 // Grouped GEMM over the permuted rows: C[r][n] = sum_k A[r][k] * B[e(r)][n][k].

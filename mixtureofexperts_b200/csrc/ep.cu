@@ -20,6 +20,7 @@
 #include <nccl.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -113,6 +114,14 @@ struct EpState {
     int64_t rows_cap = 0;
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     bool timed = false;
+    // peer-memory mode
+    bool peer_mode = true;
+    std::vector<void*> peer_xr, peer_yr;   // [world] mapped receive buffers (own entry = local pointer)
+    unsigned char* d_ipc = nullptr;        // [world][2 handles] staging for the handle all-gather
+    unsigned char* h_ipc = nullptr;        // pinned
+    void** d_ptrs = nullptr;               // [2E] expert_dst, expert_src
+    void** h_ptrs = nullptr;               // pinned
+    int32_t* d_flag = nullptr;             // barrier payload
 };
 
 // Pure host arithmetic (no CUDA, no NCCL): see ep.h.
@@ -170,6 +179,16 @@ int ep_create(EpState** out, const EpConfig& cfg, const void* id128, char* err, 
               cudaMalloc(&ep->d_tables, sizeof(int32_t) * 2 * (ep->per + 1)) == cudaSuccess &&
               cudaMallocHost(&ep->h_tables, sizeof(int32_t) * 2 * (ep->per + 1)) == cudaSuccess;
     for (auto& e : ep->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
+    const char* mode = getenv("MOE_B200_EP_MODE");
+    ep->peer_mode = !(mode && strcmp(mode, "nccl") == 0);
+    ep->peer_xr.assign(cfg.world, nullptr);
+    ep->peer_yr.assign(cfg.world, nullptr);
+    const size_t ipc_bytes = (size_t)cfg.world * 2 * sizeof(cudaIpcMemHandle_t);
+    ok = ok && cudaMalloc(&ep->d_ipc, ipc_bytes) == cudaSuccess && cudaMallocHost(&ep->h_ipc, ipc_bytes) == cudaSuccess &&
+         cudaMalloc(&ep->d_ptrs, sizeof(void*) * 2 * cfg.E) == cudaSuccess &&
+         cudaMallocHost(&ep->h_ptrs, sizeof(void*) * 2 * cfg.E) == cudaSuccess &&
+         cudaMalloc(&ep->d_flag, sizeof(int32_t)) == cudaSuccess &&
+         cudaMemset(ep->d_flag, 0, sizeof(int32_t)) == cudaSuccess;
     if (!ok) {
         ep_destroy(ep);
         return set_err(err, errlen, MOE_ERR_CUDA, "expert-parallel buffers: allocation failed");
@@ -186,9 +205,19 @@ void ep_destroy(EpState* ep) {
     if (ep->h_all_counts) cudaFreeHost(ep->h_all_counts);
     if (ep->d_tables) cudaFree(ep->d_tables);
     if (ep->h_tables) cudaFreeHost(ep->h_tables);
+    for (int r = 0; r < (int)ep->peer_xr.size(); ++r) {
+        if (r == ep->cfg.rank) continue;
+        if (ep->peer_xr[r]) cudaIpcCloseMemHandle(ep->peer_xr[r]);
+        if (ep->peer_yr[r]) cudaIpcCloseMemHandle(ep->peer_yr[r]);
+    }
     if (ep->xr) cudaFree(ep->xr);
     if (ep->hr) cudaFree(ep->hr);
     if (ep->yr) cudaFree(ep->yr);
+    if (ep->d_ipc) cudaFree(ep->d_ipc);
+    if (ep->h_ipc) cudaFreeHost(ep->h_ipc);
+    if (ep->d_ptrs) cudaFree(ep->d_ptrs);
+    if (ep->h_ptrs) cudaFreeHost(ep->h_ptrs);
+    if (ep->d_flag) cudaFree(ep->d_flag);
     for (auto& e : ep->ev)
         if (e) cudaEventDestroy(e);
     delete ep;
@@ -324,6 +353,142 @@ int ep_exchange_and_run(EpState* ep, const EpCall& c, EpRunFn run, void* self, i
     if (launches) *launches += 1;
     EP_CUDA(cudaEventRecord(ep->ev[3], s));
     ep->timed = true;
+    return MOE_OK;
+}
+
+// ---- peer-memory mode ------------------------------------------------------------------------
+
+bool ep_peer_mode(const EpState* ep) { return ep->peer_mode; }
+
+void ep_mark(EpState* ep, int i, cudaStream_t s) {
+    cudaEventRecord(ep->ev[i], s);
+    if (i == 3) ep->timed = true;
+}
+
+// Collective: every rank calls it with the same `cap` (derived from the all-gathered counts).
+// Order: drop the mappings of the peers' old buffers, allocate the new buffers, exchange their
+// IPC handles (which also tells us every rank has dropped its old mappings), free the old
+// buffers, map the peers' new ones.
+static int ep_grow_peer_buffers(EpState* ep, int64_t cap, cudaStream_t s, char* err, size_t errlen) {
+    const EpConfig& g = ep->cfg;
+    const int W = g.world, me = g.rank;
+    for (int r = 0; r < W; ++r) {
+        if (r != me) {
+            if (ep->peer_xr[r]) cudaIpcCloseMemHandle(ep->peer_xr[r]);
+            if (ep->peer_yr[r]) cudaIpcCloseMemHandle(ep->peer_yr[r]);
+        }
+        ep->peer_xr[r] = ep->peer_yr[r] = nullptr;
+    }
+    void *nxr = nullptr, *nhr = nullptr, *nyr = nullptr;
+    EP_CUDA(cudaMalloc(&nxr, (size_t)cap * g.D * g.elt));
+    EP_CUDA(cudaMalloc(&nhr, (size_t)cap * g.H * g.elt));
+    EP_CUDA(cudaMalloc(&nyr, (size_t)cap * g.O * g.elt));
+    cudaIpcMemHandle_t mine[2];
+    EP_CUDA(cudaIpcGetMemHandle(&mine[0], nxr));
+    EP_CUDA(cudaIpcGetMemHandle(&mine[1], nyr));
+    const size_t hb = 2 * sizeof(cudaIpcMemHandle_t);
+    EP_CUDA(cudaMemcpyAsync(ep->d_ipc + (size_t)me * hb, mine, hb, cudaMemcpyHostToDevice, s));
+    EP_NCCL(g_nccl.AllGather(ep->d_ipc + (size_t)me * hb, ep->d_ipc, hb, ncclChar, ep->comm, s));
+    EP_CUDA(cudaMemcpyAsync(ep->h_ipc, ep->d_ipc, hb * W, cudaMemcpyDeviceToHost, s));
+    EP_CUDA(cudaStreamSynchronize(s));
+    if (ep->xr) cudaFree(ep->xr);
+    if (ep->hr) cudaFree(ep->hr);
+    if (ep->yr) cudaFree(ep->yr);
+    ep->xr = nxr;
+    ep->hr = nhr;
+    ep->yr = nyr;
+    ep->rows_cap = cap;
+    for (int r = 0; r < W; ++r) {
+        if (r == me) {
+            ep->peer_xr[r] = nxr;
+            ep->peer_yr[r] = nyr;
+            continue;
+        }
+        cudaIpcMemHandle_t h[2];
+        memcpy(h, ep->h_ipc + (size_t)r * hb, hb);
+        EP_CUDA(cudaIpcOpenMemHandle(&ep->peer_xr[r], h[0], cudaIpcMemLazyEnablePeerAccess));
+        EP_CUDA(cudaIpcOpenMemHandle(&ep->peer_yr[r], h[1], cudaIpcMemLazyEnablePeerAccess));
+    }
+    return MOE_OK;
+}
+
+int ep_prepare(EpState* ep, const int32_t* d_expert_count, cudaStream_t s, EpPlan* plan, char* err, size_t errlen) {
+    const EpConfig& g = ep->cfg;
+    const int W = g.world, me = g.rank, per = ep->per, E = g.E;
+    EP_NCCL(g_nccl.AllGather(d_expert_count, ep->d_all_counts, (size_t)E, ncclInt32, ep->comm, s));
+    EP_CUDA(cudaMemcpyAsync(ep->h_all_counts, ep->d_all_counts, sizeof(int32_t) * W * E, cudaMemcpyDeviceToHost, s));
+    EP_CUDA(cudaStreamSynchronize(s));
+    const int32_t* cnt = ep->h_all_counts;  // cnt[r*E + e]
+
+    // rows every rank receives: the capacity decision must be the same on all ranks
+    int64_t need = 0;
+    std::vector<int64_t> expert_rows((size_t)E, 0);   // rows of expert e over all sources
+    for (int e = 0; e < E; ++e)
+        for (int r = 0; r < W; ++r) expert_rows[e] += cnt[(size_t)r * E + e];
+    for (int r = 0; r < W; ++r) {
+        int64_t rows_r = 0;
+        for (int el = 0; el < per; ++el) rows_r += expert_rows[(size_t)r * per + el];
+        if (rows_r > need) need = rows_r;
+    }
+    if (need > 0x7fffffffLL) return set_err(err, errlen, MOE_ERR_UNSUPPORTED, "more than 2^31-1 received rows");
+    if (need > ep->rows_cap || !ep->xr) {
+        const int rc = ep_grow_peer_buffers(ep, need + need / 4 + g.tile_m, s, err, errlen);
+        if (rc) return rc;
+    }
+
+    // my receive layout (for the grouped GEMM)
+    std::vector<int64_t> send_off((size_t)E + 1, 0), recv_off((size_t)per * W, 0);
+    int32_t* h_off = ep->h_tables;
+    int32_t* h_tp = ep->h_tables + (per + 1);
+    const int64_t rows = ep_plan_layout(cnt, W, E, me, g.tile_m, send_off.data(), recv_off.data(), h_off, h_tp);
+    EP_CUDA(cudaMemcpyAsync(ep->d_tables, ep->h_tables, sizeof(int32_t) * 2 * (per + 1), cudaMemcpyHostToDevice, s));
+
+    // where my rows for expert e start inside its owner's buffers:
+    //   (rows of the owner's earlier local experts) + (rows of expert e from lower ranks)
+    for (int r = 0; r < W; ++r) {
+        int64_t base = 0;
+        for (int el = 0; el < per; ++el) {
+            const int e = r * per + el;
+            int64_t before_me = 0;
+            for (int q = 0; q < me; ++q) before_me += cnt[(size_t)q * E + e];
+            const int64_t row = base + before_me;
+            ep->h_ptrs[e] = reinterpret_cast<char*>(ep->peer_xr[r]) + (size_t)row * g.D * g.elt;
+            ep->h_ptrs[E + e] = reinterpret_cast<char*>(ep->peer_yr[r]) + (size_t)row * g.O * g.elt;
+            base += expert_rows[e];
+        }
+    }
+    EP_CUDA(cudaMemcpyAsync(ep->d_ptrs, ep->h_ptrs, sizeof(void*) * 2 * E, cudaMemcpyHostToDevice, s));
+
+    plan->rows = rows;
+    plan->rows_cap = ep->rows_cap;
+    plan->xr = ep->xr;
+    plan->hr = ep->hr;
+    plan->yr = ep->yr;
+    plan->d_local_off = ep->d_tables;
+    plan->d_tile_prefix = ep->d_tables + (per + 1);
+    plan->d_expert_dst = ep->d_ptrs;
+    plan->d_expert_src = const_cast<const void* const*>(ep->d_ptrs + E);
+    return MOE_OK;
+}
+
+int ep_sums_barrier(EpState* ep, cudaStream_t s, char* err, size_t errlen) {
+    const EpConfig& g = ep->cfg;
+    EP_NCCL(g_nccl.AllReduce(ep->d_sums, ep->d_sums, (size_t)(g.E + g.E_probs + 3), ncclFloat32, ncclSum, ep->comm, s));
+    return MOE_OK;
+}
+
+int ep_barrier(EpState* ep, cudaStream_t s, char* err, size_t errlen) {
+    EP_NCCL(g_nccl.AllReduce(ep->d_flag, ep->d_flag, 1, ncclInt32, ncclMax, ep->comm, s));
+    return MOE_OK;
+}
+
+int ep_finish_loss(EpState* ep, int training, float* u_loss, float* u_entropy, cudaStream_t s, int64_t* launches,
+                   char* err, size_t errlen) {
+    const EpConfig& g = ep->cfg;
+    ep_finish_loss_kernel<<<1, 32, 0, s>>>(ep->d_sums, g.E, g.E_probs, g.k_tot, g.alpha, g.z_weight, training, u_loss,
+                                           u_entropy);
+    if (cudaGetLastError() != cudaSuccess) return set_err(err, errlen, MOE_ERR_CUDA, "loss kernel launch failed");
+    if (launches) *launches += 1;
     return MOE_OK;
 }
 

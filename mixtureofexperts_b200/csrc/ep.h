@@ -49,4 +49,32 @@ int ep_exchange_and_run(EpState*, const EpCall&, EpRunFn run, void* self, int64_
                         size_t errlen);
 float ep_last_exchange_ms(EpState*);
 
+// ---- peer-memory mode (default): rows cross NVLink inside the permute and combine kernels ----
+// Every rank exports its receive buffers with CUDA IPC; the permute kernel stores each row
+// straight into the owner GPU's buffer and the combine kernel loads expert outputs from the
+// owner's buffer.  NCCL only carries the small control collectives (counts, the loss sums that
+// double as a barrier, one more barrier).  MOE_B200_EP_MODE=nccl selects the send/recv path above.
+struct EpPlan {
+    int64_t rows;                     // rows this rank received
+    int64_t rows_cap;                 // capacity (rows) of the receive buffers
+    void* xr;                         // [rows_cap][D] received rows (this GPU's memory)
+    void* hr;                         // [rows_cap][H]
+    void* yr;                         // [rows_cap][O] expert outputs, read by the owners of the tokens
+    const int32_t* d_local_off;       // [per+1] received rows grouped by local expert
+    const int32_t* d_tile_prefix;     // [per+1]
+    void* const* d_expert_dst;        // [E] where this rank's rows for expert e start (a peer's xr)
+    const void* const* d_expert_src;  // [E] where their outputs start (a peer's yr)
+};
+bool ep_peer_mode(const EpState*);
+// all-gather of the counts, host sync, layout, (collective) buffer growth, pointer tables
+int ep_prepare(EpState*, const int32_t* d_expert_count, cudaStream_t s, EpPlan* plan, char* err, size_t errlen);
+// all-reduce of the loss sums; completes only when every rank has issued it, i.e. after every
+// rank's permute kernel: the barrier between dispatch and the expert GEMMs
+int ep_sums_barrier(EpState*, cudaStream_t s, char* err, size_t errlen);
+// barrier between the expert GEMMs and the combine kernels that read peers' outputs
+int ep_barrier(EpState*, cudaStream_t s, char* err, size_t errlen);
+int ep_finish_loss(EpState*, int training, float* u_loss, float* u_entropy, cudaStream_t s, int64_t* launches,
+                   char* err, size_t errlen);
+void ep_mark(EpState*, int i, cudaStream_t s);   // timing marks 0..3 around the two exchanges
+
 }  // namespace moe

@@ -92,6 +92,9 @@ struct moe_layer {
     int32_t* status = nullptr;
     TcGemmPlan* plan = nullptr;
     bool plan_dirty = true;
+    const void* plan_a1 = nullptr;   // what the tensor maps were last encoded for
+    const void* plan_a2 = nullptr;
+    int64_t plan_rows = 0;
 
     // host-call staging
     cudaStream_t stream = nullptr;
@@ -192,12 +195,16 @@ int ensure_workspace(moe_layer* L, int64_t T) {
     if ((rc = dev_alloc(&L->cta_counts, (size_t)num_cta * L->E))) return rc;
     if ((rc = dev_alloc(&L->cta_psum, (size_t)num_cta * (L->E_probs + 1)))) return rc;
     if ((rc = dev_alloc(&L->cta_entropy, (size_t)num_cta))) return rc;
-    CUDA_TRY(cudaMalloc(&L->xp, (size_t)P * L->cfg.input_dim * el));
+    const bool peer = L->ep && ep_peer_mode(L->ep);
+    if (!peer) {
+        // (in peer mode rows go straight into the owners' receive buffers and come back from them)
+        CUDA_TRY(cudaMalloc(&L->xp, (size_t)P * L->cfg.input_dim * el));
+        CUDA_TRY(cudaMalloc(&L->y, (size_t)P * L->cfg.output_dim * el));
+    }
     if (!L->ep) {
         // with expert parallelism the GEMMs run on the receive buffers owned by the EP state
         CUDA_TRY(cudaMalloc(&L->h, (size_t)P * L->cfg.hidden_dim * el));
     }
-    CUDA_TRY(cudaMalloc(&L->y, (size_t)P * L->cfg.output_dim * el));
     L->T_cap = T;
     L->P_cap = P;
     L->plan_dirty = true;
@@ -207,11 +214,15 @@ int ensure_workspace(moe_layer* L, int64_t T) {
 int ensure_plan(moe_layer* L, const void* a1, const void* a2, int64_t rows) {
     if (L->cfg.compute_dtype != MOE_DTYPE_BF16) return MOE_OK;
     if (!L->plan) L->plan = tc_plan_create();
+    if (!L->plan_dirty && L->plan_a1 == a1 && L->plan_a2 == a2 && L->plan_rows == rows) return MOE_OK;
     const char* msg = "";
     const int rc = tc_plan_encode(L->plan, a1, a2, rows, L->cfg.input_dim, L->cfg.hidden_dim, L->cfg.output_dim,
                                   L->e_hi - L->e_lo, L->w1, L->w3, L->w2, &msg);
     if (rc != MOE_OK) return fail(rc, "%s", msg);
     L->plan_dirty = false;
+    L->plan_a1 = a1;
+    L->plan_a2 = a2;
+    L->plan_rows = rows;
     return MOE_OK;
 }
 
@@ -375,6 +386,14 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     pp.row_token = L->row_token;
     pp.status = L->status;
     pp.P_cap = L->P_cap;
+    pp.expert_dst = nullptr;
+    const bool peer = L->ep && ep_peer_mode(L->ep);
+    EpPlan plan;
+    if (peer) {
+        if ((rc = ep_prepare(L->ep, L->expert_count, s, &plan, g_err, sizeof(g_err)))) return rc;
+        pp.expert_dst = plan.d_expert_dst;
+        ep_mark(L->ep, 0, s);
+    }
     if (num_cta > 0) {
         n = launch_permute(pp, x_dtype, c.compute_dtype, num_cta, s);
         if (n < 0) return fail(MOE_ERR_CUDA, "permute launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -385,6 +404,18 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     if (!L->ep) {
         if ((rc = run_experts(L, L->xp, L->h, L->y, L->expert_offset, L->tile_prefix, T * L->k_tot, L->E, s, 4)))
             return rc;
+    } else if (peer) {
+        // every rank's permute kernel has written its rows into the owners' buffers once the
+        // all-reduce of the loss sums completes
+        if ((rc = ep_sums_barrier(L->ep, s, g_err, sizeof(g_err)))) return rc;
+        ep_mark(L->ep, 1, s);
+        if ((rc = ensure_plan(L, plan.xr, plan.hr, plan.rows_cap))) return rc;
+        if ((rc = run_experts(L, plan.xr, plan.hr, plan.yr, plan.d_local_off, plan.d_tile_prefix, plan.rows,
+                              L->e_hi - L->e_lo, s, 4)))
+            return rc;
+        ep_mark(L->ep, 2, s);
+        // all ranks' outputs are complete before anybody's combine kernel reads them
+        if ((rc = ep_barrier(L->ep, s, g_err, sizeof(g_err)))) return rc;
     } else {
         EpCall call;
         call.T = T;
@@ -420,10 +451,17 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     cp.idx = L->idx;
     cp.gate = L->gate;
     cp.pair_pos = L->pair_pos;
+    cp.expert_src = peer ? plan.d_expert_src : nullptr;
+    cp.expert_offset = L->expert_offset;
     n = launch_combine(cp, c.compute_dtype, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
     stage_mark(L, 6, s);
+    if (peer) {
+        ep_mark(L->ep, 3, s);
+        if ((rc = ep_finish_loss(L->ep, training, opt->loss, opt->routing_entropy, s, &L->launches, g_err, sizeof(g_err))))
+            return rc;
+    }
     return MOE_OK;
 }
 

@@ -92,6 +92,7 @@ template <typename XT, typename PT>
 __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermuteParams p) {
     __shared__ int s_base[MAX_EXPERTS];
     __shared__ int s_pos[PERM_MAX_PAIRS];
+    __shared__ int s_exp[PERM_MAX_PAIRS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t tok0 = (int64_t)blockIdx.x * p.tokens_per_cta;
     const int ntok = (int)min((int64_t)p.tokens_per_cta, p.T - tok0);
@@ -122,6 +123,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
                     pos = -1;
                 }
                 s_pos[q] = pos;
+                s_exp[q] = e;
                 p.pair_pos[tok0 * p.k_tot + q] = pos;
                 if (pos >= 0) p.row_token[pos] = (int)(tok0 + q / p.k_tot);
             }
@@ -131,6 +133,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
 
     const XT* x = reinterpret_cast<const XT*>(p.x);
     PT* xp = reinterpret_cast<PT*>(p.xp);
+    // (peer segments start at row boundaries of cudaMalloc'd buffers: 16-byte aligned when the rows are)
     const bool vec = (p.D * sizeof(XT)) % 16 == 0 && (p.D * sizeof(PT)) % 16 == 0 &&
                      ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.xp)) & 15) == 0;
     for (int tl = warp; tl < ntok; tl += PERM_THREADS / 32) {
@@ -138,7 +141,13 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
         int nd = 0;
         for (int j = 0; j < p.k_tot; ++j) {
             const int pos = s_pos[tl * p.k_tot + j];
-            if (pos >= 0) dst[nd++] = xp + (size_t)pos * p.D;
+            if (pos < 0) continue;
+            if (p.expert_dst) {
+                const int e = s_exp[tl * p.k_tot + j];
+                dst[nd++] = reinterpret_cast<PT*>(p.expert_dst[e]) + (size_t)(pos - p.expert_offset[e]) * p.D;
+            } else {
+                dst[nd++] = xp + (size_t)pos * p.D;
+            }
         }
         copy_row<XT, PT>(x + (size_t)(tok0 + tl) * p.D, dst, nd, p.D, lane, vec);
     }
@@ -169,6 +178,7 @@ constexpr int COMB_THREADS = 256;
 template <typename YT>
 __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombineParams p) {
     __shared__ int s_row[MAX_KTOT];
+    __shared__ const YT* s_ptr[MAX_KTOT];
     __shared__ float s_gate[MAX_KTOT];
     __shared__ int s_n;
     const int64_t t = blockIdx.x;
@@ -193,18 +203,25 @@ __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombinePara
             s_gate[i] = g;
         }
         s_n = n;
+        // row pointers: local y, or the owner GPU's output buffer in expert-parallel peer mode
+        for (int i = 0; i < n; ++i) {
+            if (p.expert_src)
+                s_ptr[i] = reinterpret_cast<const YT*>(p.expert_src[ids[i]]) +
+                           (size_t)(s_row[i] - p.expert_offset[ids[i]]) * p.O;
+            else
+                s_ptr[i] = reinterpret_cast<const YT*>(p.y) + (size_t)s_row[i] * p.O;
+        }
     }
     __syncthreads();
     const int n = s_n;
-    const YT* y = reinterpret_cast<const YT*>(p.y);
     float* out = p.out + (size_t)t * p.O;
     const bool vec = (p.O % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) &&
-                     ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+                     ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);   // peer segments: row-aligned cudaMalloc memory
     if (vec) {
         for (int c = threadIdx.x * 4; c < p.O; c += COMB_THREADS * 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int j = 0; j < n; ++j) {
-                const float4 v = ld_y4<YT>(y + (size_t)s_row[j] * p.O + c);
+                const float4 v = ld_y4<YT>(s_ptr[j] + c);
                 const float g = s_gate[j];
                 acc.x += g * v.x;
                 acc.y += g * v.y;
@@ -216,7 +233,7 @@ __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombinePara
     } else {
         for (int c = threadIdx.x; c < p.O; c += COMB_THREADS) {
             float acc = 0.f;
-            for (int j = 0; j < n; ++j) acc += s_gate[j] * ld_y1<YT>(y + (size_t)s_row[j] * p.O + c);
+            for (int j = 0; j < n; ++j) acc += s_gate[j] * ld_y1<YT>(s_ptr[j] + c);
             out[c] = acc;
         }
     }

@@ -17,10 +17,11 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _rank_main(rank, world, port, compute, E, k, T, D, H, O, q):
+def _rank_main(rank, world, port, compute, mode, E, k, T, D, H, O, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ["MOE_B200_EP_MODE"] = mode   # "peer": rows cross NVLink inside permute/combine; "nccl": send/recv
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -66,8 +67,9 @@ def _rank_main(rank, world, port, compute, E, k, T, D, H, O, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("mode", ["peer", "nccl"])
 @pytest.mark.parametrize("compute,tol", [("f32", 1e-5), ("bf16", 2e-2)])
-def test_expert_parallel_forward_matches_single_device_oracle(compute, tol):
+def test_expert_parallel_forward_matches_single_device_oracle(compute, tol, mode):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
@@ -75,8 +77,8 @@ def test_expert_parallel_forward_matches_single_device_oracle(compute, tol):
         world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29600 + (os.getpid() % 300)
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, compute, 8, 2, 333, 128, 256, 128, q)) for r in range(world)]
+    port = 29600 + (os.getpid() % 300) + (7 if mode == "peer" else 0) + (13 if compute == "bf16" else 0)
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, compute, mode, 8, 2, 333, 128, 256, 128, q)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
