@@ -1,0 +1,140 @@
+"""Llama2 integration (convert_to_moe / moe_transformer / sample_moe): structure checks on CPU in
+the spirit of the reference's script (test_moeLlama2_integration.jl:50-61, :579-664), and on the
+GPU the stories42M-shaped model of the benchmark configuration against the per-token CPU oracle."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def small_model(m, seed=0, **kw):
+    cfg = m.ModelConfig(dim=64, hidden_dim=96, n_layers=3, n_heads=4, n_kv_heads=2, vocab_size=300, seq_len=48)
+    for k_, v in kw.items():
+        setattr(cfg, k_, v)
+    return m.random_language_model(cfg, seed)
+
+
+def test_convert_to_moe_structure(lib_built):
+    import mixtureofexperts_b200 as m
+
+    lm = small_model(m)
+    mm = m.convert_to_moe(lm, [2, 3], num_experts=4, top_k=2, expert_init_strategy="perturb", expert_init_noise=0.01,
+                          seed=5)
+    assert [l.use_moe for l in mm.layers] == [False, True, True]
+    assert mm.config.dim == 64 and mm.config.moe_num_experts == 4          # getproperty delegation
+    l2 = mm.layers[1]
+    assert len(l2.moe_experts) == 4 and l2.moe_router_weight.shape == (4, 64)
+    for e in l2.moe_experts:
+        assert e.w1.shape == (96, 64) and e.w2.shape == (64, 96) and e.w3.shape == (96, 64)
+        # :perturb = dense FFN weights + N(0, noise^2)  (src/llama2/conversion.jl:290-294)
+        d = e.w1 - lm.weights.layers[1].w1
+        assert 0.008 < float(d.std()) < 0.012
+    # router ~ randn * sqrt(2/dim)  (conversion.jl:358-367)
+    assert abs(float(l2.moe_router_weight.std()) - (2 / 64) ** 0.5) < 0.03
+    # dense layers' weights are preserved, total parameters grow, active < total
+    assert np.array_equal(mm.layers[0].llama_layer.w1, lm.weights.layers[0].w1)
+    dense_params = sum(a.size for l in lm.weights.layers for a in l.__dict__.values()) + \
+        lm.weights.token_embedding_table.size + lm.weights.rms_final_weight.size + lm.weights.output_weight.size
+    assert m.count_parameters(mm) > dense_params
+    assert dense_params < m.count_active_parameters(mm) < m.count_parameters(mm)
+
+
+def test_convert_to_moe_strategies_and_validation(lib_built):
+    import mixtureofexperts_b200 as m
+
+    lm = small_model(m)
+    cp = m.convert_to_moe(lm, [1], num_experts=2, top_k=1, expert_init_strategy="copy")
+    assert np.array_equal(cp.layers[0].moe_experts[1].w2, lm.weights.layers[0].w2)
+    sp = m.convert_to_moe(lm, [1], num_experts=4, top_k=2, expert_init_strategy="split")
+    e1 = sp.layers[0].moe_experts[1]
+    assert np.array_equal(e1.w1[24:48], lm.weights.layers[0].w1[24:48]) and not e1.w1[:24].any() and not e1.w1[48:].any()
+    rd = m.convert_to_moe(lm, [1], num_experts=2, top_k=1, expert_init_strategy="random", seed=1)
+    assert abs(float(rd.layers[0].moe_experts[0].w1.std()) - (2 / 64) ** 0.5) < 0.02
+    for bad in (dict(moe_layers=[0]), dict(moe_layers=[4]), dict(top_k=5), dict(expert_init_strategy="nope"),
+                dict(num_experts=0)):
+        kw = dict(moe_layers=[1], num_experts=4, top_k=2, expert_init_strategy="perturb")
+        kw.update(bad)
+        layers = kw.pop("moe_layers")
+        with pytest.raises(ValueError):
+            m.convert_to_moe(lm, layers, **kw)
+
+
+def _to_oracle(mm):
+    from oracle import llama2_oracle as lo
+    from oracle import moe_oracle as orc
+
+    layers = []
+    for l in mm.layers:
+        ll = l.llama_layer
+        lw = lo.LayerW(rms_att=ll.rms_att_weight, rms_ffn=ll.rms_ffn_weight, wq=ll.wq, wk=ll.wk, wv=ll.wv, wo=ll.wo,
+                       w1=ll.w1, w2=ll.w2, w3=ll.w3, use_moe=l.use_moe)
+        if l.use_moe:
+            lw.router = l.moe_router_weight
+            lw.experts = [orc.GatedExpertWeights(w1=e.w1, w2=e.w2, w3=e.w3) for e in l.moe_experts]
+        layers.append(lw)
+    c = mm.config
+    return lo.Model(dim=c.dim, hidden_dim=c.hidden_dim, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
+                    vocab_size=c.vocab_size, seq_len=c.seq_len, embedding=mm.token_embedding_table, layers=layers,
+                    rms_final=mm.rms_final_weight, output=mm.output_weight, top_k=c.moe_top_k)
+
+
+def test_dense_host_plumbing_matches_oracle(lib_built):
+    """With no MoE layer nothing touches the GPU: the batched host attention/FFN must equal the
+    oracle's token-by-token restatement (GQA with 2 kv heads, RoPE, KV cache)."""
+    import mixtureofexperts_b200 as m
+    from oracle import llama2_oracle as lo
+
+    lm = small_model(m, seed=3)
+    mm = m.convert_to_moe(lm, [], num_experts=2, top_k=1)
+    toks = np.random.default_rng(0).integers(0, 300, 20)
+    ref = lo.forward_tokens(_to_oracle(mm), toks)["logits"]
+    st = m.MoERunState(mm)
+    a = m.moe_transformer(toks[:13], mm, st)            # prefill ...
+    b = np.concatenate([m.moe_transformer([t], mm, st) for t in toks[13:]])   # ... then decode steps
+    got = np.concatenate([a, b])
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-5
+
+
+@pytest.mark.gpu
+def test_stories42m_shaped_model_matches_oracle():
+    """BASELINE config 2: dim 512, hidden 1376, 8 layers, 8 heads, vocab 32000, MoE at layers
+    [2,4,6] with 8 experts, top-2, :perturb 0.01; 64 seeded token ids.  Final logits of all 64
+    positions within 1e-4 relative (FP32 end to end through 8 layers; the MoE layer itself is
+    held to 1e-5 elsewhere) and identical expert selections in every MoE layer."""
+    import mixtureofexperts_b200 as m
+    from oracle import llama2_oracle as lo
+
+    lm = m.random_language_model(m.ModelConfig(), seed=1236, std=0.02)
+    mm = m.convert_to_moe(lm, [2, 4, 6], num_experts=8, top_k=2, expert_init_strategy="perturb",
+                          expert_init_noise=0.01, seed=1237)
+    toks = np.random.Generator(np.random.PCG64(1238)).integers(0, 32000, 64)
+    ref = lo.forward_tokens(_to_oracle(mm), toks)
+    st = m.MoERunState(mm, 64)
+    got = m.moe_transformer(toks, mm, st)
+    assert np.isfinite(got).all() and 0.1 < np.linalg.norm(got[0]) < 1000      # the reference's sanity band
+    for li in (1, 3, 5):
+        assert np.array_equal(st.selected_experts[li], ref["selected"][li]), li
+    err = np.abs(got - ref["logits"]).max() / np.abs(ref["logits"]).max()
+    assert err < 1e-4, err
+    # decode path (T = 1 per call) agrees with the batched prefill
+    st2 = m.MoERunState(mm, 64)
+    step = np.concatenate([m.moe_transformer([t], mm, st2) for t in toks[:6]])
+    assert np.abs(step - got[:6]).max() / np.abs(got[:6]).max() < 1e-5
+
+
+@pytest.mark.gpu
+def test_sample_moe_generates_and_is_deterministic():
+    import mixtureofexperts_b200 as m
+
+    lm = small_model(m, seed=7)
+    mm = m.convert_to_moe(lm, [1, 3], num_experts=4, top_k=2, seed=8)
+    a = m.sample_moe(mm, "Tim was happy.", temperature=0.0, max_seq_len=30)
+    b = m.sample_moe(mm, "Tim was happy.", temperature=0.0, max_seq_len=30)
+    assert a == b and isinstance(a, str)
+    c = m.sample_moe(mm, "", temperature=0.9, max_seq_len=12, seed=3, stop_on_special_token=False)
+    assert len(c) > 0
+    with pytest.raises(ValueError):
+        m.sample_moe(mm, "", bos_token=False)
