@@ -23,6 +23,7 @@ enum : int32_t {
 
 constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
+constexpr int ROUTER_MAX_WARPS = 12;    // largest router CTA: 384 threads
 constexpr int ROUTER_TOKENS_PER_CTA = 64;
 constexpr int MAX_ROUTER_EXPERTS = 128; // upper bound on router rows
 constexpr int MAX_EXPERTS = 256;        // upper bound on experts per layer
@@ -133,13 +134,15 @@ struct GroupGemmParams {
 // ---- launchers (each returns the number of kernels it launched, or <0 on a launch error) ---
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s);
 int router_tokens_per_cta(int e_router);
-int router_e_pad(int e_router);          // router rows padded to 8, 16, 32, 64 or 128
+int router_e_pad(int e_router);          // router rows padded to a multiple of 8 (bucketed)
 int router_d_pad(int D);                 // K rows of the K-major copy (multiple of 128)
 int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_t s);
 int launch_scan(const ScanParams& p, cudaStream_t s);
+int launch_accumulate(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E, cudaStream_t s);
 int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s);
 int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s);
-int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, cudaStream_t s);
+int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, int64_t rows, int num_sms,
+                          cudaStream_t s);
 int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const float* logits, int64_t T,
                       int32_t* indices, float* gates, float* probs, cudaStream_t s);
 int launch_loss_only(float alpha, float z_weight, int n_probs, int k, int index_base, const int32_t* indices,

@@ -124,6 +124,12 @@ struct EpState {
     int32_t* d_flag = nullptr;             // barrier payload
 };
 
+int launch_finish_loss(const float* sums, int E, int E_probs, int k_tot, float alpha, float z_weight, int training,
+                       float* u_loss, float* u_entropy, cudaStream_t s) {
+    ep_finish_loss_kernel<<<1, 32, 0, s>>>(sums, E, E_probs, k_tot, alpha, z_weight, training, u_loss, u_entropy);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
 // Pure host arithmetic (no CUDA, no NCCL): see ep.h.
 int64_t ep_plan_layout(const int32_t* cnt, int W, int E, int me, int tile_m, int64_t* send_off, int64_t* recv_off,
                        int32_t* local_off, int32_t* tile_prefix) {

@@ -41,6 +41,11 @@ typedef int (*EpRunFn)(void* self, const void* a_in, void* h_buf, void* y_buf, c
 // m-tile prefix (tile_m rows per tile).  Returns the number of rows this rank receives.
 int64_t ep_plan_layout(const int32_t* cnt, int W, int E, int me, int tile_m, int64_t* send_off, int64_t* recv_off,
                        int32_t* local_off, int32_t* tile_prefix);
+// Loss from summed statistics {counts[E], prob sums[E_probs], lse^2, T, entropy}: the Switch loss
+// (+ z-loss) over all the tokens the sums cover.  Used for all ranks' tokens (expert parallel) and
+// for all chunks of a chunked host call.
+int launch_finish_loss(const float* sums, int E, int E_probs, int k_tot, float alpha, float z_weight, int training,
+                       float* u_loss, float* u_entropy, cudaStream_t s);
 int ep_unique_id(void* id128, char* err, size_t errlen);
 int ep_create(EpState** out, const EpConfig& cfg, const void* id128, char* err, size_t errlen);
 void ep_destroy(EpState*);

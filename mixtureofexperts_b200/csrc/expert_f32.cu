@@ -133,10 +133,131 @@ __global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemm
     }
 }
 
+// ---- few rows per expert (decode, tiny batches): stream the weights once ------------------------
+// One CTA owns (expert, 8*CW output columns); a warp owns CW columns; lanes split K in 16-byte
+// pieces, so every weight load instruction of a warp is a contiguous 512-byte read and a lane keeps
+// 2*CW (mode 1: 4*CW) of them in flight.  Four rows of the expert are held in registers per pass
+// (further rows re-read the CTA's weight slice, which is then L2-resident); partial dot products are
+// reduced with warp shuffles once per pass.  Bound: HBM, E*N*K*4 bytes of weights per GEMM.
+constexpr int SK_ROWS = 4;
+constexpr int SK_THREADS = 256;
+
+__device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc) {
+    acc = fmaf(a.x, b.x, acc);
+    acc = fmaf(a.y, b.y, acc);
+    acc = fmaf(a.z, b.z, acc);
+    acc = fmaf(a.w, b.w, acc);
+    return acc;
+}
+
+template <int MODE, int CW>
+__global__ void __launch_bounds__(SK_THREADS) group_gemm_f32_skinny_kernel(const GroupGemmParams p) {
+    constexpr int NB = (MODE == 1) ? 2 : 1;
+    const int e = blockIdx.y;
+    const int row_begin = p.expert_offset[e], row_end = p.expert_offset[e + 1];
+    if (row_begin >= row_end) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_base = (blockIdx.x * (SK_THREADS / 32) + warp) * CW;
+    if (n_base >= p.N) return;
+    const float* A = reinterpret_cast<const float*>(p.A);
+    const float* Bm[2] = {reinterpret_cast<const float*>(p.B0) + (size_t)e * p.N * p.K,
+                          MODE == 1 ? reinterpret_cast<const float*>(p.B1) + (size_t)e * p.N * p.K : nullptr};
+    float* C = reinterpret_cast<float*>(p.C);
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int r0 = row_begin; r0 < row_end; r0 += SK_ROWS) {
+        float acc[NB][CW][SK_ROWS];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int c = 0; c < CW; ++c)
+#pragma unroll
+                for (int r = 0; r < SK_ROWS; ++r) acc[b][c][r] = 0.f;
+        for (int kc = 0; kc < p.K; kc += 256) {
+            const int k0 = kc + lane * 4, k1 = kc + 128 + lane * 4;   // K % 4 == 0: a piece is all in or all out
+            float4 xa[SK_ROWS], xb[SK_ROWS];
+#pragma unroll
+            for (int r = 0; r < SK_ROWS; ++r) {
+                const bool ok = r0 + r < row_end;
+                const float* row = A + (size_t)(r0 + r) * p.K;
+                xa[r] = (ok && k0 < p.K) ? *reinterpret_cast<const float4*>(row + k0) : zero4;
+                xb[r] = (ok && k1 < p.K) ? *reinterpret_cast<const float4*>(row + k1) : zero4;
+            }
+            float4 wa[NB][CW], wb[NB][CW];
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int c = 0; c < CW; ++c) {
+                    const int n = n_base + c;
+                    const float* wrow = Bm[b] + (size_t)n * p.K;
+                    wa[b][c] = (n < p.N && k0 < p.K) ? __ldg(reinterpret_cast<const float4*>(wrow + k0)) : zero4;
+                    wb[b][c] = (n < p.N && k1 < p.K) ? __ldg(reinterpret_cast<const float4*>(wrow + k1)) : zero4;
+                }
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int c = 0; c < CW; ++c)
+#pragma unroll
+                    for (int r = 0; r < SK_ROWS; ++r)
+                        acc[b][c][r] = dot4(wb[b][c], xb[r], dot4(wa[b][c], xa[r], acc[b][c][r]));
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int c = 0; c < CW; ++c)
+#pragma unroll
+                for (int r = 0; r < SK_ROWS; ++r) {
+                    float v = acc[b][c][r];
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    acc[b][c][r] = v;
+                }
+        // lane (c*SK_ROWS + r) writes element (row r, column c)
+#pragma unroll
+        for (int c = 0; c < CW; ++c)
+#pragma unroll
+            for (int r = 0; r < SK_ROWS; ++r) {
+                if (lane == c * SK_ROWS + r) {
+                    const int row = r0 + r, n = n_base + c;
+                    if (row < row_end && n < p.N) {
+                        const float v = (MODE == 1) ? apply_act(p.activation, acc[0][c][r]) * acc[NB - 1][c][r]
+                                                    : acc[0][c][r];
+                        C[(size_t)row * p.N + n] = v;
+                    }
+                }
+            }
+    }
+}
+
+template <int MODE>
+int launch_skinny(const GroupGemmParams& p, int num_sms, cudaStream_t s) {
+    // fewer columns per warp when the problem would otherwise leave SMs without a CTA
+    const long ctas4 = (long)((p.N + 31) / 32) * p.E;
+    if (ctas4 >= 2L * num_sms) {
+        dim3 grid((p.N + 31) / 32, p.E);
+        group_gemm_f32_skinny_kernel<MODE, 4><<<grid, SK_THREADS, 0, s>>>(p);
+    } else if (ctas4 * 2 >= 2L * num_sms) {
+        dim3 grid((p.N + 15) / 16, p.E);
+        group_gemm_f32_skinny_kernel<MODE, 2><<<grid, SK_THREADS, 0, s>>>(p);
+    } else {
+        dim3 grid((p.N + 7) / 8, p.E);
+        group_gemm_f32_skinny_kernel<MODE, 1><<<grid, SK_THREADS, 0, s>>>(p);
+    }
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
 }  // namespace
 
-int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, cudaStream_t s) {
+int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, int64_t rows, int num_sms,
+                          cudaStream_t s) {
     if (max_mtiles <= 0) return 0;
+    const bool aligned = (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.A) & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(p.B0) & 15) == 0) &&
+                         (mode != 1 || (reinterpret_cast<uintptr_t>(p.B1) & 15) == 0);
+    if (aligned && rows <= 16L * p.E) {
+        // on average at most 16 rows per expert: weight streaming beats tiling
+        return mode == 1 ? launch_skinny<1>(p, num_sms, s) : launch_skinny<2>(p, num_sms, s);
+    }
     dim3 grid(max_mtiles, (p.N + BN - 1) / BN);
     if (mode == 1) group_gemm_f32_kernel<1><<<grid, THREADS, 0, s>>>(p);
     else group_gemm_f32_kernel<2><<<grid, THREADS, 0, s>>>(p);

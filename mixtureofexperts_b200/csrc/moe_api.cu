@@ -104,6 +104,14 @@ struct moe_layer {
     size_t hout_bytes = 0;
     void* hopt = nullptr;
     size_t hopt_bytes = 0;
+    // chunked host calls: copy-in / compute / copy-out overlap on three streams
+    static constexpr int MAX_CHUNKS = 8;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_in[MAX_CHUNKS] = {}, ev_done[MAX_CHUNKS] = {};
+    float* chunk_acc = nullptr;      // [E + E_probs + 3] summed statistics of the chunks
+    float* chunk_tmp = nullptr;
+    int64_t* chunk_tpe_acc = nullptr;  // [E]
+    int64_t* chunk_tpe_tmp = nullptr;
 
     // profiling: a ring of event sets, one set per forward call
     int prof_slots = 0;
@@ -263,7 +271,7 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.N = c.hidden_dim;
     g.K = c.input_dim;
     if (tc) n = launch_group_gemm_tc(L->plan, 1, g, max_mtiles * ((c.hidden_dim + 127) / 128), L->num_sms, s);
-    else n = launch_group_gemm_f32(g, 1, max_mtiles, s);
+    else n = launch_group_gemm_f32(g, 1, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 1 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
     stage_mark(L, ev_base, s);
@@ -275,15 +283,18 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.N = c.output_dim;
     g.K = c.hidden_dim;
     if (tc) n = launch_group_gemm_tc(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
-    else n = launch_group_gemm_f32(g, 2, max_mtiles, s);
+    else n = launch_group_gemm_f32(g, 2, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 2 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
     stage_mark(L, ev_base + 1, s);
     return MOE_OK;
 }
 
+// partial_sums != null: this call covers one chunk of a larger batch; the scan kernel leaves its
+// statistics there and the caller finishes loss and entropy from the sum over chunks.
 int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int training, float* out,
-                   const moe_forward_outputs_t* opt, cudaStream_t s) {
+                   const moe_forward_outputs_t* opt, cudaStream_t s, float* partial_sums = nullptr,
+                   int partial_want_entropy = 0) {
     const moe_config_t& c = L->cfg;
     static const moe_forward_outputs_t none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     if (!opt) opt = &none;
@@ -324,7 +335,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     r.bias_gates_only = c.bias_gates_only;
     r.index_base = c.index_base;
     r.tokens_per_cta = L->tokens_per_cta;
-    r.want_entropy = opt->routing_entropy != nullptr;
+    r.want_entropy = opt->routing_entropy != nullptr || partial_want_entropy;
     r.idx = L->idx;
     r.gate = L->gate;
     r.cta_counts = L->cta_counts;
@@ -362,10 +373,10 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     sp.expert_offset = L->expert_offset;
     sp.tile_prefix = L->tile_prefix;
     sp.loss_internal = L->loss_dev;
-    sp.u_loss = L->ep ? nullptr : opt->loss;
+    sp.u_loss = (L->ep || partial_sums) ? nullptr : opt->loss;
     sp.u_tokens_per_expert = opt->tokens_per_expert;
-    sp.u_entropy = L->ep ? nullptr : opt->routing_entropy;
-    sp.ep_sums = L->ep ? ep_sums_buffer(L->ep) : nullptr;
+    sp.u_entropy = (L->ep || partial_sums) ? nullptr : opt->routing_entropy;
+    sp.ep_sums = L->ep ? ep_sums_buffer(L->ep) : partial_sums;
     n = launch_scan(sp, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "scan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
@@ -554,6 +565,16 @@ int moe_layer_destroy(moe_layer_t* L) {
     if (L->plan) tc_plan_destroy(L->plan);
     for (auto& e : L->ev) cudaEventDestroy(e);
     if (L->stream) cudaStreamDestroy(L->stream);
+    if (L->s_in) cudaStreamDestroy(L->s_in);
+    if (L->s_out) cudaStreamDestroy(L->s_out);
+    for (auto& e : L->ev_in)
+        if (e) cudaEventDestroy(e);
+    for (auto& e : L->ev_done)
+        if (e) cudaEventDestroy(e);
+    dev_free(L->chunk_acc);
+    dev_free(L->chunk_tmp);
+    dev_free(L->chunk_tpe_acc);
+    dev_free(L->chunk_tpe_tmp);
     delete L;
     return MOE_OK;
 }
@@ -681,6 +702,81 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     d.tokens_per_expert = opt->tokens_per_expert ? reinterpret_cast<int64_t*>(ob_dev + o_tpe) : nullptr;
     d.routing_entropy = opt->routing_entropy ? reinterpret_cast<float*>(ob_dev + o_ent) : nullptr;
     cudaStream_t s = L->stream;
+    // Large batches are cut into token chunks: chunk c+1 is copied in and chunk c-1 copied out
+    // while chunk c computes.  Tokens are independent, so outputs do not change; loss, entropy
+    // and counts are finished from the statistics summed over the chunks.
+    int nchunks = 1;
+    if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192) {
+        static int env_chunks = -1;
+        if (env_chunks < 0) {
+            const char* e = getenv("MOE_B200_HOST_CHUNKS");
+            env_chunks = e ? atoi(e) : 0;
+        }
+        nchunks = env_chunks > 0 ? env_chunks : 4;
+        if (nchunks > moe_layer::MAX_CHUNKS) nchunks = moe_layer::MAX_CHUNKS;
+    }
+    if (nchunks > 1) {
+        const int nsum = L->E + L->E_probs + 3;
+        if (!L->s_in) {
+            CUDA_TRY(cudaStreamCreateWithFlags(&L->s_in, cudaStreamNonBlocking));
+            CUDA_TRY(cudaStreamCreateWithFlags(&L->s_out, cudaStreamNonBlocking));
+            for (auto& e : L->ev_in) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            for (auto& e : L->ev_done) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            if ((rc = dev_alloc(&L->chunk_acc, (size_t)nsum))) return rc;
+            if ((rc = dev_alloc(&L->chunk_tmp, (size_t)nsum))) return rc;
+            if ((rc = dev_alloc(&L->chunk_tpe_acc, (size_t)L->E))) return rc;
+            if ((rc = dev_alloc(&L->chunk_tpe_tmp, (size_t)L->E))) return rc;
+        }
+        const int64_t Tc = ((T + nchunks - 1) / nchunks + 63) / 64 * 64;
+        const size_t xrow = (size_t)L->cfg.input_dim * dtype_size(x_dtype), orow = (size_t)L->cfg.output_dim * 4;
+        CUDA_TRY(cudaMemsetAsync(L->chunk_acc, 0, sizeof(float) * nsum, s));
+        CUDA_TRY(cudaMemsetAsync(L->chunk_tpe_acc, 0, sizeof(int64_t) * L->E, s));
+        int c = 0;
+        for (int64_t t0 = 0; t0 < T; t0 += Tc, ++c) {
+            const int64_t n = (T - t0 < Tc) ? T - t0 : Tc;
+            CUDA_TRY(cudaMemcpyAsync((char*)L->hx + t0 * xrow, (const char*)x + t0 * xrow, n * xrow,
+                                     cudaMemcpyHostToDevice, L->s_in));
+            CUDA_TRY(cudaEventRecord(L->ev_in[c], L->s_in));
+            CUDA_TRY(cudaStreamWaitEvent(s, L->ev_in[c], 0));
+            moe_forward_outputs_t dc = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+            if (d.indices) dc.indices = d.indices + t0 * ku;
+            if (d.gates) dc.gates = d.gates + t0 * ku;
+            if (d.probs) dc.probs = d.probs + t0 * ep;
+            if (d.logits) dc.logits = d.logits + t0 * er;
+            dc.tokens_per_expert = L->chunk_tpe_tmp;
+            if ((rc = forward_device(L, (char*)L->hx + t0 * xrow, x_dtype, n, training, L->hout + t0 * L->cfg.output_dim,
+                                     &dc, s, L->chunk_tmp, d.routing_entropy != nullptr)))
+                return rc;
+            if (launch_accumulate(L->chunk_acc, L->chunk_tmp, nsum, L->chunk_tpe_acc, L->chunk_tpe_tmp, L->E, s) < 0)
+                return fail(MOE_ERR_CUDA, "accumulate launch failed");
+            L->launches += 1;
+            CUDA_TRY(cudaEventRecord(L->ev_done[c], s));
+            CUDA_TRY(cudaStreamWaitEvent(L->s_out, L->ev_done[c], 0));
+            CUDA_TRY(cudaMemcpyAsync((char*)out + t0 * orow, (char*)L->hout + t0 * orow, n * orow, cudaMemcpyDeviceToHost,
+                                     L->s_out));
+            if (d.indices) CUDA_TRY(cudaMemcpyAsync(opt->indices + t0 * ku, dc.indices, (size_t)n * ku * 4, cudaMemcpyDeviceToHost, L->s_out));
+            if (d.gates) CUDA_TRY(cudaMemcpyAsync(opt->gates + t0 * ku, dc.gates, (size_t)n * ku * 4, cudaMemcpyDeviceToHost, L->s_out));
+            if (d.probs) CUDA_TRY(cudaMemcpyAsync(opt->probs + t0 * ep, dc.probs, (size_t)n * ep * 4, cudaMemcpyDeviceToHost, L->s_out));
+            if (d.logits) CUDA_TRY(cudaMemcpyAsync(opt->logits + t0 * er, dc.logits, (size_t)n * er * 4, cudaMemcpyDeviceToHost, L->s_out));
+        }
+        if (launch_finish_loss(L->chunk_acc, L->E, L->E_probs, L->k_tot, L->cfg.balance_alpha, L->cfg.z_loss_weight,
+                               training, d.loss, d.routing_entropy, s) < 0)
+            return fail(MOE_ERR_CUDA, "loss launch failed");
+        L->launches += 1;
+        if (d.loss) CUDA_TRY(cudaMemcpyAsync(opt->loss, d.loss, 4, cudaMemcpyDeviceToHost, s));
+        if (d.tokens_per_expert)
+            CUDA_TRY(cudaMemcpyAsync(opt->tokens_per_expert, L->chunk_tpe_acc, (size_t)L->E * 8, cudaMemcpyDeviceToHost, s));
+        if (d.routing_entropy) CUDA_TRY(cudaMemcpyAsync(opt->routing_entropy, d.routing_entropy, 4, cudaMemcpyDeviceToHost, s));
+        CUDA_TRY(cudaStreamSynchronize(L->s_out));
+        CUDA_TRY(cudaStreamSynchronize(s));
+        int32_t stc = 0;
+        CUDA_TRY(cudaMemcpy(&stc, L->status, sizeof(stc), cudaMemcpyDeviceToHost));
+        if (stc != DEV_OK) {
+            cudaMemset(L->status, 0, sizeof(int32_t));
+            return fail(stc == DEV_BAD_INDEX ? MOE_ERR_INVALID : MOE_ERR_TIMEOUT, "device status %d after forward", stc);
+        }
+        return MOE_OK;
+    }
     if (xb) CUDA_TRY(cudaMemcpyAsync(L->hx, x, xb, cudaMemcpyHostToDevice, s));
     if ((rc = forward_device(L, L->hx, x_dtype, T, training, L->hout, &d, s))) return rc;
     if (ob) CUDA_TRY(cudaMemcpyAsync(out, L->hout, ob, cudaMemcpyDeviceToHost, s));

@@ -265,23 +265,26 @@ struct RouterStage {
     float w[BK][E_PAD];
 };
 
-template <int E_PAD, int BK, typename XT>
+template <int E_PAD, int BK, int KS, typename XT>
 union RouterSmem {
     RouterStage<E_PAD, BK, XT> st[RT_STAGES];
-    float red[(ROUTER_THREADS / (16 * (E_PAD / 8))) * RT_BT * E_PAD];  // [KS][64][E_PAD] = 8192 floats
+    float red[KS * RT_BT * E_PAD];  // [KS][64][E_PAD]
 };
 
 // Gate GEMM as a register-tiled FP32 FMA kernel: a CTA owns 64 tokens x E_PAD router rows; a
-// thread owns 4 tokens x 8 rows and 1/KS of every K chunk, KS = 256/(16*E_PAD/8), so the
+// thread owns 4 tokens x 8 rows and 1/KS of every K chunk (16 * E_PAD/8 * KS threads), so the
 // per-thread FP32 chain stays short; an inner accumulator is folded into an outer one every
 // ~256 products (two-level summation) and the KS partials are added in a fixed order.  x (in
 // its own dtype) and the K-major router matrix ([K][E_PAD], built once per set_router) stream
 // through a 3-stage cp.async ring; every token row contributes BK contiguous elements per chunk.
-template <int E_PAD, int BK, typename XT>
-__global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterParams p) {
+template <int E_PAD, int BK, int KS, typename XT>
+__global__ void __launch_bounds__(16 * (E_PAD / 8) * KS, (16 * (E_PAD / 8) * KS <= 320 ? 2 : 1))
+router_kernel(const RouterParams p) {
     constexpr int EG = E_PAD / 8;
     constexpr int TG = 16;
-    constexpr int KS = ROUTER_THREADS / (TG * EG);
+    constexpr int NTHREADS = TG * EG * KS;
+    constexpr int NWARPS = NTHREADS / 32;
+    static_assert(NTHREADS % 32 == 0 && NWARPS <= ROUTER_MAX_WARPS, "thread layout");
     constexpr int KPT = BK / KS;
     constexpr int FOLD = (256 / KPT) > 0 ? (256 / KPT) : 1;
     constexpr int PER16 = XElt<XT>::PER16;
@@ -290,16 +293,16 @@ __global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterP
     using Stage = RouterStage<E_PAD, BK, XT>;
     static_assert(KPT >= 2 && KPT % 2 == 0, "tile configuration");
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    RouterSmem<E_PAD, BK, XT>& sm = *reinterpret_cast<RouterSmem<E_PAD, BK, XT>*>(smem_raw);
+    RouterSmem<E_PAD, BK, KS, XT>& sm = *reinterpret_cast<RouterSmem<E_PAD, BK, KS, XT>*>(smem_raw);
     __shared__ int s_cnt[MAX_EXPERTS];
-    __shared__ float s_psum[ROUTER_WARPS][MAX_EXPERTS];
-    __shared__ float s_lse2[ROUTER_WARPS];
-    __shared__ double s_ent[ROUTER_WARPS];
+    __shared__ float s_psum[NWARPS][MAX_EXPERTS];
+    __shared__ float s_lse2[NWARPS];
+    __shared__ double s_ent[NWARPS];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int eg = tid % EG, tg = (tid / EG) % TG, ks = tid / (EG * TG);
-    for (int i = tid; i < MAX_EXPERTS; i += ROUTER_THREADS) s_cnt[i] = 0;
-    for (int i = tid; i < ROUTER_WARPS * MAX_EXPERTS; i += ROUTER_THREADS) (&s_psum[0][0])[i] = 0.f;
+    for (int i = tid; i < MAX_EXPERTS; i += NTHREADS) s_cnt[i] = 0;
+    for (int i = tid; i < NWARPS * MAX_EXPERTS; i += NTHREADS) (&s_psum[0][0])[i] = 0.f;
 
     const int64_t tok0 = (int64_t)blockIdx.x * RT_BT;
     const XT* x = reinterpret_cast<const XT*>(p.x);
@@ -311,7 +314,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterP
             Stage& st = sm.st[c % RT_STAGES];
             const int kbase = c * BK;
             if (vec_x) {
-                for (int u = tid; u < XUNITS; u += ROUTER_THREADS) {
+                for (int u = tid; u < XUNITS; u += NTHREADS) {
                     const int tok = u / UPR, q = u % UPR;
                     const int64_t t = tok0 + tok;
                     const int k0 = kbase + q * PER16;
@@ -320,7 +323,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterP
                     cp_async16_zfill(&st.x[tok][q * PER16], src, bytes);
                 }
             } else {
-                for (int i = tid; i < RT_BT * BK; i += ROUTER_THREADS) {
+                for (int i = tid; i < RT_BT * BK; i += NTHREADS) {
                     const int tok = i / BK, kk = i % BK;
                     const int64_t t = tok0 + tok;
                     XT v = XT(0.f);
@@ -331,7 +334,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterP
             // rows [kbase, kbase+BK) of the K-major router matrix: one contiguous block (rows past D are zero)
             const float* src = p.wt + (size_t)kbase * E_PAD;
             float* dst = &st.w[0][0];
-            for (int u = tid; u < BK * E_PAD / 4; u += ROUTER_THREADS) cp_async16(dst + u * 4, src + u * 4);
+            for (int u = tid; u < BK * E_PAD / 4; u += NTHREADS) cp_async16(dst + u * 4, src + u * 4);
         }
         cp_async_commit();   // always commit, so that group counting stays uniform
     };
@@ -421,8 +424,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterP
     constexpr int NJ = (E_PAD + 31) / 32;
     float lse2 = 0.f;
     double ent = 0.0;
-    for (int a = 0; a < RT_BT / ROUTER_WARPS; ++a) {
-        const int tok = warp * (RT_BT / ROUTER_WARPS) + a;
+    for (int tok = warp; tok < RT_BT; tok += NWARPS) {
         const int64_t t = tok0 + tok;
         if (t >= p.T) break;
         float lg[NJ];
@@ -443,17 +445,17 @@ __global__ void __launch_bounds__(ROUTER_THREADS, 2) router_kernel(const RouterP
         s_ent[warp] = ent;
     }
     __syncthreads();
-    for (int e = tid; e < p.E; e += ROUTER_THREADS) p.cta_counts[(size_t)blockIdx.x * p.E + e] = s_cnt[e];
-    for (int e = tid; e < p.E_probs; e += ROUTER_THREADS) {
+    for (int e = tid; e < p.E; e += NTHREADS) p.cta_counts[(size_t)blockIdx.x * p.E + e] = s_cnt[e];
+    for (int e = tid; e < p.E_probs; e += NTHREADS) {
         float s = 0.f;
 #pragma unroll
-        for (int w = 0; w < ROUTER_WARPS; ++w) s += s_psum[w][e];
+        for (int w = 0; w < NWARPS; ++w) s += s_psum[w][e];
         p.cta_psum[(size_t)blockIdx.x * (p.E_probs + 1) + e] = s;
     }
     if (tid == 0) {
         float s = 0.f;
         double d = 0.0;
-        for (int w = 0; w < ROUTER_WARPS; ++w) {
+        for (int w = 0; w < NWARPS; ++w) {
             s += s_lse2[w];
             d += s_ent[w];
         }
@@ -490,33 +492,35 @@ __global__ void __launch_bounds__(ROUTER_THREADS) gates_only_kernel(GateCtx c, c
     gate_token<NJ>(c, t, lg, lane, s_cnt, s_psum[warp], lse2, ent);
 }
 
-template <int E_PAD, int BK, typename XT>
+template <int E_PAD, int BK, int KS, typename XT>
 int launch_router_t(const RouterParams& p, int num_cta, cudaStream_t s) {
-    auto kern = router_kernel<E_PAD, BK, XT>;
-    const size_t smem = sizeof(RouterSmem<E_PAD, BK, XT>);
+    auto kern = router_kernel<E_PAD, BK, KS, XT>;
+    const size_t smem = sizeof(RouterSmem<E_PAD, BK, KS, XT>);
     static bool attr_done = false;   // per instantiation
     if (!attr_done) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
         attr_done = true;
     }
-    kern<<<num_cta, ROUTER_THREADS, smem, s>>>(p);
+    kern<<<num_cta, 16 * (E_PAD / 8) * KS, smem, s>>>(p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
-template <int E_PAD, int BK>
+template <int E_PAD, int BK, int KS>
 int launch_router_e(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s) {
-    if (x_dtype == MOE_DTYPE_F32) return launch_router_t<E_PAD, BK, float>(p, num_cta, s);
-    return launch_router_t<E_PAD, BK, __nv_bfloat16>(p, num_cta, s);
+    if (x_dtype == MOE_DTYPE_F32) return launch_router_t<E_PAD, BK, KS, float>(p, num_cta, s);
+    return launch_router_t<E_PAD, BK, KS, __nv_bfloat16>(p, num_cta, s);
 }
 
 }  // namespace
 
 int router_tokens_per_cta(int) { return ROUTER_TOKENS_PER_CTA; }
 
+// Router rows are padded to one of these widths (multiples of 8 = the per-thread row tile).
 int router_e_pad(int e_router) {
-    int e = 8;
-    while (e < e_router) e <<= 1;
-    return e;
+    static const int buckets[] = {8, 16, 24, 32, 48, 64, 72, 80, 96, 128};
+    for (int b : buckets)
+        if (e_router <= b) return b;
+    return 128;
 }
 
 int router_d_pad(int D) { return (D + 127) / 128 * 128; }
@@ -530,12 +534,18 @@ int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_
 }
 
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s) {
+    // <E_PAD, BK, KS>: 16 * E_PAD/8 * KS threads
     switch (router_e_pad(p.E_router)) {
-        case 8: return launch_router_e<8, 128>(p, x_dtype, num_cta, s);
-        case 16: return launch_router_e<16, 128>(p, x_dtype, num_cta, s);
-        case 32: return launch_router_e<32, 128>(p, x_dtype, num_cta, s);
-        case 64: return launch_router_e<64, 64>(p, x_dtype, num_cta, s);
-        case 128: return launch_router_e<128, 32>(p, x_dtype, num_cta, s);
+        case 8: return launch_router_e<8, 128, 16>(p, x_dtype, num_cta, s);
+        case 16: return launch_router_e<16, 128, 8>(p, x_dtype, num_cta, s);
+        case 24: return launch_router_e<24, 128, 4>(p, x_dtype, num_cta, s);
+        case 32: return launch_router_e<32, 128, 4>(p, x_dtype, num_cta, s);
+        case 48: return launch_router_e<48, 64, 2>(p, x_dtype, num_cta, s);
+        case 64: return launch_router_e<64, 64, 2>(p, x_dtype, num_cta, s);
+        case 72: return launch_router_e<72, 64, 2>(p, x_dtype, num_cta, s);
+        case 80: return launch_router_e<80, 32, 2>(p, x_dtype, num_cta, s);
+        case 96: return launch_router_e<96, 32, 2>(p, x_dtype, num_cta, s);
+        case 128: return launch_router_e<128, 32, 1>(p, x_dtype, num_cta, s);
         default: return -1;
     }
 }

@@ -175,7 +175,20 @@ __global__ void __launch_bounds__(SCAN_THREADS) loss_only_kernel(float alpha, fl
     }
 }
 
+// acc += tmp for the per-chunk loss sums and expert counts of a chunked host forward
+__global__ void accumulate_kernel(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) acc[i] += tmp[i];
+    if (tacc && i < E) tacc[i] += ttmp[i];
+}
+
 }  // namespace
+
+int launch_accumulate(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E, cudaStream_t s) {
+    const int m = n > E ? n : E;
+    accumulate_kernel<<<(m + 255) / 256, 256, 0, s>>>(acc, tmp, n, tacc, ttmp, E);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
 
 int launch_scan(const ScanParams& p, cudaStream_t s) {
     scan_loss_kernel<<<1, SCAN_THREADS, 0, s>>>(p);

@@ -190,7 +190,33 @@ def test_two_runs_are_bit_identical_and_workspace_grows():
     a = a.clone()
     b, lb = layer(xt.t(), training=True)
     assert torch.equal(a, b) and float(la.item()) == float(lb.item())
-    assert torch.equal(small, a[:, :10])
+    # a 10-token call may take another kernel (weight streaming) than the 700-token call: same
+    # values up to FP32 summation order
+    assert (small - a[:, :10]).abs().max().item() <= 1e-5 * a.abs().max().item()
+    layer.close()
+
+
+@pytest.mark.parametrize("gate_kind,E,S,k", [("topk", 8, 0, 2), ("shared", 10, 2, 3)])
+def test_chunked_host_call_equals_device_call(gate_kind, E, S, k):
+    """Host calls with >= 8192 tokens are pipelined over token chunks (copy-in / compute / copy-out
+    overlap); outputs must not change, and loss/entropy/counts finished from the summed chunk
+    statistics must agree with the one-pass device call."""
+    T, D, H, O = 8200 + 37, 64, 96, 48
+    x, w = orc.make_layer_inputs(31, T, D, H, O, E, init="normal", std=0.25)
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=device_gate(gate_kind, k, S, E))
+    out_d, loss_d, st_d, rt_d = layer(torch.from_numpy(x).cuda().t(), training=True, return_stats=True,
+                                      return_routing=True)
+    counts_d = st_d["tokens_per_expert"].copy()
+    ent_d = st_d["routing_entropy"][-1]
+    out_h, loss_h, st_h, rt_h = layer(np.asfortranarray(x.T), training=True, return_stats=True, return_routing=True)
+    assert np.array_equal(out_h, out_d.cpu().numpy())
+    assert np.array_equal(rt_h["indices"], rt_d["indices"].cpu().numpy())
+    assert np.array_equal(rt_h["gates"], rt_d["gates"].cpu().numpy())
+    assert np.array_equal(rt_h["probs"], rt_d["probs"].cpu().numpy())
+    assert abs(float(loss_h) - float(loss_d.item())) < 1e-6 * abs(float(loss_d.item()))
+    assert np.array_equal(st_h["tokens_per_expert"], 2 * counts_d)
+    assert abs(st_h["routing_entropy"][-1] - ent_d) < 1e-6
+    assert layer.device_status() == 0
     layer.close()
 
 
