@@ -88,6 +88,12 @@ typedef struct moe_config {
     int32_t bias_gates_only;  /* 1: logit_bias changes indices/gates but not probs (the
                                  AuxiliaryFreeLoss hook, moe_layer.jl:137-140); 0: bias is
                                  part of the logits (a Dense router with bias) */
+    float   capacity_factor;  /* MoEConfig.capacity_factor */
+    int32_t drop_tokens;      /* MoEConfig.drop_tokens: when set and training != 0, a forward applies
+                                 apply_capacity_constraint (src/core/moe_layer.jl:221-248): per expert
+                                 the first ceil(capacity_factor*T/E) (token, slot) pairs in token order
+                                 keep their slot, later ones get id index_base-1 and gate 0, and every
+                                 token's gates are renormalised.  Not with LAYER_BLEND or expert parallel. */
 } moe_config_t;
 
 typedef struct moe_layer moe_layer_t;   /* opaque: one per (layer, device) */

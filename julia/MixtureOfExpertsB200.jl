@@ -27,6 +27,7 @@ struct CMoeConfig            # moe_config_t
     gate_kind::Int32; activation::Int32; compute_dtype::Int32; shared_mode::Int32
     balance_alpha::Float32; z_loss_weight::Float32
     index_base::Int32; bias_gates_only::Int32
+    capacity_factor::Float32; drop_tokens::Int32
 end
 
 struct CForwardOutputs       # moe_forward_outputs_t (all nullable)
@@ -128,7 +129,8 @@ function MoELayer(config::MoEConfig; device::Int = 0, compute_dtype::Symbol = :f
     nshared = gate_shared > 0 ? gate_shared : config.num_shared_experts
     c = CMoeConfig(config.num_experts, nshared, k, config.input_dim, config.hidden_dim, config.output_dim,
                    kind, activation_enum(config.activation), compute_dtype == :bf16 ? DTYPE_BF16 : DTYPE_F32,
-                   shared_mode, config.balance_loss.α, config.z_loss_weight, 1, 0)
+                   shared_mode, config.balance_loss.α, config.z_loss_weight, 1, 0,
+                   config.capacity_factor, config.drop_tokens ? 1 : 0)
     h = Ref{Ptr{Cvoid}}(C_NULL)
     check(ccall((:moe_layer_create, LIB), Cint, (Ref{CMoeConfig}, Cint, Ref{Ptr{Cvoid}}), c, device, h))
     experts = [GatedExpert(config.input_dim, config.hidden_dim, config.output_dim, config.activation)

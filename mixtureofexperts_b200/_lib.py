@@ -44,6 +44,7 @@ class MoeConfig(C.Structure):
         ("gate_kind", C.c_int32), ("activation", C.c_int32), ("compute_dtype", C.c_int32),
         ("shared_mode", C.c_int32), ("balance_alpha", C.c_float), ("z_loss_weight", C.c_float),
         ("index_base", C.c_int32), ("bias_gates_only", C.c_int32),
+        ("capacity_factor", C.c_float), ("drop_tokens", C.c_int32),
     ]
 
 

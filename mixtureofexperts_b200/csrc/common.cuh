@@ -30,7 +30,8 @@ constexpr int MAX_EXPERTS = 256;        // upper bound on experts per layer
 constexpr int MAX_KTOT = 16;            // upper bound on selected experts per token
 
 // Tile height of the grouped GEMMs: an expert's rows are cut into tiles of this many rows.
-constexpr int TC_TILE_M = 128;   // tcgen05 path
+constexpr int TC_TILE_M = 128;   // tcgen05 path, one CTA per tile
+constexpr int TC_PAIR_TILE_M = 256;  // tcgen05 path, CTA pair per tile (cta_group::2)
 constexpr int F32_TILE_M = 16;   // FP32 SIMT path
 
 struct RouterParams {
@@ -70,6 +71,7 @@ struct ScanParams {
     int num_cta;
     int tile_m;
     int training;
+    int capacity;             // rows an expert may keep (capacity constraint), -1 = unlimited
     float alpha, z_weight;
     int32_t* cta_counts;      // in: per-CTA counts; out: exclusive prefix over CTAs
     const float* cta_psum;
@@ -99,6 +101,14 @@ struct PermuteParams {
     int32_t* row_token;           // [P]
     int32_t* status;
     int64_t P_cap;
+    // capacity constraint (capacity >= 0): pairs ranked >= capacity inside their expert are dropped,
+    // gates renormalised per token; idx/gate (and the caller's copies) are rewritten
+    int capacity;
+    int index_base;
+    int32_t* idx_rw;
+    float* gate_rw;
+    int32_t* u_idx;
+    float* u_gate;
     // expert-parallel peer mode (else null): expert_dst[e] is where this rank's rows for expert e
     // start, possibly in another GPU's memory; row (pos - expert_offset[e]) of that segment is written
     void* const* expert_dst;
@@ -160,6 +170,8 @@ int tc_plan_encode(TcGemmPlan*, const void* xp, const void* h, int64_t P_cap, in
                    const void* w1, const void* w3, const void* w2, const char** out_msg);
 int launch_group_gemm_tc(const TcGemmPlan*, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
                          cudaStream_t s);
+int launch_group_gemm_tc2(const TcGemmPlan*, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
+                          cudaStream_t s);
 
 __host__ __device__ inline float bf16_bits_to_float(uint16_t b) {
     union { uint32_t u; float f; } v;

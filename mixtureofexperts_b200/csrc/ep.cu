@@ -182,8 +182,8 @@ int ep_create(EpState** out, const EpConfig& cfg, const void* id128, char* err, 
     bool ok = cudaMalloc(&ep->d_sums, sizeof(float) * (cfg.E + cfg.E_probs + 3)) == cudaSuccess &&
               cudaMalloc(&ep->d_all_counts, sizeof(int32_t) * cfg.world * cfg.E) == cudaSuccess &&
               cudaMallocHost(&ep->h_all_counts, sizeof(int32_t) * cfg.world * cfg.E) == cudaSuccess &&
-              cudaMalloc(&ep->d_tables, sizeof(int32_t) * 2 * (ep->per + 1)) == cudaSuccess &&
-              cudaMallocHost(&ep->h_tables, sizeof(int32_t) * 2 * (ep->per + 1)) == cudaSuccess;
+              cudaMalloc(&ep->d_tables, sizeof(int32_t) * 3 * (ep->per + 1)) == cudaSuccess &&
+              cudaMallocHost(&ep->h_tables, sizeof(int32_t) * 3 * (ep->per + 1)) == cudaSuccess;
     for (auto& e : ep->ev) ok = ok && cudaEventCreate(&e) == cudaSuccess;
     const char* mode = getenv("MOE_B200_EP_MODE");
     ep->peer_mode = !(mode && strcmp(mode, "nccl") == 0);
@@ -447,7 +447,16 @@ int ep_prepare(EpState* ep, const int32_t* d_expert_count, cudaStream_t s, EpPla
     int32_t* h_off = ep->h_tables;
     int32_t* h_tp = ep->h_tables + (per + 1);
     const int64_t rows = ep_plan_layout(cnt, W, E, me, g.tile_m, send_off.data(), recv_off.data(), h_off, h_tp);
-    EP_CUDA(cudaMemcpyAsync(ep->d_tables, ep->h_tables, sizeof(int32_t) * 2 * (per + 1), cudaMemcpyHostToDevice, s));
+    int32_t* h_tp_alt = ep->h_tables + 2 * (per + 1);
+    if (g.tile_m_alt > 0) {
+        int32_t tiles = 0;
+        for (int el = 0; el < per; ++el) {
+            h_tp_alt[el] = tiles;
+            tiles += (int32_t)((expert_rows[(size_t)me * per + el] + g.tile_m_alt - 1) / g.tile_m_alt);
+        }
+        h_tp_alt[per] = tiles;
+    }
+    EP_CUDA(cudaMemcpyAsync(ep->d_tables, ep->h_tables, sizeof(int32_t) * 3 * (per + 1), cudaMemcpyHostToDevice, s));
 
     // where my rows for expert e start inside its owner's buffers:
     //   (rows of the owner's earlier local experts) + (rows of expert e from lower ranks)
@@ -472,6 +481,7 @@ int ep_prepare(EpState* ep, const int32_t* d_expert_count, cudaStream_t s, EpPla
     plan->yr = ep->yr;
     plan->d_local_off = ep->d_tables;
     plan->d_tile_prefix = ep->d_tables + (per + 1);
+    plan->d_tile_prefix_alt = g.tile_m_alt > 0 ? ep->d_tables + 2 * (per + 1) : nullptr;
     plan->d_expert_dst = ep->d_ptrs;
     plan->d_expert_src = const_cast<const void* const*>(ep->d_ptrs + E);
     return MOE_OK;

@@ -15,6 +15,7 @@ struct EpConfig {
     int D, H, O;
     int elt;       // bytes per element of the row buffers (2 = BF16, 4 = FP32)
     int tile_m;    // m-tile height of the grouped GEMM that will run on the received rows
+    int tile_m_alt;  // second tile height the caller may choose per call (0 = none)
     float alpha, z_weight;
 };
 
@@ -66,7 +67,8 @@ struct EpPlan {
     void* hr;                         // [rows_cap][H]
     void* yr;                         // [rows_cap][O] expert outputs, read by the owners of the tokens
     const int32_t* d_local_off;       // [per+1] received rows grouped by local expert
-    const int32_t* d_tile_prefix;     // [per+1]
+    const int32_t* d_tile_prefix;     // [per+1] for EpConfig.tile_m rows per tile
+    const int32_t* d_tile_prefix_alt; // [per+1] for EpConfig.tile_m_alt rows per tile (0 = none)
     void* const* d_expert_dst;        // [E] where this rank's rows for expert e start (a peer's xr)
     const void* const* d_expert_src;  // [E] where their outputs start (a peer's yr)
 };

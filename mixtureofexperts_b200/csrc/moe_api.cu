@@ -4,6 +4,7 @@
 // that replaces (moe::MoELayer)(x; training) (src/core/moe_layer.jl:107-156) and
 // cuda_moe_forward! (src/cuda/layer.jl:3-32).  No CPU fallback exists in this file: every
 // compute entry point fails with MOE_ERR_CUDA when the device is unusable.
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -156,6 +157,9 @@ int validate_config(const moe_config_t& c) {
     if (c.compute_dtype == MOE_DTYPE_BF16 && (c.input_dim % 8 || c.hidden_dim % 8))
         return fail(MOE_ERR_UNSUPPORTED,
                     "the BF16 tensor-core path needs input_dim and hidden_dim to be multiples of 8");
+    if (c.drop_tokens && c.shared_mode == MOE_SHARED_LAYER_BLEND)
+        return fail(MOE_ERR_INVALID, "drop_tokens does not apply to num_shared_experts > 0 (forward_with_shared_experts)");
+    if (c.drop_tokens && !(c.capacity_factor > 0.f)) return fail(MOE_ERR_INVALID, "capacity_factor must be positive");
     return MOE_OK;
 }
 
@@ -248,8 +252,18 @@ int check_ready(moe_layer* L) {
 }
 
 // The grouped GEMM pair on `rows_cap` rows described by (expert_offset, tile_prefix).
+// CTA-pair tiles (256 rows) pay off when rounding every expert up to a multiple of 256 rows costs
+// little: on average at least 2048 rows per expert.  MOE_B200_PAIR=0/1 forces the choice.
+int pick_tile_m(const moe_layer* L, int64_t rows, int n_experts) {
+    if (L->cfg.compute_dtype != MOE_DTYPE_BF16) return F32_TILE_M;
+    const char* ev = getenv("MOE_B200_PAIR");   // read per call: tests switch it at run time
+    const int env_pair = ev ? atoi(ev) : -1;
+    const bool pair = env_pair >= 0 ? env_pair != 0 : rows >= 2048LL * n_experts;
+    return pair ? TC_PAIR_TILE_M : TC_TILE_M;
+}
+
 int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const int32_t* expert_offset,
-                const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base) {
+                const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base, int tile_m) {
     const moe_config_t& c = L->cfg;
     GroupGemmParams g;
     g.E = n_experts;
@@ -258,7 +272,7 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.tile_prefix = tile_prefix;
     g.status = L->status;
     const bool tc = c.compute_dtype == MOE_DTYPE_BF16;
-    const int tile_m = tc ? TC_TILE_M : F32_TILE_M;
+    const bool pair = tc && tile_m == TC_PAIR_TILE_M;
     const int64_t max_mtiles64 = (rows + tile_m - 1) / tile_m + n_experts;
     if (max_mtiles64 > 0x7fffffff / 256) return fail(MOE_ERR_UNSUPPORTED, "too many row tiles");
     const int max_mtiles = (int)max_mtiles64;
@@ -270,7 +284,8 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.C = h_buf;
     g.N = c.hidden_dim;
     g.K = c.input_dim;
-    if (tc) n = launch_group_gemm_tc(L->plan, 1, g, max_mtiles * ((c.hidden_dim + 127) / 128), L->num_sms, s);
+    if (pair) n = launch_group_gemm_tc2(L->plan, 1, g, max_mtiles * ((c.hidden_dim + 127) / 128), L->num_sms, s);
+    else if (tc) n = launch_group_gemm_tc(L->plan, 1, g, max_mtiles * ((c.hidden_dim + 127) / 128), L->num_sms, s);
     else n = launch_group_gemm_f32(g, 1, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 1 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
@@ -282,7 +297,8 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.C = y_buf;
     g.N = c.output_dim;
     g.K = c.hidden_dim;
-    if (tc) n = launch_group_gemm_tc(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
+    if (pair) n = launch_group_gemm_tc2(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
+    else if (tc) n = launch_group_gemm_tc(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
     else n = launch_group_gemm_f32(g, 2, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 2 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
@@ -362,8 +378,13 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     sp.k_tot = L->k_tot;
     sp.shared_mode = c.shared_mode;
     sp.num_cta = num_cta;
-    sp.tile_m = c.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M;
+    const int tile_m_local = pick_tile_m(L, T * L->k_tot, L->E);   // non-expert-parallel GEMMs
+    sp.tile_m = tile_m_local;
     sp.training = training;
+    // capacity = ceil(Int, capacity_factor * T / E), evaluated in Float32 like the reference (moe_layer.jl:223)
+    const int capacity = (c.drop_tokens && training) ? (int)ceilf(c.capacity_factor * (float)T / (float)L->E) : -1;
+    if (capacity >= 0 && L->ep) return fail(MOE_ERR_UNSUPPORTED, "drop_tokens with expert parallelism is not implemented");
+    sp.capacity = capacity;
     sp.alpha = c.balance_alpha;
     sp.z_weight = c.z_loss_weight;
     sp.cta_counts = L->cta_counts;
@@ -398,8 +419,15 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     pp.status = L->status;
     pp.P_cap = L->P_cap;
     pp.expert_dst = nullptr;
+    pp.capacity = capacity;
+    pp.index_base = c.index_base;
+    pp.idx_rw = L->idx;
+    pp.gate_rw = L->gate;
+    pp.u_idx = opt->indices;
+    pp.u_gate = opt->gates;
     const bool peer = L->ep && ep_peer_mode(L->ep);
     EpPlan plan;
+    const int ep_tile_m = L->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M;
     if (peer) {
         if ((rc = ep_prepare(L->ep, L->expert_count, s, &plan, g_err, sizeof(g_err)))) return rc;
         pp.expert_dst = plan.d_expert_dst;
@@ -413,7 +441,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     stage_mark(L, 3, s);
 
     if (!L->ep) {
-        if ((rc = run_experts(L, L->xp, L->h, L->y, L->expert_offset, L->tile_prefix, T * L->k_tot, L->E, s, 4)))
+        if ((rc = run_experts(L, L->xp, L->h, L->y, L->expert_offset, L->tile_prefix, T * L->k_tot, L->E, s, 4, tile_m_local)))
             return rc;
     } else if (peer) {
         // every rank's permute kernel has written its rows into the owners' buffers once the
@@ -421,8 +449,11 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
         if ((rc = ep_sums_barrier(L->ep, s, g_err, sizeof(g_err)))) return rc;
         ep_mark(L->ep, 1, s);
         if ((rc = ensure_plan(L, plan.xr, plan.hr, plan.rows_cap))) return rc;
-        if ((rc = run_experts(L, plan.xr, plan.hr, plan.yr, plan.d_local_off, plan.d_tile_prefix, plan.rows,
-                              L->e_hi - L->e_lo, s, 4)))
+        const int n_local = L->e_hi - L->e_lo;
+        const bool pair = plan.d_tile_prefix_alt && pick_tile_m(L, plan.rows, n_local) == TC_PAIR_TILE_M;
+        if ((rc = run_experts(L, plan.xr, plan.hr, plan.yr, plan.d_local_off,
+                              pair ? plan.d_tile_prefix_alt : plan.d_tile_prefix, plan.rows, n_local, s, 4,
+                              pair ? TC_PAIR_TILE_M : ep_tile_m)))
             return rc;
         ep_mark(L->ep, 2, s);
         // all ranks' outputs are complete before anybody's combine kernel reads them
@@ -446,7 +477,8 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
                 moe_layer* M = reinterpret_cast<moe_layer*>(self);
                 int rc2 = ensure_plan(M, a_in, h_buf, cap_rows);
                 if (rc2) return rc2;
-                return run_experts(M, a_in, h_buf, y_buf, eo, tp, rows, n_exp, st, 4);
+                return run_experts(M, a_in, h_buf, y_buf, eo, tp, rows, n_exp, st, 4,
+                                   M->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M);
             },
             L, &ep_launches, g_err, sizeof(g_err));
         L->launches += ep_launches;
@@ -706,7 +738,8 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     // while chunk c computes.  Tokens are independent, so outputs do not change; loss, entropy
     // and counts are finished from the statistics summed over the chunks.
     int nchunks = 1;
-    if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192) {
+    // (not with the capacity constraint, whose capacity and first-come order span the whole batch)
+    if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192 && !(L->cfg.drop_tokens && training)) {
         static int env_chunks = -1;
         if (env_chunks < 0) {
             const char* e = getenv("MOE_B200_HOST_CHUNKS");
@@ -905,6 +938,7 @@ int moe_ep_init(moe_layer_t* L, const void* id128, int rank, int world) {
     ec.O = L->cfg.output_dim;
     ec.elt = (int)dtype_size(L->cfg.compute_dtype);
     ec.tile_m = L->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M;
+    ec.tile_m_alt = L->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_PAIR_TILE_M : 0;
     ec.alpha = L->cfg.balance_alpha;
     ec.z_weight = L->cfg.z_loss_weight;
     const int rc = ep_create(&L->ep, ec, id128, g_err, sizeof(g_err));

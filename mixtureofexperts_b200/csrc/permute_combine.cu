@@ -98,8 +98,8 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
     const int ntok = (int)min((int64_t)p.tokens_per_cta, p.T - tok0);
     const int npairs = ntok * p.k_tot;
 
-    for (int e = threadIdx.x; e < p.E; e += PERM_THREADS)
-        s_base[e] = p.expert_offset[e] + p.cta_base[(size_t)blockIdx.x * p.E + e];
+    // s_base[e]: rank, inside expert e, of the first pair of this tile (pairs of earlier tiles)
+    for (int e = threadIdx.x; e < p.E; e += PERM_THREADS) s_base[e] = p.cta_base[(size_t)blockIdx.x * p.E + e];
     __syncthreads();
 
     if (warp == 0) {
@@ -111,14 +111,17 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
             const unsigned m = __match_any_sync(0xffffffffu, e);
             const int rank = __popc(m & ((1u << lane) - 1u));
             int pos = -1;
+            bool dropped = false;
             if (act && e >= 0 && e < p.E) {
-                pos = s_base[e] + rank;
+                const int r = s_base[e] + rank;                      // rank inside the expert, token order
+                dropped = p.capacity >= 0 && r >= p.capacity;        // first come, first served
+                if (!dropped) pos = p.expert_offset[e] + r;
             }
             __syncwarp();
             if (act && e >= 0 && e < p.E && rank == 0) s_base[e] += __popc(m);
             __syncwarp();
             if (act) {
-                if (pos < 0 || (int64_t)pos >= p.P_cap) {
+                if (!dropped && (pos < 0 || (int64_t)pos >= p.P_cap)) {
                     if (p.status) atomicCAS(p.status, DEV_OK, DEV_BAD_INDEX);
                     pos = -1;
                 }
@@ -130,6 +133,25 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
         }
     }
     __syncthreads();
+    if (p.capacity >= 0) {
+        // apply_capacity_constraint (src/core/moe_layer.jl:239-244): dropped slots get id 0 and gate 0,
+        // then the token's gates are divided by their sum (if positive)
+        for (int tl = threadIdx.x; tl < ntok; tl += PERM_THREADS) {
+            const int64_t base = (tok0 + tl) * p.k_tot;
+            float sum = 0.f;
+            for (int j = 0; j < p.k_tot; ++j)
+                if (s_pos[tl * p.k_tot + j] >= 0) sum += p.gate_rw[base + j];
+            for (int j = 0; j < p.k_tot; ++j) {
+                const bool kept = s_pos[tl * p.k_tot + j] >= 0;
+                float g = kept ? p.gate_rw[base + j] : 0.f;
+                if (sum > 0.f) g = g / sum;
+                p.gate_rw[base + j] = g;
+                if (!kept) p.idx_rw[base + j] = -1;
+                if (p.u_gate) p.u_gate[base + j] = g;
+                if (p.u_idx && !kept) p.u_idx[base + j] = p.index_base - 1;
+            }
+        }
+    }
 
     const XT* x = reinterpret_cast<const XT*>(p.x);
     PT* xp = reinterpret_cast<PT*>(p.xp);

@@ -147,6 +147,7 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
     sp.num_cta = (int)num_cta64;
     sp.tile_m = TC_TILE_M;
     sp.training = training;
+    sp.capacity = -1;
     sp.alpha = balance_alpha;
     sp.z_weight = z_loss_weight;
     sp.cta_counts = cta_counts;

@@ -40,7 +40,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_loss_kernel(const ScanParam
             if (c < p.num_cta) p.cta_counts[(size_t)c * p.E + e] = run + inc - v;
             run += __shfl_sync(0xffffffffu, inc, 31);
         }
-        if (lane == 0) s_count[e] = run;
+        // with a capacity constraint an expert keeps its first `capacity` pairs (token order)
+        if (lane == 0) s_count[e] = (p.capacity >= 0 && run > p.capacity) ? p.capacity : run;
     }
     // per-expert probability sums (and the lse^2 sum in the last column): lanes stride the
     // CTAs, then a shuffle tree -- a fixed association order

@@ -170,8 +170,6 @@ class MoELayer:
             raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "only expert_type='gated' (GatedExpert) is accelerated")
         if config.use_cur:
             raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "CUR experts are not accelerated")
-        if config.drop_tokens:
-            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "drop_tokens (capacity constraint) is not accelerated")
         kind, k, gate_shared = gate_kind_of(config.gate_type)
         if gate_shared and config.num_shared_experts:
             raise _lib.MoEError(_lib.ERR_INVALID, "use either SharedExpertGating or num_shared_experts, not both")
@@ -191,7 +189,8 @@ class MoELayer:
             activation=activation_enum(config.activation),
             compute_dtype={"f32": _lib.DTYPE_F32, "bf16": _lib.DTYPE_BF16}[compute_dtype],
             shared_mode=shared_mode, balance_alpha=float(alpha), z_loss_weight=float(config.z_loss_weight),
-            index_base=1, bias_gates_only=1 if isinstance(self.balance_loss, AuxiliaryFreeLoss) else 0)
+            index_base=1, bias_gates_only=1 if isinstance(self.balance_loss, AuxiliaryFreeLoss) else 0,
+            capacity_factor=float(config.capacity_factor), drop_tokens=int(bool(config.drop_tokens)))
         _lib.check(_lib.lib.moe_layer_create(C.byref(self._cfg), self.device, C.byref(self._handle)))
         kt, ep, er = C.c_int32(), C.c_int32(), C.c_int32()
         _lib.check(_lib.lib.moe_layer_dims(self._handle, C.byref(kt), C.byref(ep), C.byref(er)))

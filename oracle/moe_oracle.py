@@ -281,7 +281,8 @@ def apply_capacity_constraint(indices: np.ndarray, gates: np.ndarray, capacity_f
     indices = indices.copy()
     gates = gates.copy()
     T, k = indices.shape
-    capacity = math.ceil(float(np.float32(capacity_factor)) * T / num_experts)
+    # Float32 * Int / Int evaluates in Float32 in Julia
+    capacity = math.ceil(float(np.float32(capacity_factor) * np.float32(T) / np.float32(num_experts)))
     counts = np.zeros(num_experts + 1, dtype=np.int64)
     for j in range(T):
         for s in range(k):

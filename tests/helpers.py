@@ -33,7 +33,8 @@ def device_gate(kind, k, S=0, E=None):
 
 
 def make_device_layer(weights: orc.MoEWeights, *, D, H, O, gate, activation="silu", alpha=0.01, z=0.001,
-                      compute_dtype="f32", num_shared_experts=0, balance_loss=None, router_bias=None, device=0):
+                      compute_dtype="f32", num_shared_experts=0, balance_loss=None, router_bias=None, device=0,
+                      **config_extra):
     """A MoELayer of the product package holding exactly the oracle's weights."""
     import mixtureofexperts_b200 as m
 
@@ -41,7 +42,7 @@ def make_device_layer(weights: orc.MoEWeights, *, D, H, O, gate, activation="sil
     cfg = m.create_moe_config(num_experts=len(weights.experts), expert_type="gated", input_dim=D, hidden_dim=H,
                               output_dim=O, activation=act, gate_type=gate,
                               balance_loss=balance_loss or m.SwitchTransformerLoss(alpha), z_loss_weight=z,
-                              num_shared_experts=num_shared_experts)
+                              num_shared_experts=num_shared_experts, **config_extra)
     experts = []
     for e in weights.experts:
         ex = m.GatedExpert.__new__(m.GatedExpert)

@@ -171,6 +171,38 @@ def test_router_bias_skews_routing_like_config4():
     layer.close()
 
 
+@pytest.mark.parametrize("T,E,k,cf,host", [(200, 8, 2, 1.25, False), (64, 4, 2, 0.5, True), (8300, 8, 2, 1.0, True),
+                                             (333, 10, 3, 0.75, False)])
+def test_capacity_constraint_drops_late_tokens(T, E, k, cf, host):
+    """drop_tokens && training: apply_capacity_constraint (src/core/moe_layer.jl:221-248) - first come,
+    first served in token order, dropped slots get id 0 / gate 0, gates renormalised per token."""
+    D, H, O = 64, 96, 48
+    x, w = orc.make_layer_inputs(400 + T, T, D, H, O, E, init="normal", std=0.25)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(k), balance_alpha=0.01, z_loss_weight=0.001, drop_tokens=True,
+                        capacity_factor=cf)
+    o_out, o_loss, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+    assert (aux["indices"] == 0).any()                      # the case does drop something
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=device_gate("topk", k), drop_tokens=True, capacity_factor=cf)
+    xin = np.asfortranarray(x.T) if host else torch.from_numpy(x).cuda().t()
+    out, loss, stats, routing = layer(xin, training=True, return_stats=True, return_routing=True)
+    if not host:
+        out, loss = out.cpu().numpy(), float(loss.item())
+        routing = {k_: v.cpu().numpy() for k_, v in routing.items()}
+    assert np.array_equal(routing["indices"].T, aux["indices"])
+    assert rel_inf(routing["gates"].T, aux["gates"]) < F32_TOL
+    assert rel_inf(out.T, o_out) < F32_TOL
+    assert abs(float(loss) - float(o_loss)) < F32_TOL * abs(float(o_loss))
+    assert np.array_equal(stats["tokens_per_expert"], aux["stats"]["tokens_per_expert"])
+    # inference mode ignores the constraint
+    o2, _, aux2 = orc.moe_layer_forward(cfg, w, x, training=False)
+    out2, _, rt2 = layer(xin, training=False, return_routing=True)
+    out2 = out2 if host else out2.cpu().numpy()
+    idx2 = rt2["indices"] if host else rt2["indices"].cpu().numpy()
+    assert np.array_equal(idx2.T, aux2["indices"]) and rel_inf(out2.T, o2) < F32_TOL
+    layer.close()
+
+
 def test_empty_batch():
     x, w = orc.make_layer_inputs(1, 1, 64, 96, 64, 4, init="normal", std=0.25)
     layer = make_device_layer(w, D=64, H=96, O=64, gate=device_gate("topk", 2))
@@ -274,10 +306,20 @@ def test_exact_ties_go_to_the_lowest_index():
     (300, 4, 1, 136, 200, 104),       # D, H, O not multiples of the 64/128/256 tile edges
     (257, 66, 6, 128, 256, 128),      # many small experts, some empty
     (1, 8, 2, 128, 256, 128),         # a single token
+    (4500, 2, 1, 128, 256, 128),      # >= 2048 rows per expert: the CTA-pair (cta_group::2) kernel
 ])
 def test_bf16_tensor_core_path(T, E, k, D, H, O):
     err = run_case(T, D, H, O, E, "topk", k, seed=T + E, compute="bf16", std=0.05)
     assert err < BF16_TOL
+
+
+@pytest.mark.parametrize("pair", ["0", "1"])
+def test_bf16_both_tensor_core_kernels_on_ragged_experts(pair, monkeypatch):
+    """MOE_B200_PAIR forces the single-CTA (128-row tiles) or the CTA-pair kernel (256-row tiles)
+    on a shape with empty experts, partial last tiles and widths off the tile edges."""
+    monkeypatch.setenv("MOE_B200_PAIR", pair)
+    assert run_case(777, 136, 200, 104, 10, "topk", 3, seed=91, compute="bf16", std=0.05) < BF16_TOL
+    assert run_case(3, 128, 256, 128, 66, "topk", 2, seed=92, compute="bf16", std=0.05) < BF16_TOL
 
 
 def test_bf16_shared_gating_and_f32_input():
