@@ -23,7 +23,7 @@ enum : int32_t {
 
 constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
-constexpr int ROUTER_MAX_WARPS = 12;    // largest router CTA: 384 threads
+constexpr int ROUTER_MAX_WARPS = 18;    // largest router CTA: 576 threads
 constexpr int ROUTER_TOKENS_PER_CTA = 64;
 constexpr int MAX_ROUTER_EXPERTS = 128; // upper bound on router rows
 constexpr int MAX_EXPERTS = 256;        // upper bound on experts per layer

@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 #include <cfloat>
+#include <cstdlib>
 #include <climits>
 
 namespace moe {

@@ -306,7 +306,7 @@ def test_exact_ties_go_to_the_lowest_index():
     (300, 4, 1, 136, 200, 104),       # D, H, O not multiples of the 64/128/256 tile edges
     (257, 66, 6, 128, 256, 128),      # many small experts, some empty
     (1, 8, 2, 128, 256, 128),         # a single token
-    (4500, 2, 1, 128, 256, 128),      # >= 2048 rows per expert: the CTA-pair (cta_group::2) kernel
+    (4500, 2, 1, 128, 256, 128),      # many m-tiles per expert
 ])
 def test_bf16_tensor_core_path(T, E, k, D, H, O):
     err = run_case(T, D, H, O, E, "topk", k, seed=T + E, compute="bf16", std=0.05)
