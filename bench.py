@@ -319,6 +319,7 @@ def main():
             stages[k_] = stages.get(k_, 0.0) + v / n_prof
     layer.set_profiling(0)
     loss_value = float(loss.item())
+    output_finite = bool(torch.isfinite(out).all().item())   # the timed steps produced real numbers
 
     # ---- end to end through the host entry point ---------------------------------------------
     e2e = None
@@ -349,13 +350,21 @@ def main():
         f_g1 = 2.0 * w["H"] * 2 * w["D"] * tokens_local_pairs * (w["k"] + w["S"])
         f_g2 = 2.0 * w["H"] * w["O"] * tokens_local_pairs * (w["k"] + w["S"])
         roof = None
+        # DRAM bytes of one group_gemm_tc_kernel<1> launch, from an ncu capture of this command at full
+        # size (dram__bytes_read.sum + dram__bytes_write.sum, 1 pass; profiles/c3_dram_bytes.md).
+        # Algorithmic bytes of the launch: weights 1.879 GB + rows 0.268 GB + h 0.940 GB = 3.087 GB.
+        traffic, traffic_note = None, "no ncu capture for this workload size"
+        if name == "c3" and args.tokens == 0 and args.experts == 0:
+            traffic = 2889976576 + 925794304
+            traffic_note = "ncu capture of this workload: 2.890 GB read + 0.926 GB written vs 3.087 GB algorithmic"
         if w["dtype"] == "bf16" and stages.get("gemm1", 0) > 0 and world == 1:
             ach = f_g1 / (stages["gemm1"] * 1e-3) / 1e12
             peak = peaks["bf16_tflops_sustained"]
             roof = {"bound": "tensor", "kernel": "group_gemm_tc_kernel<1> (x W1^T, x W3^T, act*up)",
                     "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                     "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (kernel timed inside a long step); burst {peaks['bf16_tflops']}",
-                    "traffic": None,
+                    "traffic": traffic, "traffic_unit": "bytes per launch",
+                    "traffic_note": traffic_note,
                     "gemm2_achieved": f_g2 / (stages["gemm2"] * 1e-3) / 1e12 if stages.get("gemm2", 0) > 0 else None,
                     "layer_frac": expert_flops(w, T) / (ms_step * 1e-3) / 1e12 / peak}
         elif w["dtype"] == "bf16" and world > 1:
@@ -387,9 +396,11 @@ def main():
                        "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world} (NCCL all-to-all)",
                        "training": True, "l2": "inputs (activations + expert weights) are larger than L2; no flush needed"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu,
-            "stage_ms": stages, "loss": loss_value, "device_status": status,
+            "stage_ms": stages, "loss": loss_value, "output_finite": output_finite, "device_status": status,
         }
         print(json.dumps(line), flush=True)
+        if not output_finite or status != 0:
+            raise SystemExit("bench: the layer produced non-finite output or a device status")
     layer.close()
     if world > 1:
         dist.barrier()

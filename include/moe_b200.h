@@ -121,8 +121,9 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out);
  * (src/cuda/utils.jl:4-15, src/amdgpu/utils.jl:62-105): copies and repacks the three
  * matrices of expert `expert` (0-based) into the handle; the caller's arrays may be freed
  * after return.  w1,w3: (H x D); w2: (O x H).  src_dtype MOE_DTYPE_*; layout MOE_LAYOUT_*;
- * src_is_device != 0 if the pointers are device pointers on the handle's device.
- * Synchronises the device before returning. */
+ * src_is_device != 0 if the pointers are device pointers on the handle's device; the call then
+ * first waits for all work queued on the device, so sources still being produced on any of the
+ * caller's streams are complete before they are read.  Synchronises before returning. */
 int moe_layer_set_expert(moe_layer_t*, int expert, const void* w1, const void* w2, const void* w3,
                          int src_dtype, int layout, int src_is_device);
 

@@ -633,6 +633,9 @@ int moe_layer_set_expert(moe_layer_t* L, int expert, const void* w1, const void*
     if (expert < L->e_lo || expert >= L->e_hi)
         return fail(MOE_ERR_INVALID, "expert %d is not held by this rank (it holds %d..%d)", expert, L->e_lo, L->e_hi - 1);
     CUDA_TRY(cudaSetDevice(L->device));
+    // Device sources may still be being written by work the caller queued on its own streams; the
+    // repack below runs on the handle's stream, which is not ordered after them.
+    if (src_is_device) CUDA_TRY(cudaDeviceSynchronize());
     int rc = ensure_weights(L);
     if (rc) return rc;
     const size_t D = L->cfg.input_dim, H = L->cfg.hidden_dim, O = L->cfg.output_dim;
@@ -666,6 +669,7 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     if (!L || !w) return fail(MOE_ERR_INVALID, "null argument");
     if (layout != MOE_LAYOUT_IN_CONTIG && layout != MOE_LAYOUT_OUT_CONTIG) return fail(MOE_ERR_INVALID, "unknown layout");
     CUDA_TRY(cudaSetDevice(L->device));
+    if (src_is_device) CUDA_TRY(cudaDeviceSynchronize());   // see moe_layer_set_expert
     const size_t bytes = (size_t)L->E_router * L->cfg.input_dim * sizeof(float);
     const void* src = w;
     int rc;

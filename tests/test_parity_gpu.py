@@ -252,6 +252,32 @@ def test_chunked_host_call_equals_device_call(gate_kind, E, S, k):
     layer.close()
 
 
+def test_device_resident_weights_still_being_produced():
+    """Weights handed over as CUDA tensors right after the kernels that produce them were queued:
+    the upload must wait for them (it runs on the handle's own stream)."""
+    import mixtureofexperts_b200 as m
+
+    T, D, H, O, E = 256, 1024, 2048, 1024, 4
+    g = torch.Generator(device="cuda").manual_seed(5)
+    big = torch.randn((64, 1024, 1024), device="cuda", generator=g)          # keeps the stream busy for a while
+    for _ in range(4):
+        big = big @ big.transpose(1, 2) * 1e-3
+    ws = [[torch.randn(s, device="cuda", generator=g) * 0.05 for s in ((H, D), (O, H), (H, D))] for _ in range(E)]
+    router = torch.randn((E, D), device="cuda", generator=g) * 0.05
+    weights = orc.MoEWeights(router=router, experts=[orc.GatedExpertWeights(w1=a, w2=b, w3=c) for a, b, c in ws])
+    layer = make_device_layer(weights, D=D, H=H, O=O, gate=m.TopKGating(2), z=0.0)   # uploads device tensors at once
+    x = torch.randn((T, D), device="cuda", generator=g)
+    out, _ = layer(x.t(), training=False)
+    host = orc.MoEWeights(router=router.cpu().numpy(), experts=[
+        orc.GatedExpertWeights(w1=a.cpu().numpy(), w2=b.cpu().numpy(), w3=c.cpu().numpy()) for a, b, c in ws])
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(2), z_loss_weight=0.0)
+    o_out, _, _ = orc.moe_layer_forward(cfg, host, x.cpu().numpy(), training=False)
+    assert torch.isfinite(out).all()
+    assert rel_inf(out.cpu().numpy().T, o_out) < F32_TOL
+    layer.close()
+
+
 def test_token_permutation_equivariance():
     """Each token's output depends on that token only: permuting the batch permutes the output."""
     x, w = orc.make_layer_inputs(3, 500, 64, 96, 64, 8, init="normal", std=0.25)
