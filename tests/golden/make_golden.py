@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 # name -> (seed, T, D, H, O, E, gate spec, extra config)
 CASES = {
-    # BASELINE config 1: 8 GatedExperts (silu) 512/2048/512, TopKGating(2), SwitchTransformerLoss(0.01),
+    # the CPU-runnable benchmark configuration: 8 GatedExperts (silu) 512/2048/512, TopKGating(2), SwitchTransformerLoss(0.01),
     # input 512x32 N(0,1), Glorot-uniform weights, training=true
     "c1": dict(seed=1235, T=32, D=512, H=2048, O=512, E=8, gate=("topk", 2), z=0.001, init="glorot"),
     "c1_noz": dict(seed=1235, T=32, D=512, H=2048, O=512, E=8, gate=("topk", 2), z=0.0, init="glorot"),

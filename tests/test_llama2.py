@@ -100,7 +100,7 @@ def test_dense_host_plumbing_matches_oracle(lib_built):
 
 @pytest.mark.gpu
 def test_stories42m_shaped_model_matches_oracle():
-    """BASELINE config 2: dim 512, hidden 1376, 8 layers, 8 heads, vocab 32000, MoE at layers
+    """The stories42M-shaped benchmark configuration: dim 512, hidden 1376, 8 layers, 8 heads, vocab 32000, MoE at layers
     [2,4,6] with 8 experts, top-2, :perturb 0.01; 64 seeded token ids.  Final logits of all 64
     positions within 1e-4 relative (FP32 end to end through 8 layers; the MoE layer itself is
     held to 1e-5 elsewhere) and identical expert selections in every MoE layer."""

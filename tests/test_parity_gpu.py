@@ -72,7 +72,7 @@ def run_case(T, D, H, O, E, gate_kind, k, S=0, *, seed=0, activation="silu", com
     return rel_inf(out.T, o_out)
 
 
-# ---- golden fixtures (BASELINE config 1 and the small gate/shared-expert variants) -------------
+# ---- golden fixtures (the 8-expert 512/2048/512 benchmark configuration and the small gate/shared-expert variants) -------------
 
 @pytest.mark.parametrize("case", list(make_golden.CASES))
 @pytest.mark.parametrize("host", [False, True])
@@ -153,7 +153,7 @@ def test_aux_free_bias_selects_but_does_not_change_probs():
 
 
 def test_router_bias_skews_routing_like_config4():
-    """A per-expert logit bias N(0,1.5) that is part of the logits (BASELINE config 4's skew)."""
+    """A per-expert logit bias N(0,1.5) that is part of the logits (the skew of the DeepSeek-style benchmark configuration)."""
     T, D, H, O, E, S, k = 300, 64, 96, 64, 18, 2, 6
     x, w = orc.make_layer_inputs(12, T, D, H, O, E, init="normal", std=0.25)
     bias = np.concatenate([np.zeros(S), np.random.default_rng(4).normal(0, 1.5, E - S)]).astype(np.float32)
