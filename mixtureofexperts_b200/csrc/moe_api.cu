@@ -745,14 +745,12 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     // while chunk c computes.  Tokens are independent, so outputs do not change; loss, entropy
     // and counts are finished from the statistics summed over the chunks.
     int nchunks = 1;
+    int env_chunks = 0;   // MOE_B200_HOST_CHUNKS = n: n equal chunks (1 = off); unset: the default schedule
     // (not with the capacity constraint, whose capacity and first-come order span the whole batch)
     if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192 && !(L->cfg.drop_tokens && training)) {
-        static int env_chunks = -1;
-        if (env_chunks < 0) {
-            const char* e = getenv("MOE_B200_HOST_CHUNKS");
-            env_chunks = e ? atoi(e) : 0;
-        }
-        nchunks = env_chunks > 0 ? env_chunks : 4;
+        const char* e = getenv("MOE_B200_HOST_CHUNKS");
+        env_chunks = e ? atoi(e) : 0;
+        nchunks = env_chunks > 0 ? env_chunks : 5;
         if (nchunks > moe_layer::MAX_CHUNKS) nchunks = moe_layer::MAX_CHUNKS;
     }
     if (nchunks > 1) {
@@ -767,13 +765,30 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
             if ((rc = dev_alloc(&L->chunk_tpe_acc, (size_t)L->E))) return rc;
             if ((rc = dev_alloc(&L->chunk_tpe_tmp, (size_t)L->E))) return rc;
         }
-        const int64_t Tc = ((T + nchunks - 1) / nchunks + 63) / 64 * 64;
+        // Chunk boundaries (multiples of 64 tokens).  By default small first and last chunks: only the
+        // copy-in of the first and the copy-out of the last chunk are not hidden behind compute.
+        std::vector<int64_t> bounds;
+        bounds.push_back(0);
+        if (env_chunks > 0) {
+            const int64_t Tc = ((T + nchunks - 1) / nchunks + 63) / 64 * 64;
+            for (int64_t t = Tc; t < T; t += Tc) bounds.push_back(t);
+        } else {
+            static const int parts[] = {1, 5, 5, 4, 1};     // sixteenths of the batch
+            nchunks = 5;
+            int64_t acc16 = 0;
+            for (int i = 0; i < 4; ++i) {
+                acc16 += parts[i];
+                const int64_t t = (T * acc16 / 16 + 63) / 64 * 64;
+                if (t > bounds.back() && t < T) bounds.push_back(t);
+            }
+        }
+        bounds.push_back(T);
         const size_t xrow = (size_t)L->cfg.input_dim * dtype_size(x_dtype), orow = (size_t)L->cfg.output_dim * 4;
         CUDA_TRY(cudaMemsetAsync(L->chunk_acc, 0, sizeof(float) * nsum, s));
         CUDA_TRY(cudaMemsetAsync(L->chunk_tpe_acc, 0, sizeof(int64_t) * L->E, s));
-        int c = 0;
-        for (int64_t t0 = 0; t0 < T; t0 += Tc, ++c) {
-            const int64_t n = (T - t0 < Tc) ? T - t0 : Tc;
+        for (int c = 0; c + 1 < (int)bounds.size(); ++c) {
+            const int64_t t0 = bounds[c];
+            const int64_t n = bounds[c + 1] - t0;
             CUDA_TRY(cudaMemcpyAsync((char*)L->hx + t0 * xrow, (const char*)x + t0 * xrow, n * xrow,
                                      cudaMemcpyHostToDevice, L->s_in));
             CUDA_TRY(cudaEventRecord(L->ev_in[c], L->s_in));
