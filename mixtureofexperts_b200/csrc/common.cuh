@@ -139,7 +139,25 @@ struct GroupGemmParams {
     const int32_t* expert_offset; // [E+1]
     const int32_t* tile_prefix;   // [E+1]
     int32_t* status;
+    // Scattered output (expert-parallel peer mode, GEMM 2; else seg_dst == null): the rows of expert e
+    // form seg_per_expert consecutive segments, one per source rank; segment q starts at row
+    // seg_start[e*seg_per_expert + q] and its rows are stored at seg_dst[e*seg_per_expert + q]
+    // (a row-major [rows][N] block, possibly in another GPU's memory) instead of C.
+    const int32_t* seg_start;
+    void* const* seg_dst;
+    int seg_per_expert;
 };
+
+// Where row `row` of expert `e` of a grouped GEMM's output goes.
+template <typename T>
+__device__ __forceinline__ T* group_gemm_out_row(const GroupGemmParams& p, int e, int row) {
+    if (!p.seg_dst) return reinterpret_cast<T*>(p.C) + (size_t)row * p.N;
+    const int32_t* st = p.seg_start + (size_t)e * p.seg_per_expert;
+    int q = 0;
+    for (int i = 1; i < p.seg_per_expert; ++i)
+        if (st[i] <= row) q = i;           // last segment starting at or before the row (empty ones skipped)
+    return reinterpret_cast<T*>(p.seg_dst[(size_t)e * p.seg_per_expert + q]) + (size_t)(row - st[q]) * p.N;
+}
 
 // ---- launchers (each returns the number of kernels it launched, or <0 on a launch error) ---
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s);

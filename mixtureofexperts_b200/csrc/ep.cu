@@ -116,7 +116,13 @@ struct EpState {
     bool timed = false;
     // peer-memory mode
     bool peer_mode = true;
-    std::vector<void*> peer_xr, peer_yr;   // [world] mapped receive buffers (own entry = local pointer)
+    std::vector<void*> peer_xr, peer_yb;   // [world] mapped buffers of every rank (own entry = local pointer)
+    void* yb = nullptr;                    // [pairs_cap][O] outputs of this rank's pairs (written by the expert owners)
+    int64_t pairs_cap = 0;
+    int32_t* d_seg = nullptr;              // [per*world] segment starts
+    int32_t* h_seg = nullptr;              // pinned
+    void** d_segp = nullptr;               // [per*world] segment destinations
+    void** h_segp = nullptr;               // pinned
     unsigned char* d_ipc = nullptr;        // [world][2 handles] staging for the handle all-gather
     unsigned char* h_ipc = nullptr;        // pinned
     void** d_ptrs = nullptr;               // [2E] expert_dst, expert_src
@@ -188,11 +194,15 @@ int ep_create(EpState** out, const EpConfig& cfg, const void* id128, char* err, 
     const char* mode = getenv("MOE_B200_EP_MODE");
     ep->peer_mode = !(mode && strcmp(mode, "nccl") == 0);
     ep->peer_xr.assign(cfg.world, nullptr);
-    ep->peer_yr.assign(cfg.world, nullptr);
+    ep->peer_yb.assign(cfg.world, nullptr);
     const size_t ipc_bytes = (size_t)cfg.world * 2 * sizeof(cudaIpcMemHandle_t);
     ok = ok && cudaMalloc(&ep->d_ipc, ipc_bytes) == cudaSuccess && cudaMallocHost(&ep->h_ipc, ipc_bytes) == cudaSuccess &&
          cudaMalloc(&ep->d_ptrs, sizeof(void*) * 2 * cfg.E) == cudaSuccess &&
          cudaMallocHost(&ep->h_ptrs, sizeof(void*) * 2 * cfg.E) == cudaSuccess &&
+         cudaMalloc(&ep->d_seg, sizeof(int32_t) * ep->per * cfg.world) == cudaSuccess &&
+         cudaMallocHost(&ep->h_seg, sizeof(int32_t) * ep->per * cfg.world) == cudaSuccess &&
+         cudaMalloc(&ep->d_segp, sizeof(void*) * ep->per * cfg.world) == cudaSuccess &&
+         cudaMallocHost(&ep->h_segp, sizeof(void*) * ep->per * cfg.world) == cudaSuccess &&
          cudaMalloc(&ep->d_flag, sizeof(int32_t)) == cudaSuccess &&
          cudaMemset(ep->d_flag, 0, sizeof(int32_t)) == cudaSuccess;
     if (!ok) {
@@ -214,8 +224,13 @@ void ep_destroy(EpState* ep) {
     for (int r = 0; r < (int)ep->peer_xr.size(); ++r) {
         if (r == ep->cfg.rank) continue;
         if (ep->peer_xr[r]) cudaIpcCloseMemHandle(ep->peer_xr[r]);
-        if (ep->peer_yr[r]) cudaIpcCloseMemHandle(ep->peer_yr[r]);
+        if (ep->peer_yb[r]) cudaIpcCloseMemHandle(ep->peer_yb[r]);
     }
+    if (ep->yb) cudaFree(ep->yb);
+    if (ep->d_seg) cudaFree(ep->d_seg);
+    if (ep->h_seg) cudaFreeHost(ep->h_seg);
+    if (ep->d_segp) cudaFree(ep->d_segp);
+    if (ep->h_segp) cudaFreeHost(ep->h_segp);
     if (ep->xr) cudaFree(ep->xr);
     if (ep->hr) cudaFree(ep->hr);
     if (ep->yr) cudaFree(ep->yr);
@@ -365,33 +380,34 @@ int ep_exchange_and_run(EpState* ep, const EpCall& c, EpRunFn run, void* self, i
 // ---- peer-memory mode ------------------------------------------------------------------------
 
 bool ep_peer_mode(const EpState* ep) { return ep->peer_mode; }
+int ep_world(const EpState* ep) { return ep->cfg.world; }
 
 void ep_mark(EpState* ep, int i, cudaStream_t s) {
     cudaEventRecord(ep->ev[i], s);
     if (i == 3) ep->timed = true;
 }
 
-// Collective: every rank calls it with the same `cap` (derived from the all-gathered counts).
+// Collective: every rank calls it with the same capacities (derived from the all-gathered counts).
 // Order: drop the mappings of the peers' old buffers, allocate the new buffers, exchange their
 // IPC handles (which also tells us every rank has dropped its old mappings), free the old
 // buffers, map the peers' new ones.
-static int ep_grow_peer_buffers(EpState* ep, int64_t cap, cudaStream_t s, char* err, size_t errlen) {
+static int ep_grow_peer_buffers(EpState* ep, int64_t cap, int64_t pairs_cap, cudaStream_t s, char* err, size_t errlen) {
     const EpConfig& g = ep->cfg;
     const int W = g.world, me = g.rank;
     for (int r = 0; r < W; ++r) {
         if (r != me) {
             if (ep->peer_xr[r]) cudaIpcCloseMemHandle(ep->peer_xr[r]);
-            if (ep->peer_yr[r]) cudaIpcCloseMemHandle(ep->peer_yr[r]);
+            if (ep->peer_yb[r]) cudaIpcCloseMemHandle(ep->peer_yb[r]);
         }
-        ep->peer_xr[r] = ep->peer_yr[r] = nullptr;
+        ep->peer_xr[r] = ep->peer_yb[r] = nullptr;
     }
-    void *nxr = nullptr, *nhr = nullptr, *nyr = nullptr;
+    void *nxr = nullptr, *nhr = nullptr, *nyb = nullptr;
     EP_CUDA(cudaMalloc(&nxr, (size_t)cap * g.D * g.elt));
     EP_CUDA(cudaMalloc(&nhr, (size_t)cap * g.H * g.elt));
-    EP_CUDA(cudaMalloc(&nyr, (size_t)cap * g.O * g.elt));
+    EP_CUDA(cudaMalloc(&nyb, (size_t)pairs_cap * g.O * g.elt));
     cudaIpcMemHandle_t mine[2];
     EP_CUDA(cudaIpcGetMemHandle(&mine[0], nxr));
-    EP_CUDA(cudaIpcGetMemHandle(&mine[1], nyr));
+    EP_CUDA(cudaIpcGetMemHandle(&mine[1], nyb));
     const size_t hb = 2 * sizeof(cudaIpcMemHandle_t);
     EP_CUDA(cudaMemcpyAsync(ep->d_ipc + (size_t)me * hb, mine, hb, cudaMemcpyHostToDevice, s));
     EP_NCCL(g_nccl.AllGather(ep->d_ipc + (size_t)me * hb, ep->d_ipc, hb, ncclChar, ep->comm, s));
@@ -399,21 +415,22 @@ static int ep_grow_peer_buffers(EpState* ep, int64_t cap, cudaStream_t s, char* 
     EP_CUDA(cudaStreamSynchronize(s));
     if (ep->xr) cudaFree(ep->xr);
     if (ep->hr) cudaFree(ep->hr);
-    if (ep->yr) cudaFree(ep->yr);
+    if (ep->yb) cudaFree(ep->yb);
     ep->xr = nxr;
     ep->hr = nhr;
-    ep->yr = nyr;
+    ep->yb = nyb;
     ep->rows_cap = cap;
+    ep->pairs_cap = pairs_cap;
     for (int r = 0; r < W; ++r) {
         if (r == me) {
             ep->peer_xr[r] = nxr;
-            ep->peer_yr[r] = nyr;
+            ep->peer_yb[r] = nyb;
             continue;
         }
         cudaIpcMemHandle_t h[2];
         memcpy(h, ep->h_ipc + (size_t)r * hb, hb);
         EP_CUDA(cudaIpcOpenMemHandle(&ep->peer_xr[r], h[0], cudaIpcMemLazyEnablePeerAccess));
-        EP_CUDA(cudaIpcOpenMemHandle(&ep->peer_yr[r], h[1], cudaIpcMemLazyEnablePeerAccess));
+        EP_CUDA(cudaIpcOpenMemHandle(&ep->peer_yb[r], h[1], cudaIpcMemLazyEnablePeerAccess));
     }
     return MOE_OK;
 }
@@ -437,8 +454,16 @@ int ep_prepare(EpState* ep, const int32_t* d_expert_count, cudaStream_t s, EpPla
         if (rows_r > need) need = rows_r;
     }
     if (need > 0x7fffffffLL) return set_err(err, errlen, MOE_ERR_UNSUPPORTED, "more than 2^31-1 received rows");
-    if (need > ep->rows_cap || !ep->xr) {
-        const int rc = ep_grow_peer_buffers(ep, need + need / 4 + g.tile_m, s, err, errlen);
+    int64_t need_pairs = 0;                           // largest number of pairs any rank sends
+    for (int r = 0; r < W; ++r) {
+        int64_t pr = 0;
+        for (int e = 0; e < E; ++e) pr += cnt[(size_t)r * E + e];
+        if (pr > need_pairs) need_pairs = pr;
+    }
+    if (need > ep->rows_cap || need_pairs > ep->pairs_cap || !ep->xr) {
+        const int64_t cap = need > ep->rows_cap ? need + need / 4 + g.tile_m : ep->rows_cap;
+        const int64_t pcap = need_pairs > ep->pairs_cap ? need_pairs + need_pairs / 4 + 64 : ep->pairs_cap;
+        const int rc = ep_grow_peer_buffers(ep, cap, pcap, s, err, errlen);
         if (rc) return rc;
     }
 
@@ -458,7 +483,7 @@ int ep_prepare(EpState* ep, const int32_t* d_expert_count, cudaStream_t s, EpPla
     }
     EP_CUDA(cudaMemcpyAsync(ep->d_tables, ep->h_tables, sizeof(int32_t) * 3 * (per + 1), cudaMemcpyHostToDevice, s));
 
-    // where my rows for expert e start inside its owner's buffers:
+    // where my rows for expert e start inside its owner's receive buffer:
     //   (rows of the owner's earlier local experts) + (rows of expert e from lower ranks)
     for (int r = 0; r < W; ++r) {
         int64_t base = 0;
@@ -466,24 +491,37 @@ int ep_prepare(EpState* ep, const int32_t* d_expert_count, cudaStream_t s, EpPla
             const int e = r * per + el;
             int64_t before_me = 0;
             for (int q = 0; q < me; ++q) before_me += cnt[(size_t)q * E + e];
-            const int64_t row = base + before_me;
-            ep->h_ptrs[e] = reinterpret_cast<char*>(ep->peer_xr[r]) + (size_t)row * g.D * g.elt;
-            ep->h_ptrs[E + e] = reinterpret_cast<char*>(ep->peer_yr[r]) + (size_t)row * g.O * g.elt;
+            ep->h_ptrs[e] = reinterpret_cast<char*>(ep->peer_xr[r]) + (size_t)(base + before_me) * g.D * g.elt;
             base += expert_rows[e];
         }
     }
-    EP_CUDA(cudaMemcpyAsync(ep->d_ptrs, ep->h_ptrs, sizeof(void*) * 2 * E, cudaMemcpyHostToDevice, s));
+    EP_CUDA(cudaMemcpyAsync(ep->d_ptrs, ep->h_ptrs, sizeof(void*) * E, cudaMemcpyHostToDevice, s));
+    // where the outputs of the rows I received go: segment (el, r) = rank r's pairs for my expert el,
+    // stored at rank r's yb from its send offset of that expert (its pair_pos order)
+    for (int r = 0; r < W; ++r) {
+        int64_t send_off_r = 0;                       // rank r's send offset of expert e, e ascending
+        for (int e = 0; e < me * per; ++e) send_off_r += cnt[(size_t)r * E + e];
+        for (int el = 0; el < per; ++el) {
+            const int e = me * per + el;
+            ep->h_seg[(size_t)el * W + r] = (int32_t)recv_off[(size_t)el * W + r];
+            ep->h_segp[(size_t)el * W + r] = reinterpret_cast<char*>(ep->peer_yb[r]) + (size_t)send_off_r * g.O * g.elt;
+            send_off_r += cnt[(size_t)r * E + e];
+        }
+    }
+    EP_CUDA(cudaMemcpyAsync(ep->d_seg, ep->h_seg, sizeof(int32_t) * per * W, cudaMemcpyHostToDevice, s));
+    EP_CUDA(cudaMemcpyAsync(ep->d_segp, ep->h_segp, sizeof(void*) * per * W, cudaMemcpyHostToDevice, s));
 
     plan->rows = rows;
     plan->rows_cap = ep->rows_cap;
     plan->xr = ep->xr;
     plan->hr = ep->hr;
-    plan->yr = ep->yr;
+    plan->yb = ep->yb;
+    plan->d_seg_start = ep->d_seg;
+    plan->d_seg_dst = ep->d_segp;
     plan->d_local_off = ep->d_tables;
     plan->d_tile_prefix = ep->d_tables + (per + 1);
     plan->d_tile_prefix_alt = g.tile_m_alt > 0 ? ep->d_tables + 2 * (per + 1) : nullptr;
     plan->d_expert_dst = ep->d_ptrs;
-    plan->d_expert_src = const_cast<const void* const*>(ep->d_ptrs + E);
     return MOE_OK;
 }
 

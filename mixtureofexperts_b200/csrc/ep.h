@@ -57,22 +57,26 @@ float ep_last_exchange_ms(EpState*);
 
 // ---- peer-memory mode (default): rows cross NVLink inside the permute and combine kernels ----
 // Every rank exports its receive buffers with CUDA IPC; the permute kernel stores each row
-// straight into the owner GPU's buffer and the combine kernel loads expert outputs from the
-// owner's buffer.  NCCL only carries the small control collectives (counts, the loss sums that
+// straight into the owner GPU's buffer, and the GEMM 2 epilogue stores every output row straight into
+// the buffer of the GPU that owns the token, tile by tile while the GEMM runs; the combine kernel then
+// reads local memory only.  NCCL only carries the small control collectives (counts, the loss sums that
 // double as a barrier, one more barrier).  MOE_B200_EP_MODE=nccl selects the send/recv path above.
 struct EpPlan {
     int64_t rows;                     // rows this rank received
     int64_t rows_cap;                 // capacity (rows) of the receive buffers
     void* xr;                         // [rows_cap][D] received rows (this GPU's memory)
     void* hr;                         // [rows_cap][H]
-    void* yr;                         // [rows_cap][O] expert outputs, read by the owners of the tokens
+    void* yb;                         // [pairs_cap][O] outputs of THIS rank's pairs, in its send (pair_pos) order;
+                                      // written by the owners of the experts from their GEMM 2 epilogues
+    const int32_t* d_seg_start;       // [per][world] first received row of the pairs of source rank s, expert el
+    void* const* d_seg_dst;           // [per][world] where that segment's outputs go (rank s's yb)
     const int32_t* d_local_off;       // [per+1] received rows grouped by local expert
     const int32_t* d_tile_prefix;     // [per+1] for EpConfig.tile_m rows per tile
     const int32_t* d_tile_prefix_alt; // [per+1] for EpConfig.tile_m_alt rows per tile (0 = none)
     void* const* d_expert_dst;        // [E] where this rank's rows for expert e start (a peer's xr)
-    const void* const* d_expert_src;  // [E] where their outputs start (a peer's yr)
 };
 bool ep_peer_mode(const EpState*);
+int ep_world(const EpState*);
 // all-gather of the counts, host sync, layout, (collective) buffer growth, pointer tables
 int ep_prepare(EpState*, const int32_t* d_expert_count, cudaStream_t s, EpPlan* plan, char* err, size_t errlen);
 // all-reduce of the loss sums; completes only when every rank has issued it, i.e. after every

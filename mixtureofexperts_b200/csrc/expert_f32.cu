@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemm
             float v;
             if (MODE == 1) v = apply_act(p.activation, acc[0][r][i]) * acc[NB - 1][r][i];
             else v = acc[0][r][i];
-            C[(size_t)row * p.N + n] = v;
+            group_gemm_out_row<float>(p, e, row)[n] = v;
         }
     }
 }
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(SK_THREADS) group_gemm_f32_skinny_kernel(const
                     if (row < row_end && n < p.N) {
                         const float v = (MODE == 1) ? apply_act(p.activation, acc[0][c][r]) * acc[NB - 1][c][r]
                                                     : acc[0][c][r];
-                        C[(size_t)row * p.N + n] = v;
+                        group_gemm_out_row<float>(p, e, row)[n] = v;
                     }
                 }
             }

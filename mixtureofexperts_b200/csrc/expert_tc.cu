@@ -194,7 +194,7 @@ group_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             tc_fence_after();
             const int row = t.row0 + row_in_tile;
             const bool row_ok = row < t.row_end;
-            __nv_bfloat16* dst_row = C + (size_t)row * p.N;
+            __nv_bfloat16* dst_row = row_ok ? group_gemm_out_row<__nv_bfloat16>(p, t.e, row) : C;
             const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(as * BN);
             const int col_base = t.n_idx * TILE_N_OUT;
             if (MODE == 1) {

@@ -266,7 +266,8 @@ int pick_tile_m(const moe_layer* L, int64_t rows, int n_experts) {
 }
 
 int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const int32_t* expert_offset,
-                const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base, int tile_m) {
+                const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base, int tile_m,
+                const int32_t* seg_start = nullptr, void* const* seg_dst = nullptr, int seg_per_expert = 0) {
     const moe_config_t& c = L->cfg;
     GroupGemmParams g;
     g.E = n_experts;
@@ -274,6 +275,9 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.expert_offset = expert_offset;
     g.tile_prefix = tile_prefix;
     g.status = L->status;
+    g.seg_start = nullptr;
+    g.seg_dst = nullptr;
+    g.seg_per_expert = 0;
     const bool tc = c.compute_dtype == MOE_DTYPE_BF16;
     const bool pair = tc && tile_m == TC_PAIR_TILE_M;
     const int64_t max_mtiles64 = (rows + tile_m - 1) / tile_m + n_experts;
@@ -300,6 +304,9 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.C = y_buf;
     g.N = c.output_dim;
     g.K = c.hidden_dim;
+    g.seg_start = seg_start;      // expert-parallel peer mode: rows go straight to the token owners
+    g.seg_dst = seg_dst;
+    g.seg_per_expert = seg_per_expert;
     if (pair) n = launch_group_gemm_tc2(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
     else if (tc) n = launch_group_gemm_tc(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
     else n = launch_group_gemm_f32(g, 2, max_mtiles, rows, L->num_sms, s);
@@ -454,12 +461,12 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
         if ((rc = ensure_plan(L, plan.xr, plan.hr, plan.rows_cap))) return rc;
         const int n_local = L->e_hi - L->e_lo;
         const bool pair = plan.d_tile_prefix_alt && pick_tile_m(L, plan.rows, n_local) == TC_PAIR_TILE_M;
-        if ((rc = run_experts(L, plan.xr, plan.hr, plan.yr, plan.d_local_off,
+        if ((rc = run_experts(L, plan.xr, plan.hr, nullptr, plan.d_local_off,
                               pair ? plan.d_tile_prefix_alt : plan.d_tile_prefix, plan.rows, n_local, s, 4,
-                              pair ? TC_PAIR_TILE_M : ep_tile_m)))
+                              pair ? TC_PAIR_TILE_M : ep_tile_m, plan.d_seg_start, plan.d_seg_dst, ep_world(L->ep))))
             return rc;
         ep_mark(L->ep, 2, s);
-        // all ranks' outputs are complete before anybody's combine kernel reads them
+        // every rank's GEMM 2 has stored its rows into the token owners' buffers before anybody combines
         if ((rc = ep_barrier(L->ep, s, g_err, sizeof(g_err)))) return rc;
     } else {
         EpCall call;
@@ -489,7 +496,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     }
 
     CombineParams cp;
-    cp.y = L->y;
+    cp.y = peer ? plan.yb : L->y;
     cp.out = out;
     cp.T = T;
     cp.O = c.output_dim;
@@ -497,7 +504,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     cp.idx = L->idx;
     cp.gate = L->gate;
     cp.pair_pos = L->pair_pos;
-    cp.expert_src = peer ? plan.d_expert_src : nullptr;
+    cp.expert_src = nullptr;
     cp.expert_offset = L->expert_offset;
     n = launch_combine(cp, c.compute_dtype, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(cudaGetLastError()));
