@@ -122,10 +122,6 @@ struct CombineParams {
     const int32_t* idx;
     const float* gate;
     const int32_t* pair_pos;
-    // expert-parallel peer mode (else null): outputs of expert e for this rank's rows start at
-    // expert_src[e] (possibly another GPU's memory); expert_offset is this rank's send layout
-    const void* const* expert_src;
-    const int32_t* expert_offset;
 };
 
 // Grouped GEMM over the permuted rows: C[r][n] = sum_k A[r][k] * B[e(r)][n][k].

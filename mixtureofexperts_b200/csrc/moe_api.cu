@@ -504,8 +504,6 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     cp.idx = L->idx;
     cp.gate = L->gate;
     cp.pair_pos = L->pair_pos;
-    cp.expert_src = nullptr;
-    cp.expert_offset = L->expert_offset;
     n = launch_combine(cp, c.compute_dtype, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;

@@ -225,20 +225,13 @@ __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombinePara
             s_gate[i] = g;
         }
         s_n = n;
-        // row pointers: local y, or the owner GPU's output buffer in expert-parallel peer mode
-        for (int i = 0; i < n; ++i) {
-            if (p.expert_src)
-                s_ptr[i] = reinterpret_cast<const YT*>(p.expert_src[ids[i]]) +
-                           (size_t)(s_row[i] - p.expert_offset[ids[i]]) * p.O;
-            else
-                s_ptr[i] = reinterpret_cast<const YT*>(p.y) + (size_t)s_row[i] * p.O;
-        }
+        for (int i = 0; i < n; ++i) s_ptr[i] = reinterpret_cast<const YT*>(p.y) + (size_t)s_row[i] * p.O;
     }
     __syncthreads();
     const int n = s_n;
     float* out = p.out + (size_t)t * p.O;
     const bool vec = (p.O % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) &&
-                     ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);   // peer segments: row-aligned cudaMalloc memory
+                     ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     if (vec) {
         for (int c = threadIdx.x * 4; c < p.O; c += COMB_THREADS * 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
