@@ -133,6 +133,13 @@ int moe_layer_set_expert(moe_layer_t*, int expert, const void* w1, const void* w
 int moe_layer_set_router(moe_layer_t*, const float* w, const float* logit_bias,
                          int layout, int src_is_device);
 
+/* Training-time router noise (src/core/router.jl:32-41, noise_scale > 0 without a noise network):
+ * `noise` is a caller-owned DEVICE array [T][E_router] of standard-normal draws (the caller keeps
+ * its own random stream, as Julia's randn does in the reference); forward calls with training != 0
+ * gate on logits + noise_scale*noise until it is replaced or cleared with NULL.  The z-loss still
+ * comes from the noise-free logits, like the reference's second router pass. */
+int moe_layer_set_router_noise(moe_layer_t*, const float* noise, float noise_scale);
+
 /* Number of values per token in indices/gates (k_tot), probs (E_probs), logits (E_router). */
 int moe_layer_dims(const moe_layer_t*, int32_t* k_tot, int32_t* e_probs, int32_t* e_router);
 

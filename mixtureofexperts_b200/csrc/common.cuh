@@ -39,6 +39,8 @@ struct RouterParams {
     const float* w;           // [E_router][D]
     const float* wt;          // [D_pad][E_pad] K-major zero-padded copy (launch_router_transpose)
     const float* bias;        // [E_router] or null
+    const float* noise;       // [T][E_router] standard-normal draws for training-time router noise, or null
+    float noise_scale;
     int64_t T;
     int D;
     int E;                    // layer experts (shared included)

@@ -69,6 +69,8 @@ struct moe_layer {
     float* router_wt = nullptr;  // [D_pad][E_pad] K-major zero-padded copy read by the router kernel
     float* router_bias = nullptr;
     bool has_bias = false, router_set = false;
+    const float* noise = nullptr;   // caller-owned device draws for the next training forward
+    float noise_scale = 0.f;
     std::vector<char> expert_set;
     void* stage_w = nullptr;     // device staging for host-side weight sources
     size_t stage_w_bytes = 0;
@@ -349,6 +351,8 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     r.w = L->router_w;
     r.wt = L->router_wt;
     r.bias = L->has_bias ? L->router_bias : nullptr;
+    r.noise = (training && L->noise_scale > 0.f) ? L->noise : nullptr;
+    r.noise_scale = L->noise_scale;
     r.T = T;
     r.D = c.input_dim;
     r.E = L->E;
@@ -702,6 +706,14 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     return MOE_OK;
 }
 
+int moe_layer_set_router_noise(moe_layer_t* L, const float* noise, float noise_scale) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    if (noise && !(noise_scale >= 0.f)) return fail(MOE_ERR_INVALID, "noise_scale must be non-negative");
+    L->noise = noise;
+    L->noise_scale = noise ? noise_scale : 0.f;
+    return MOE_OK;
+}
+
 int moe_layer_forward(moe_layer_t* L, const void* x, int x_dtype, int64_t T, int training, float* out,
                       const moe_forward_outputs_t* opt, void* cuda_stream) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");
@@ -752,7 +764,8 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     int nchunks = 1;
     int env_chunks = 0;   // MOE_B200_HOST_CHUNKS = n: n equal chunks (1 = off); unset: the default schedule
     // (not with the capacity constraint, whose capacity and first-come order span the whole batch)
-    if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192 && !(L->cfg.drop_tokens && training)) {
+    if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192 && !(L->cfg.drop_tokens && training) &&
+        !(L->noise && training)) {
         const char* e = getenv("MOE_B200_HOST_CHUNKS");
         env_chunks = e ? atoi(e) : 0;
         nchunks = env_chunks > 0 ? env_chunks : 5;

@@ -110,6 +110,8 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
     r.w = router_w;
     r.wt = wt;
     r.bias = logit_bias;
+    r.noise = nullptr;
+    r.noise_scale = 0.f;
     r.T = T;
     r.D = input_dim;
     r.E = num_experts;

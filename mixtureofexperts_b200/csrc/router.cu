@@ -23,6 +23,8 @@ struct GateCtx {
     int S, k, k_tot, E, E_probs;
     int shared_mode, bias_gates_only, index_base, want_entropy;
     int idx_base;     // base added to the ids stored through `idx` (0 inside the layer)
+    const float* noise;   // [T][E_router] standard-normal draws or null; scaled by noise_scale
+    float noise_scale;
     const float* bias;
     int32_t* idx;
     float* gate;
@@ -53,15 +55,21 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 template <int NJ>
 __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ], int lane,
                                            int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc) {
-    float lsel[NJ], lprob[NJ];
+    // Training-time router noise (src/core/router.jl:32-41): logits + noise_scale * randn feed the
+    // gate and are the logits the router returns; the z-loss is computed by a second, noise-free
+    // router pass in the reference (src/core/moe_layer.jl:117-121), hence from the clean logits.
+    float lsel[NJ], lprob[NJ], lclean[NJ];
     bool valid[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int e = lane + 32 * j;
         const bool in = e < c.E_router;
         const float b = (in && c.bias) ? c.bias[e] : 0.f;
-        lsel[j] = lg_in[j] + b;
-        lprob[j] = c.bias_gates_only ? lg_in[j] : lsel[j];
+        const float nz = (in && c.noise) ? c.noise_scale * c.noise[t * c.E_router + e] : 0.f;
+        const float noisy = lg_in[j] + nz;
+        lsel[j] = noisy + b;
+        lprob[j] = c.bias_gates_only ? noisy : lsel[j];
+        lclean[j] = c.bias_gates_only ? lg_in[j] : lg_in[j] + b;
         valid[j] = in && e >= c.r0;
         if (in && c.u_logits) c.u_logits[t * c.E_router + e] = lprob[j];
     }
@@ -70,12 +78,12 @@ __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const fl
         float m = -FLT_MAX;
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j < c.E_router) m = fmaxf(m, lprob[j]);
+            if (lane + 32 * j < c.E_router) m = fmaxf(m, lclean[j]);
         m = warp_max(m);
         float s = 0.f;
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j < c.E_router) s += expf(lprob[j] - m);
+            if (lane + 32 * j < c.E_router) s += expf(lclean[j] - m);
         s = warp_sum(s);
         const float lse = m + logf(s);
         lse2_acc += lse * lse;
@@ -221,6 +229,8 @@ __device__ __forceinline__ GateCtx make_ctx(const RouterParams& p) {
     c.index_base = p.index_base;
     c.want_entropy = p.want_entropy;
     c.idx_base = 0;
+    c.noise = p.noise;
+    c.noise_scale = p.noise_scale;
     c.bias = p.bias;
     c.idx = p.idx;
     c.gate = p.gate;
@@ -570,6 +580,8 @@ int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const 
     c.bias = nullptr;
     // the layer-internal arrays are the caller's arrays here, with the caller's index base
     c.idx_base = index_base;
+    c.noise = nullptr;
+    c.noise_scale = 0.f;
     c.idx = indices;
     c.gate = gates;
     c.u_idx = nullptr;

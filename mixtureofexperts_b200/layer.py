@@ -98,8 +98,8 @@ class Router:
         self.gate_type = gate_type
         self.noise_scale = float(noise_scale)
         self.use_fp32 = bool(use_fp32)
-        if use_noise_network or noise_scale > 0:
-            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "training-time router noise is not accelerated (noise_scale must be 0)")
+        if use_noise_network:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "the router noise network is not accelerated (use_noise_network)")
 
 
 def _is_torch(x) -> bool:
@@ -278,21 +278,27 @@ class MoELayer:
 
     # -- forward ---------------------------------------------------------------------------
     def __call__(self, x, training: bool = False, return_stats: bool = False, return_routing: bool = False,
-                 out=None):
+                 out=None, router_noise=None):
         """``out`` (optional, no counterpart in the reference): a preallocated float32 (T, output_dim)
         C-ordered buffer of the same kind as x (CUDA tensor / NumPy array, e.g. pinned) that
-        receives the result; the returned output is its (output_dim, T) view."""
+        receives the result; the returned output is its (output_dim, T) view.
+        ``router_noise`` (optional): the standard-normal draws, shape (router rows, T), used when
+        ``training`` and ``config.noise_scale > 0`` (src/core/router.jl:38-40); drawn with torch on the
+        layer's device when omitted."""
         cfg = self.config
         if x.ndim != 2 or x.shape[0] != cfg.input_dim:
             raise _lib.MoEError(_lib.ERR_INVALID, f"x must have shape (input_dim={cfg.input_dim}, T), got {tuple(x.shape)}")
         T = int(x.shape[1])
         aux_free = isinstance(self.balance_loss, AuxiliaryFreeLoss) and training
+        noise_keep = self._arm_router_noise(T, training, router_noise)
         want_stats = cfg.num_shared_experts == 0 or aux_free
         if _is_torch(x) and x.is_cuda:
             out, loss, extra = self._forward_torch(x, T, training, want_stats, return_routing, out)
         else:
             out, loss, extra = self._forward_host(x if _is_torch(x) else np.asarray(x), T, training, want_stats,
                                                   return_routing, out)
+        if noise_keep is not None:
+            _lib.check(_lib.lib.moe_layer_set_router_noise(self._handle, None, 0.0))
         if cfg.num_shared_experts == 0:
             # update_stats! (src/core/moe_layer.jl:250-264) runs in forward_standard only
             self._pending.append((extra["tokens_per_expert"], extra["routing_entropy"]))
@@ -308,6 +314,28 @@ class MoELayer:
         if return_routing:
             ret = ret + ({k: extra[k] for k in ("indices", "gates", "probs", "logits")},)
         return ret
+
+    def _arm_router_noise(self, T, training, router_noise):
+        """Hand the draws of this call's router noise to the device handle (a (T, rows) float32
+        CUDA tensor that must stay alive until the forward has been queued)."""
+        scale = float(getattr(self.router, "noise_scale", 0.0) or 0.0)
+        if not training or scale <= 0.0:
+            return None
+        import torch
+
+        dev = torch.device(f"cuda:{self.device}")
+        if router_noise is None:
+            if not hasattr(self, "_noise_gen"):
+                self._noise_gen = torch.Generator(device=dev)
+            nz = torch.randn((T, self.e_router), device=dev, generator=self._noise_gen, dtype=torch.float32)
+        else:
+            nz = torch.as_tensor(np.asarray(router_noise) if not _is_torch(router_noise) else router_noise)
+            nz = nz.to(device=dev, dtype=torch.float32).t().contiguous()
+            if tuple(nz.shape) != (T, self.e_router):
+                raise _lib.MoEError(_lib.ERR_INVALID, f"router_noise must have shape ({self.e_router}, T)")
+        torch.cuda.synchronize(dev)     # the draws are read on another stream by a host-path call
+        _lib.check(_lib.lib.moe_layer_set_router_noise(self._handle, nz.data_ptr(), scale))
+        return nz
 
     def _forward_torch(self, x, T, training, want_stats, want_routing, out=None):
         import torch

@@ -235,6 +235,11 @@ class MoEConfig:
     aux_free_bias: Optional[np.ndarray] = None
     # A bias that is part of the logits themselves (a router Dense with bias).
     router_bias: Optional[np.ndarray] = None
+    # Router.noise_scale (src/core/router.jl:32-41): logits += noise_scale * randn when training; the
+    # standard-normal draws are passed in (router_noise, shape (T, E_router)) so that a test can give
+    # the device path the same draws.
+    noise_scale: float = 0.0
+    router_noise: Optional[np.ndarray] = None
 
 
 @dataclass
@@ -243,12 +248,14 @@ class MoEWeights:
     experts: List[GatedExpertWeights]
 
 
-def router_forward(cfg: MoEConfig, w: MoEWeights, x: np.ndarray, dtype=np.float32):
-    """(router::Router)(x) (src/core/router.jl:25-46) with noise off."""
+def router_forward(cfg: MoEConfig, w: MoEWeights, x: np.ndarray, dtype=np.float32, training: bool = False):
+    """(router::Router)(x; training) (src/core/router.jl:25-46), without a noise network."""
     xr = x.astype(dtype) if cfg.use_fp32_router or x.dtype != dtype else x
     logits = xr @ w.router.astype(dtype).T
     if cfg.router_bias is not None:
         logits = logits + cfg.router_bias.astype(dtype)
+    if training and cfg.noise_scale > 0:
+        logits = logits + (cfg.router_noise.astype(dtype) * dtype(cfg.noise_scale))     # router.jl:38-40
     indices, gates, probs = compute_gates(cfg.gate_type, logits)
     return indices, gates, probs, logits
 
@@ -304,7 +311,7 @@ def forward_standard(cfg: MoEConfig, w: MoEWeights, x: np.ndarray, training: boo
     T = x.shape[0]
     act = ACTIVATIONS[cfg.activation]
     output = np.zeros((T, cfg.output_dim), dtype=dtype)
-    indices, gates, probs, logits = router_forward(cfg, w, x, dtype)
+    indices, gates, probs, logits = router_forward(cfg, w, x, dtype, training)
     if cfg.aux_free_bias is not None:
         biased = logits + cfg.aux_free_bias.astype(logits.dtype)      # auxiliary_free.jl:90-92
         indices, gates, _ = compute_gates(cfg.gate_type, biased)
@@ -347,7 +354,9 @@ def moe_layer_forward(cfg: MoEConfig, w: MoEWeights, x: np.ndarray, training: bo
     else:
         out, loss, aux = forward_standard(cfg, w, x, training, dtype)
     if training and cfg.z_loss_weight > 0:
-        loss = np.float32(loss + z_loss(cfg.z_loss_weight, aux["logits"]))
+        # the reference runs the router again with training=false: no noise in these logits
+        clean = aux["logits"] if cfg.noise_scale <= 0 else router_forward(cfg, w, x, dtype, False)[3]
+        loss = np.float32(loss + z_loss(cfg.z_loss_weight, clean))
     return out, np.float32(loss), aux
 
 

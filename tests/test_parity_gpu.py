@@ -203,6 +203,41 @@ def test_capacity_constraint_drops_late_tokens(T, E, k, cf, host):
     layer.close()
 
 
+@pytest.mark.parametrize("host", [False, True])
+def test_training_time_router_noise_with_given_draws(host):
+    """noise_scale > 0 && training (src/core/router.jl:38-40): logits + noise_scale*randn feed the gate;
+    the z-loss comes from the noise-free logits (the reference's second router pass).  The draws are
+    passed in, so the comparison with the oracle is exact up to FP32 rounding."""
+    T, D, H, O, E, k = 300, 64, 96, 48, 8, 2
+    x, w = orc.make_layer_inputs(77, T, D, H, O, E, init="normal", std=0.25)
+    noise = np.random.default_rng(9).standard_normal((T, E)).astype(np.float32)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(k), balance_alpha=0.01, z_loss_weight=0.001, noise_scale=0.7,
+                        router_noise=noise)
+    o_out, o_loss, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+    clean_idx = orc.moe_layer_forward(cfg, w, x, training=False)[2]["indices"]
+    assert (aux["indices"] != clean_idx).any()                   # the noise does change the routing
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=device_gate("topk", k), noise_scale=0.7)
+    layer.router.noise_scale = 0.7
+    xin = np.asfortranarray(x.T) if host else torch.from_numpy(x).cuda().t()
+    out, loss, routing = layer(xin, training=True, return_routing=True, router_noise=noise.T)
+    if not host:
+        out, loss = out.cpu().numpy(), float(loss.item())
+        routing = {k_: v.cpu().numpy() for k_, v in routing.items()}
+    assert np.array_equal(routing["indices"].T, aux["indices"])
+    assert rel_inf(routing["logits"].T, aux["logits"]) < F32_TOL
+    assert rel_inf(routing["gates"].T, aux["gates"]) < F32_TOL
+    assert rel_inf(out.T, o_out) < F32_TOL
+    assert abs(float(loss) - float(o_loss)) < F32_TOL * abs(float(o_loss))
+    # inference ignores the noise; a training call without given draws still runs (draws made on the device)
+    out2, _, rt2 = layer(xin, training=False, return_routing=True)
+    idx2 = rt2["indices"] if host else rt2["indices"].cpu().numpy()
+    assert np.array_equal(idx2.T, clean_idx)
+    out3, _ = layer(xin, training=True)
+    assert np.isfinite(out3 if host else out3.cpu().numpy()).all()
+    layer.close()
+
+
 def test_empty_batch():
     x, w = orc.make_layer_inputs(1, 1, 64, 96, 64, 4, init="normal", std=0.25)
     layer = make_device_layer(w, D=64, H=96, O=64, gate=device_gate("topk", 2))
