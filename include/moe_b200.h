@@ -64,6 +64,9 @@ extern "C" {
 #define MOE_SHARED_GATING      1   /* via SharedExpertGating: experts 1..S are always selected */
 #define MOE_SHARED_LAYER_BLEND 2   /* MoEConfig.num_shared_experts>0:
                                       forward_with_shared_experts, src/core/moe_layer.jl:158-185 */
+/* expert_kind */
+#define MOE_EXPERT_GATED       0   /* GatedExpert: w2(act.(w1 x) .* (w3 x))            src/experts/gated.jl:29-34    */
+#define MOE_EXPERT_STANDARD    1   /* StandardExpert: w2(act.(w1 x .+ b1)) .+ b2       src/experts/standard.jl:38-55 */
 /* memory layout of a weight matrix W with logical shape (out x in), y = W*x */
 #define MOE_LAYOUT_IN_CONTIG   0   /* [out][in], in fastest: Llama2.jl (in x out) column-major
                                       (src/llama2/conversion.jl:277-331), NumPy (out,in) C-order */
@@ -94,6 +97,7 @@ typedef struct moe_config {
                                  the first ceil(capacity_factor*T/E) (token, slot) pairs in token order
                                  keep their slot, later ones get id index_base-1 and gate 0, and every
                                  token's gates are renormalised.  Not with LAYER_BLEND or expert parallel. */
+    int32_t expert_kind;      /* MOE_EXPERT_* (MoEConfig.expert_type :gated / :standard) */
 } moe_config_t;
 
 typedef struct moe_layer moe_layer_t;   /* opaque: one per (layer, device) */
@@ -126,6 +130,12 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out);
  * caller's streams are complete before they are read.  Synchronises before returning. */
 int moe_layer_set_expert(moe_layer_t*, int expert, const void* w1, const void* w2, const void* w3,
                          int src_dtype, int layout, int src_is_device);
+
+/* The same for a StandardExpert (src/experts/standard.jl:8-36; create_cuda_experts, src/cuda/types.jl):
+ * w1 (H x D), w2 (O x H) in src_dtype/layout, b1 [H] and b2 [O] FP32 (NULL = no bias), all host or all
+ * device pointers.  Dropout inside the expert is not offered (expert_dropout must be 0). */
+int moe_layer_set_expert_standard(moe_layer_t*, int expert, const void* w1, const float* b1, const void* w2,
+                                  const float* b2, int src_dtype, int layout, int src_is_device);
 
 /* Router.weight (src/core/router.jl:14-23): FP32 (E_router x D), E_router = E - S.
  * (E_router = E in GATING mode: the first S rows are present but unused by the gate.)

@@ -27,7 +27,7 @@ struct CMoeConfig            # moe_config_t
     gate_kind::Int32; activation::Int32; compute_dtype::Int32; shared_mode::Int32
     balance_alpha::Float32; z_loss_weight::Float32
     index_base::Int32; bias_gates_only::Int32
-    capacity_factor::Float32; drop_tokens::Int32
+    capacity_factor::Float32; drop_tokens::Int32; expert_kind::Int32
 end
 
 struct CForwardOutputs       # moe_forward_outputs_t (all nullable)
@@ -71,6 +71,19 @@ function GatedExpert(input_dim::Int, hidden_dim::Int, output_dim::Int, activatio
     σ = sqrt(2.0f0 / input_dim)
     GatedExpert(randn(Float32, hidden_dim, input_dim) .* σ, randn(Float32, output_dim, hidden_dim) .* σ,
                 randn(Float32, hidden_dim, input_dim) .* σ, activation)
+end
+
+struct StandardExpert{A}                            # src/experts/standard.jl:8-36 (dropout not offered)
+    w1::Matrix{Float32}                      # (hidden x input)
+    w2::Matrix{Float32}                      # (output x hidden)
+    b1::Union{Vector{Float32}, Nothing}
+    b2::Union{Vector{Float32}, Nothing}
+    activation::A
+end
+function StandardExpert(input_dim::Int, hidden_dim::Int, output_dim::Int, activation; bias::Bool = true)
+    StandardExpert(randn(Float32, hidden_dim, input_dim) .* sqrt(2.0f0 / input_dim),
+                   randn(Float32, output_dim, hidden_dim) .* sqrt(2.0f0 / hidden_dim),
+                   bias ? zeros(Float32, hidden_dim) : nothing, bias ? zeros(Float32, output_dim) : nothing, activation)
 end
 
 Base.@kwdef struct MoEConfig                        # src/core/moe_layer.jl:4-29
@@ -123,18 +136,19 @@ mutable struct MoELayer                              # src/core/moe_layer.jl:34-
 end
 
 function MoELayer(config::MoEConfig; device::Int = 0, compute_dtype::Symbol = :f32)
-    config.expert_type == :gated || error("only expert_type = :gated is accelerated")
+    gated = config.expert_type == :gated          # create_experts: anything else is a StandardExpert
+    gated || config.expert_dropout == 0 || error("expert_dropout > 0 is not accelerated")
     kind, k, gate_shared = gate_kind(config.gate_type)
     shared_mode = gate_shared > 0 ? SHARED_GATING : (config.num_shared_experts > 0 ? SHARED_LAYER_BLEND : SHARED_NONE)
     nshared = gate_shared > 0 ? gate_shared : config.num_shared_experts
     c = CMoeConfig(config.num_experts, nshared, k, config.input_dim, config.hidden_dim, config.output_dim,
                    kind, activation_enum(config.activation), compute_dtype == :bf16 ? DTYPE_BF16 : DTYPE_F32,
                    shared_mode, config.balance_loss.α, config.z_loss_weight, 1, 0,
-                   config.capacity_factor, config.drop_tokens ? 1 : 0)
+                   config.capacity_factor, config.drop_tokens ? 1 : 0, gated ? 0 : 1)
     h = Ref{Ptr{Cvoid}}(C_NULL)
     check(ccall((:moe_layer_create, LIB), Cint, (Ref{CMoeConfig}, Cint, Ref{Ptr{Cvoid}}), c, device, h))
-    experts = [GatedExpert(config.input_dim, config.hidden_dim, config.output_dim, config.activation)
-               for _ in 1:config.num_experts]
+    experts = [(gated ? GatedExpert : StandardExpert)(config.input_dim, config.hidden_dim, config.output_dim,
+                                                      config.activation) for _ in 1:config.num_experts]
     e_router = shared_mode == SHARED_LAYER_BLEND ? config.num_experts - nshared : config.num_experts
     lim = sqrt(6.0f0 / (config.input_dim + e_router))            # Flux Dense default: Glorot uniform
     router = (rand(Float32, e_router, config.input_dim) .* 2 .- 1) .* lim
@@ -150,6 +164,13 @@ end
 function sync_weights!(moe::MoELayer)
     for (i, e) in enumerate(moe.experts)
         # Flux (out x in) column-major arrays: the OUT index is contiguous
+        if e isa StandardExpert
+            check(ccall((:moe_layer_set_expert_standard, LIB), Cint,
+                        (Ptr{Cvoid}, Cint, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Cint, Cint, Cint),
+                        moe.handle, i - 1, e.w1, something(e.b1, C_NULL), e.w2, something(e.b2, C_NULL),
+                        DTYPE_F32, LAYOUT_OUT_CONTIG, 0))
+            continue
+        end
         check(ccall((:moe_layer_set_expert, LIB), Cint,
                     (Ptr{Cvoid}, Cint, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Cint, Cint, Cint),
                     moe.handle, i - 1, e.w1, e.w2, e.w3, DTYPE_F32, LAYOUT_OUT_CONTIG, 0))

@@ -11,7 +11,7 @@ import importlib
 
 _EXPORTS = {
     "LIB_PATH": "_lib", "MoEError": "_lib", "version": "_lib",
-    "Expert": "experts", "GatedExpert": "experts", "gelu": "experts", "identity": "experts", "relu": "experts",
+    "Expert": "experts", "GatedExpert": "experts", "StandardExpert": "experts", "gelu": "experts", "identity": "experts", "relu": "experts",
     "silu": "experts", "swish": "experts",
     "GatingMechanism": "gating", "SharedExpertGating": "gating", "SwitchGating": "gating", "TopKGating": "gating",
     "compute_gates": "gating",

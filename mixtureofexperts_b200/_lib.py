@@ -18,9 +18,10 @@ ACT_SILU, ACT_GELU_TANH, ACT_RELU, ACT_IDENTITY = 0, 1, 2, 3
 DTYPE_F32, DTYPE_BF16 = 0, 1
 SHARED_NONE, SHARED_GATING, SHARED_LAYER_BLEND = 0, 1, 2
 LAYOUT_IN_CONTIG, LAYOUT_OUT_CONTIG = 0, 1
+EXPERT_GATED, EXPERT_STANDARD = 0, 1
 
 EXPORTS = [
-    "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_router", "moe_layer_set_router_noise", "moe_layer_dims",
+    "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_expert_standard", "moe_layer_set_router", "moe_layer_set_router_noise", "moe_layer_dims",
     "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_loss",
     "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_launch_count",
     "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_ep_layout", "moe_layer_destroy",
@@ -44,7 +45,7 @@ class MoeConfig(C.Structure):
         ("gate_kind", C.c_int32), ("activation", C.c_int32), ("compute_dtype", C.c_int32),
         ("shared_mode", C.c_int32), ("balance_alpha", C.c_float), ("z_loss_weight", C.c_float),
         ("index_base", C.c_int32), ("bias_gates_only", C.c_int32),
-        ("capacity_factor", C.c_float), ("drop_tokens", C.c_int32),
+        ("capacity_factor", C.c_float), ("drop_tokens", C.c_int32), ("expert_kind", C.c_int32),
     ]
 
 
@@ -64,6 +65,7 @@ def _load():
     vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
     lib.moe_layer_create.argtypes = [C.POINTER(MoeConfig), i32, C.POINTER(vp)]
     lib.moe_layer_set_expert.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32]
+    lib.moe_layer_set_expert_standard.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32]
     lib.moe_layer_set_router.argtypes = [vp, vp, vp, i32, i32]
     lib.moe_layer_set_router_noise.argtypes = [vp, vp, f32]
     lib.moe_layer_dims.argtypes = [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]

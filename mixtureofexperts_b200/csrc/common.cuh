@@ -133,7 +133,10 @@ struct GroupGemmParams {
     const void* B1;           // [E][N][K]  (w3 for mode 1, unused for mode 2)
     void* C;                  // [P][N]
     int N, K, E;
-    int activation;
+    int activation;           // mode 1: activation of the gate branch
+    // mode 2 epilogue extras (StandardExpert, src/experts/standard.jl:38-55): C = act(A*B0^T + bias)
+    const float* bias;        // [E][N] FP32 or null
+    int epilogue_act;         // MOE_ACT_* applied after the bias, or -1 for none
     const int32_t* expert_offset; // [E+1]
     const int32_t* tile_prefix;   // [E+1]
     int32_t* status;
@@ -184,10 +187,12 @@ void tc_plan_destroy(TcGemmPlan*);
 // (re)encodes the tensor maps; returns 0 or a negative MOE_ERR_* (message via out_msg)
 int tc_plan_encode(TcGemmPlan*, const void* xp, const void* h, int64_t P_cap, int D, int H, int O, int E,
                    const void* w1, const void* w3, const void* w2, const char** out_msg);
-int launch_group_gemm_tc(const TcGemmPlan*, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
-                         cudaStream_t s);
-int launch_group_gemm_tc2(const TcGemmPlan*, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
-                          cudaStream_t s);
+// stage 1: A = permuted rows, B = w1 (and w3 in mode 1); stage 2: A = hidden activations, B = w2.
+// mode 1: gated pair with act(gate)*up epilogue; mode 2: single matrix (+ bias, + activation).
+int launch_group_gemm_tc(const TcGemmPlan*, int stage, int mode, const GroupGemmParams& p, int max_tiles,
+                         int num_sms, cudaStream_t s);
+int launch_group_gemm_tc2(const TcGemmPlan*, int stage, int mode, const GroupGemmParams& p, int max_tiles,
+                          int num_sms, cudaStream_t s);
 
 __host__ __device__ inline float bf16_bits_to_float(uint16_t b) {
     union { uint32_t u; float f; } v;

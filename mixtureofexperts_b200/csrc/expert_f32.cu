@@ -126,8 +126,13 @@ __global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemm
             const int n = n0 + tx + 32 * i;
             if (n >= p.N) continue;
             float v;
-            if (MODE == 1) v = apply_act(p.activation, acc[0][r][i]) * acc[NB - 1][r][i];
-            else v = acc[0][r][i];
+            if (MODE == 1) {
+                v = apply_act(p.activation, acc[0][r][i]) * acc[NB - 1][r][i];
+            } else {
+                v = acc[0][r][i];
+                if (p.bias) v += p.bias[(size_t)e * p.N + n];
+                if (p.epilogue_act >= 0) v = apply_act(p.epilogue_act, v);
+            }
             group_gemm_out_row<float>(p, e, row)[n] = v;
         }
     }
@@ -220,8 +225,14 @@ __global__ void __launch_bounds__(SK_THREADS) group_gemm_f32_skinny_kernel(const
                 if (lane == c * SK_ROWS + r) {
                     const int row = r0 + r, n = n_base + c;
                     if (row < row_end && n < p.N) {
-                        const float v = (MODE == 1) ? apply_act(p.activation, acc[0][c][r]) * acc[NB - 1][c][r]
-                                                    : acc[0][c][r];
+                        float v;
+                        if (MODE == 1) {
+                            v = apply_act(p.activation, acc[0][c][r]) * acc[NB - 1][c][r];
+                        } else {
+                            v = acc[0][c][r];
+                            if (p.bias) v += p.bias[(size_t)e * p.N + n];
+                            if (p.epilogue_act >= 0) v = apply_act(p.epilogue_act, v);
+                        }
                         group_gemm_out_row<float>(p, e, row)[n] = v;
                     }
                 }

@@ -219,6 +219,16 @@ group_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(a[i]);
+                    if (p.bias) {
+                        const float* b = p.bias + (size_t)t.e * p.N + col_base + c;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col_base + c + i < p.N) v[i] += b[i];
+                    }
+                    if (p.epilogue_act >= 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = act_fast(p.epilogue_act, v[i]);
+                    }
                     if (row_ok && col_base + c < p.N) store_row32(dst_row, col_base + c, p.N, v, vec_ok);
                 }
             }
@@ -302,7 +312,7 @@ int tc_plan_encode(TcGemmPlan* plan, const void* xp, const void* h, int64_t P_ca
     const bool ok = encode_map(&plan->map_xp, xp, (uint64_t)D, (uint64_t)P_cap, 1, false) &&
                     encode_map(&plan->map_h, h, (uint64_t)H, (uint64_t)P_cap, 1, false) &&
                     encode_map(&plan->map_w1, w1, (uint64_t)D, (uint64_t)H, (uint64_t)E, true) &&
-                    encode_map(&plan->map_w3, w3, (uint64_t)D, (uint64_t)H, (uint64_t)E, true) &&
+                    (!w3 || encode_map(&plan->map_w3, w3, (uint64_t)D, (uint64_t)H, (uint64_t)E, true)) &&
                     encode_map(&plan->map_w2, w2, (uint64_t)H, (uint64_t)O, (uint64_t)E, true);
     if (!ok) {
         *out_msg = "cuTensorMapEncodeTiled failed";
@@ -312,8 +322,8 @@ int tc_plan_encode(TcGemmPlan* plan, const void* xp, const void* h, int64_t P_ca
     return MOE_OK;
 }
 
-int launch_group_gemm_tc(const TcGemmPlan* plan_c, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
-                         cudaStream_t s) {
+int launch_group_gemm_tc(const TcGemmPlan* plan_c, int stage, int mode, const GroupGemmParams& p, int max_tiles,
+                         int num_sms, cudaStream_t s) {
     TcGemmPlan* plan = const_cast<TcGemmPlan*>(plan_c);
     if (!plan->valid) return -1;
     if (max_tiles <= 0) return 0;
@@ -330,6 +340,8 @@ int launch_group_gemm_tc(const TcGemmPlan* plan_c, int mode, const GroupGemmPara
     const int grid = max_tiles < num_sms ? max_tiles : num_sms;
     if (mode == 1)
         group_gemm_tc_kernel<1><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w3, p, gm);
+    else if (stage == 1)
+        group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w1, p, gm);
     else
         group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_h, plan->map_w2, plan->map_w2, p, gm);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;

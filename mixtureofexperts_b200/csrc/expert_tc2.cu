@@ -270,6 +270,16 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(a[i]);
+                    if (p.bias) {
+                        const float* b = p.bias + (size_t)t.e * p.N + col_base + c;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col_base + c + i < p.N) v[i] += b[i];
+                    }
+                    if (p.epilogue_act >= 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = act_fast(p.epilogue_act, v[i]);
+                    }
                     if (row_ok && col_base + c < p.N) store_row32(dst_row, col_base + c, p.N, v, vec_ok);
                 }
             }
@@ -299,8 +309,8 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
 // Launch of the CTA-pair kernel; same contract as launch_group_gemm_tc.  `p.tile_prefix` must have
 // been built for TC_PAIR_TILE_M rows per tile.
-int launch_group_gemm_tc2(const TcGemmPlan* plan_c, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
-                          cudaStream_t s) {
+int launch_group_gemm_tc2(const TcGemmPlan* plan_c, int stage, int mode, const GroupGemmParams& p, int max_tiles,
+                          int num_sms, cudaStream_t s) {
     TcGemmPlan* plan = const_cast<TcGemmPlan*>(plan_c);
     if (!plan->valid) return -1;
     if (max_tiles <= 0) return 0;
@@ -340,6 +350,8 @@ int launch_group_gemm_tc2(const TcGemmPlan* plan_c, int mode, const GroupGemmPar
     cudaError_t e;
     if (mode == 1)
         e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<1>, plan->map_xp, plan->map_w1, plan->map_w3, p, gm);
+    else if (stage == 1)
+        e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<2>, plan->map_xp, plan->map_w1, plan->map_w1, p, gm);
     else
         e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<2>, plan->map_h, plan->map_w2, plan->map_w2, p, gm);
     return e == cudaSuccess ? 1 : -1;

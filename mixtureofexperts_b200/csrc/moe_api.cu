@@ -65,6 +65,8 @@ struct moe_layer {
     void* w1 = nullptr;
     void* w3 = nullptr;
     void* w2 = nullptr;
+    float* b1 = nullptr;         // [E_local][H] FP32, standard experts only
+    float* b2 = nullptr;         // [E_local][O]
     float* router_w = nullptr;   // [E_router][D]
     float* router_wt = nullptr;  // [D_pad][E_pad] K-major zero-padded copy read by the router kernel
     float* router_bias = nullptr;
@@ -137,6 +139,8 @@ int validate_config(const moe_config_t& c) {
         return fail(MOE_ERR_INVALID, "unknown gate_kind %d", c.gate_kind);
     if (c.activation < MOE_ACT_SILU || c.activation > MOE_ACT_IDENTITY)
         return fail(MOE_ERR_INVALID, "unknown activation %d", c.activation);
+    if (c.expert_kind != MOE_EXPERT_GATED && c.expert_kind != MOE_EXPERT_STANDARD)
+        return fail(MOE_ERR_INVALID, "unknown expert_kind %d", c.expert_kind);
     if (c.compute_dtype != MOE_DTYPE_F32 && c.compute_dtype != MOE_DTYPE_BF16)
         return fail(MOE_ERR_INVALID, "unknown compute_dtype %d", c.compute_dtype);
     if (c.shared_mode < MOE_SHARED_NONE || c.shared_mode > MOE_SHARED_LAYER_BLEND)
@@ -171,8 +175,15 @@ int ensure_weights(moe_layer* L) {
     const size_t n_local = (size_t)(L->e_hi - L->e_lo);
     const size_t D = L->cfg.input_dim, H = L->cfg.hidden_dim, O = L->cfg.output_dim;
     CUDA_TRY(cudaMalloc(&L->w1, n_local * H * D * el));
-    CUDA_TRY(cudaMalloc(&L->w3, n_local * H * D * el));
     CUDA_TRY(cudaMalloc(&L->w2, n_local * O * H * el));
+    if (L->cfg.expert_kind == MOE_EXPERT_STANDARD) {
+        CUDA_TRY(cudaMalloc(&L->b1, n_local * H * sizeof(float)));
+        CUDA_TRY(cudaMalloc(&L->b2, n_local * O * sizeof(float)));
+        CUDA_TRY(cudaMemset(L->b1, 0, n_local * H * sizeof(float)));
+        CUDA_TRY(cudaMemset(L->b2, 0, n_local * O * sizeof(float)));
+    } else {
+        CUDA_TRY(cudaMalloc(&L->w3, n_local * H * D * el));
+    }
     L->expert_set.assign(n_local, 0);
     L->plan_dirty = true;
     return MOE_OK;
@@ -286,31 +297,38 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     if (max_mtiles64 > 0x7fffffff / 256) return fail(MOE_ERR_UNSUPPORTED, "too many row tiles");
     const int max_mtiles = (int)max_mtiles64;
     int n;
-    // GEMM 1: h = act(a W1^T) .* (a W3^T)
+    const bool standard = c.expert_kind == MOE_EXPERT_STANDARD;
+    // GEMM 1: gated h = act(a W1^T) .* (a W3^T); standard h = act(a W1^T + b1)
+    const int mode1 = standard ? 2 : 1;
+    const int ntile1 = standard ? (c.hidden_dim + 255) / 256 : (c.hidden_dim + 127) / 128;
     g.A = a_in;
     g.B0 = L->w1;
-    g.B1 = L->w3;
+    g.B1 = standard ? nullptr : L->w3;
     g.C = h_buf;
     g.N = c.hidden_dim;
     g.K = c.input_dim;
-    if (pair) n = launch_group_gemm_tc2(L->plan, 1, g, max_mtiles * ((c.hidden_dim + 127) / 128), L->num_sms, s);
-    else if (tc) n = launch_group_gemm_tc(L->plan, 1, g, max_mtiles * ((c.hidden_dim + 127) / 128), L->num_sms, s);
-    else n = launch_group_gemm_f32(g, 1, max_mtiles, rows, L->num_sms, s);
+    g.bias = standard ? L->b1 : nullptr;
+    g.epilogue_act = standard ? c.activation : -1;
+    if (pair) n = launch_group_gemm_tc2(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
+    else if (tc) n = launch_group_gemm_tc(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
+    else n = launch_group_gemm_f32(g, mode1, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 1 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
     stage_mark(L, ev_base, s);
-    // GEMM 2: y = h W2^T
+    // GEMM 2: y = h W2^T (+ b2 for a standard expert)
     g.A = h_buf;
     g.B0 = L->w2;
     g.B1 = nullptr;
+    g.bias = standard ? L->b2 : nullptr;
+    g.epilogue_act = -1;
     g.C = y_buf;
     g.N = c.output_dim;
     g.K = c.hidden_dim;
     g.seg_start = seg_start;      // expert-parallel peer mode: rows go straight to the token owners
     g.seg_dst = seg_dst;
     g.seg_per_expert = seg_per_expert;
-    if (pair) n = launch_group_gemm_tc2(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
-    else if (tc) n = launch_group_gemm_tc(L->plan, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
+    if (pair) n = launch_group_gemm_tc2(L->plan, 2, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
+    else if (tc) n = launch_group_gemm_tc(L->plan, 2, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
     else n = launch_group_gemm_f32(g, 2, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 2 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
@@ -594,6 +612,8 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->w1);
     dev_free(L->w3);
     dev_free(L->w2);
+    dev_free(L->b1);
+    dev_free(L->b2);
     dev_free(L->router_w);
     dev_free(L->router_bias);
     dev_free(L->router_wt);
@@ -633,9 +653,9 @@ int moe_layer_dims(const moe_layer_t* L, int32_t* k_tot, int32_t* e_probs, int32
     return MOE_OK;
 }
 
-int moe_layer_set_expert(moe_layer_t* L, int expert, const void* w1, const void* w2, const void* w3, int src_dtype,
-                         int layout, int src_is_device) {
-    if (!L || !w1 || !w2 || !w3) return fail(MOE_ERR_INVALID, "null argument");
+// shared body of the two expert setters: w3 == null for a standard expert (then b1/b2 may be given)
+static int set_expert_impl(moe_layer_t* L, int expert, const void* w1, const void* w2, const void* w3, const float* b1,
+                           const float* b2, int src_dtype, int layout, int src_is_device) {
     if (src_dtype != MOE_DTYPE_F32 && src_dtype != MOE_DTYPE_BF16) return fail(MOE_ERR_INVALID, "unknown src_dtype");
     if (layout != MOE_LAYOUT_IN_CONTIG && layout != MOE_LAYOUT_OUT_CONTIG) return fail(MOE_ERR_INVALID, "unknown layout");
     if (expert < 0 || expert >= L->E) return fail(MOE_ERR_INVALID, "expert %d out of range 0..%d", expert, L->E - 1);
@@ -653,10 +673,11 @@ int moe_layer_set_expert(moe_layer_t* L, int expert, const void* w1, const void*
     struct Item { const void* src; void* dst; int rows, cols; };
     const Item items[3] = {
         {w1, (char*)L->w1 + slot * H * D * el, (int)H, (int)D},
-        {w3, (char*)L->w3 + slot * H * D * el, (int)H, (int)D},
+        {w3, w3 ? (char*)L->w3 + slot * H * D * el : nullptr, (int)H, (int)D},
         {w2, (char*)L->w2 + slot * O * H * el, (int)O, (int)H},
     };
     for (const Item& it : items) {
+        if (!it.src) continue;
         const void* src = it.src;
         const size_t bytes = (size_t)it.rows * it.cols * sel;
         if (!src_is_device) {
@@ -670,8 +691,32 @@ int moe_layer_set_expert(moe_layer_t* L, int expert, const void* w1, const void*
         L->launches += n;
         CUDA_TRY(cudaStreamSynchronize(L->stream));
     }
+    const cudaMemcpyKind kind = src_is_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+    if (L->b1) {
+        if (b1) CUDA_TRY(cudaMemcpyAsync(L->b1 + slot * H, b1, H * sizeof(float), kind, L->stream));
+        else CUDA_TRY(cudaMemsetAsync(L->b1 + slot * H, 0, H * sizeof(float), L->stream));
+        if (b2) CUDA_TRY(cudaMemcpyAsync(L->b2 + slot * O, b2, O * sizeof(float), kind, L->stream));
+        else CUDA_TRY(cudaMemsetAsync(L->b2 + slot * O, 0, O * sizeof(float), L->stream));
+        CUDA_TRY(cudaStreamSynchronize(L->stream));
+    }
     L->expert_set[slot] = 1;
     return MOE_OK;
+}
+
+int moe_layer_set_expert(moe_layer_t* L, int expert, const void* w1, const void* w2, const void* w3, int src_dtype,
+                         int layout, int src_is_device) {
+    if (!L || !w1 || !w2 || !w3) return fail(MOE_ERR_INVALID, "null argument");
+    if (L->cfg.expert_kind != MOE_EXPERT_GATED)
+        return fail(MOE_ERR_STATE, "this layer holds standard experts: use moe_layer_set_expert_standard");
+    return set_expert_impl(L, expert, w1, w2, w3, nullptr, nullptr, src_dtype, layout, src_is_device);
+}
+
+int moe_layer_set_expert_standard(moe_layer_t* L, int expert, const void* w1, const float* b1, const void* w2,
+                                  const float* b2, int src_dtype, int layout, int src_is_device) {
+    if (!L || !w1 || !w2) return fail(MOE_ERR_INVALID, "null argument");
+    if (L->cfg.expert_kind != MOE_EXPERT_STANDARD)
+        return fail(MOE_ERR_STATE, "this layer holds gated experts: use moe_layer_set_expert");
+    return set_expert_impl(L, expert, w1, w2, nullptr, b1, b2, src_dtype, layout, src_is_device);
 }
 
 int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias, int layout, int src_is_device) {

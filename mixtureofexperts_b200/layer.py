@@ -23,7 +23,7 @@ import numpy as np
 
 from . import _lib
 from . import experts as _experts
-from .experts import GatedExpert
+from .experts import GatedExpert, StandardExpert
 from .gating import GatingMechanism, SharedExpertGating, SwitchGating, TopKGating, gate_kind_of
 from .losses import AuxiliaryFreeLoss, LoadBalancingLoss, SwitchTransformerLoss
 
@@ -166,8 +166,10 @@ class MoELayer:
         self.device = int(device)
         self.compute_dtype = compute_dtype
         self._handle = C.c_void_p()
-        if config.expert_type != "gated" and str(config.expert_type) != ":gated":
-            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "only expert_type='gated' (GatedExpert) is accelerated")
+        # create_experts (src/core/moe_layer.jl:65-102): :gated builds GatedExpert, anything else StandardExpert
+        self.gated = str(config.expert_type).lstrip(":") == "gated"
+        if not self.gated and config.expert_dropout > 0:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "expert_dropout > 0 (Dropout inside StandardExpert) is not accelerated")
         if config.use_cur:
             raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "CUR experts are not accelerated")
         kind, k, gate_shared = gate_kind_of(config.gate_type)
@@ -190,7 +192,8 @@ class MoELayer:
             compute_dtype={"f32": _lib.DTYPE_F32, "bf16": _lib.DTYPE_BF16}[compute_dtype],
             shared_mode=shared_mode, balance_alpha=float(alpha), z_loss_weight=float(config.z_loss_weight),
             index_base=1, bias_gates_only=1 if isinstance(self.balance_loss, AuxiliaryFreeLoss) else 0,
-            capacity_factor=float(config.capacity_factor), drop_tokens=int(bool(config.drop_tokens)))
+            capacity_factor=float(config.capacity_factor), drop_tokens=int(bool(config.drop_tokens)),
+            expert_kind=_lib.EXPERT_GATED if self.gated else _lib.EXPERT_STANDARD)
         _lib.check(_lib.lib.moe_layer_create(C.byref(self._cfg), self.device, C.byref(self._handle)))
         kt, ep, er = C.c_int32(), C.c_int32(), C.c_int32()
         _lib.check(_lib.lib.moe_layer_dims(self._handle, C.byref(kt), C.byref(ep), C.byref(er)))
@@ -205,8 +208,9 @@ class MoELayer:
 
         if experts is None:
             dev = f"cuda:{self.device}" if weights_on_device else None
-            experts = [GatedExpert(config.input_dim, config.hidden_dim, config.output_dim, config.activation,
-                                   rng=rng, device=dev) if e in self.expert_range else None
+            make = GatedExpert if self.gated else StandardExpert
+            experts = [make(config.input_dim, config.hidden_dim, config.output_dim, config.activation,
+                            rng=rng, device=dev) if e in self.expert_range else None
                        for e in range(config.num_experts)]
         # `experts` may be a callable e -> GatedExpert: each expert is then built, copied to the
         # device and dropped, so the host (or torch) copy of a large layer never exists at once
@@ -239,11 +243,40 @@ class MoELayer:
             ex = self._expert_factory(e) if self._expert_factory else self.experts[e]
             p1, d1, l1, dev1, k1 = _weight_ptr_layout(ex.w1)
             p2, d2, l2, dev2, k2 = _weight_ptr_layout(ex.w2)
+            if not self.gated:
+                if not (d1 == d2 and l1 == l2 and dev1 == dev2):
+                    raise _lib.MoEError(_lib.ERR_INVALID, "w1, w2 of an expert must share dtype, layout and device")
+                pb1, kb1 = self._bias_ptr(ex.b1, ex.hidden_dim, dev1)
+                pb2, kb2 = self._bias_ptr(ex.b2, ex.output_dim, dev1)
+                _lib.check(_lib.lib.moe_layer_set_expert_standard(self._handle, e, p1, pb1, p2, pb2, d1, l1, dev1))
+                continue
             p3, d3, l3, dev3, k3 = _weight_ptr_layout(ex.w3)
             if not (d1 == d2 == d3 and l1 == l2 == l3 and dev1 == dev2 == dev3):
                 raise _lib.MoEError(_lib.ERR_INVALID, "w1, w2, w3 of an expert must share dtype, layout and device")
             _lib.check(_lib.lib.moe_layer_set_expert(self._handle, e, p1, p2, p3, d1, l1, dev1))
         self.sync_router()
+
+    def _bias_ptr(self, b, n: int, on_device: int):
+        """Pointer to a float32 copy of bias vector ``b`` in the memory kind of the weights."""
+        if b is None:
+            return None, None
+        if _is_torch(b):
+            import torch
+
+            keep = b.detach().to(dtype=torch.float32).contiguous()
+            keep = keep.cuda(self.device) if on_device else keep.cpu()
+            ptr, size = keep.data_ptr(), keep.numel()
+        elif on_device:
+            import torch
+
+            keep = torch.as_tensor(np.asarray(b, dtype=np.float32)).cuda(self.device)
+            ptr, size = keep.data_ptr(), keep.numel()
+        else:
+            keep = np.ascontiguousarray(b, dtype=np.float32)
+            ptr, size = keep.ctypes.data, keep.size
+        if size != n:
+            raise _lib.MoEError(_lib.ERR_INVALID, f"expert bias must have {n} entries, got {size}")
+        return ptr, keep
 
     def sync_router(self) -> None:
         w = self.router.weight

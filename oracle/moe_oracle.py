@@ -216,6 +216,34 @@ def gated_expert_forward(e: GatedExpertWeights, x: np.ndarray, act: Callable) ->
 
 
 @dataclass
+class StandardExpertWeights:
+    """StandardExpert (src/experts/standard.jl:8-36): w1 (H, D), w2 (O, H), b1 (H,) / b2 (O,) or None."""
+    w1: np.ndarray
+    w2: np.ndarray
+    b1: Optional[np.ndarray] = None
+    b2: Optional[np.ndarray] = None
+
+
+def standard_expert_forward(e: StandardExpertWeights, x: np.ndarray, act: Callable) -> np.ndarray:
+    """(expert::StandardExpert)(x; training=false) (src/experts/standard.jl:38-55):
+    w2(act.(w1 x .+ b1)) .+ b2; the Dropout branch only runs when training.  x (n, D) -> (n, O)."""
+    h = x @ e.w1.T
+    if e.b1 is not None:
+        h = h + e.b1.astype(h.dtype)
+    y = act(h) @ e.w2.T
+    if e.b2 is not None:
+        y = y + e.b2.astype(y.dtype)
+    return y
+
+
+def expert_forward(e, x: np.ndarray, act: Callable) -> np.ndarray:
+    """Dispatch on the expert's type, like Julia's call overloads."""
+    if isinstance(e, StandardExpertWeights):
+        return standard_expert_forward(e, x, act)
+    return gated_expert_forward(e, x, act)
+
+
+@dataclass
 class MoEConfig:
     """The MoEConfig fields the forward reads (src/core/moe_layer.jl:4-29)."""
     num_experts: int = 8
@@ -276,7 +304,7 @@ def process_expert_forward(output: np.ndarray, experts: List[GatedExpertWeights]
             continue
         tokens = tok[sel]
         weights = flat_g[sel].astype(output.dtype)
-        y = gated_expert_forward(experts[eid - 1], x[tokens], act)
+        y = expert_forward(experts[eid - 1], x[tokens], act)
         # a token can list the same expert at most once per slot; np.add.at keeps duplicates right
         np.add.at(output, tokens, weights[:, None] * y.astype(output.dtype))
 
@@ -335,7 +363,7 @@ def forward_with_shared_experts(cfg: MoEConfig, w: MoEWeights, x: np.ndarray, tr
     xd = x.astype(dtype)
     shared = np.zeros((T, cfg.output_dim), dtype=dtype)
     for i in range(S):
-        shared += gated_expert_forward(w.experts[i], xd, act) / dtype(S)
+        shared += expert_forward(w.experts[i], xd, act) / dtype(S)
     indices, gates, probs, logits = router_forward(cfg, w, x, dtype)
     routed = np.zeros((T, cfg.output_dim), dtype=dtype)
     process_expert_forward(routed, w.experts[S:], xd, indices, gates, act)
@@ -411,8 +439,9 @@ def glorot_uniform(rng, out_dim, in_dim):
 
 
 def make_layer_inputs(seed: int, T: int, D: int, H: int, O: int, E: int, *, e_router: Optional[int] = None,
-                      init: str = "glorot", std: float = 0.02, bf16: bool = False):
-    """Seeded generator (NumPy PCG64): draws x, the router, then per expert w1, w3, w2.
+                      init: str = "glorot", std: float = 0.02, bf16: bool = False, expert_kind: str = "gated"):
+    """Seeded generator (NumPy PCG64): draws x, the router, then per expert w1, w3, w2
+    (expert_kind='standard': w1, w2, then b1, b2 ~ N(0, 0.1^2), kept float32).
     init='glorot' -> Glorot-uniform; init='normal' -> N(0, std^2).  bf16=True rounds x and the
     expert weights to bfloat16-representable float32 values (the router stays float32)."""
     rng = np.random.Generator(np.random.PCG64(seed))
@@ -427,11 +456,19 @@ def make_layer_inputs(seed: int, T: int, D: int, H: int, O: int, E: int, *, e_ro
     experts = []
     for _ in range(E):
         w1 = mk(H, D)
+        if expert_kind == "standard":
+            w2 = mk(O, H)
+            b1 = rng.standard_normal(H, dtype=np.float32) * np.float32(0.1)
+            b2 = rng.standard_normal(O, dtype=np.float32) * np.float32(0.1)
+            experts.append(StandardExpertWeights(w1=w1, w2=w2, b1=b1, b2=b2))
+            continue
         w3 = mk(H, D)
         w2 = mk(O, H)
         experts.append(GatedExpertWeights(w1=w1, w2=w2, w3=w3))
     if bf16:
         x = bf16_round(x)
         for e in experts:
-            e.w1, e.w2, e.w3 = bf16_round(e.w1), bf16_round(e.w2), bf16_round(e.w3)
+            e.w1, e.w2 = bf16_round(e.w1), bf16_round(e.w2)
+            if isinstance(e, GatedExpertWeights):
+                e.w3 = bf16_round(e.w3)
     return x, MoEWeights(router=router, experts=experts)

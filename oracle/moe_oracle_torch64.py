@@ -47,7 +47,8 @@ def topk_passes(probs: torch.Tensor, k: int):
 
 def layer_forward64(x, router, experts, *, k, activation="silu", alpha=0.01, z_weight=0.001,
                     training=True, num_shared_gating=0, logit_bias=None, bias_gates_only=False):
-    """x (T,D); router (E_r,D); experts list of (w1,w2,w3) with shapes (H,D),(O,H),(H,D).
+    """x (T,D); router (E_r,D); experts list of (w1,w2,w3) with shapes (H,D),(O,H),(H,D),
+    or of (w1,w2,b1,b2) for standard experts.
     num_shared_gating=S>0 reproduces SharedExpertGating(S, TopKGating(k), E)
     (src/gating/advanced.jl:80-108) inside forward_standard.
     Returns output (T,O), loss, 0-based indices (T,k_tot), gates, probs -- all float64."""
@@ -89,13 +90,16 @@ def layer_forward64(x, router, experts, *, k, activation="silu", alpha=0.01, z_w
     gate_matrix.scatter_add_(1, idx, g)
     O = experts[0][1].shape[0]
     out = torch.zeros((T, O), dtype=torch.float64)
-    for e, (w1, w2, w3) in enumerate(experts):
+    for e, ws in enumerate(experts):
         if not bool((gate_matrix[:, e] != 0).any()):
             continue
-        w1 = torch.as_tensor(w1, dtype=torch.float64)
-        w2 = torch.as_tensor(w2, dtype=torch.float64)
-        w3 = torch.as_tensor(w3, dtype=torch.float64)
-        y = (_act(activation, x @ w1.T) * (x @ w3.T)) @ w2.T
+        f64 = lambda a: torch.as_tensor(a, dtype=torch.float64)
+        if len(ws) == 4:      # StandardExpert (w1, w2, b1, b2): w2(act.(w1 x .+ b1)) .+ b2
+            w1, w2, b1, b2 = (f64(a) for a in ws)
+            y = _act(activation, x @ w1.T + b1) @ w2.T + b2
+        else:
+            w1, w2, w3 = (f64(a) for a in ws)
+            y = (_act(activation, x @ w1.T) * (x @ w3.T)) @ w2.T
         out += gate_matrix[:, e:e + 1] * y
 
     loss = torch.zeros((), dtype=torch.float64)

@@ -39,12 +39,19 @@ def make_device_layer(weights: orc.MoEWeights, *, D, H, O, gate, activation="sil
     import mixtureofexperts_b200 as m
 
     act = {"silu": m.silu, "gelu": m.gelu, "relu": m.relu, "identity": m.identity}[activation]
-    cfg = m.create_moe_config(num_experts=len(weights.experts), expert_type="gated", input_dim=D, hidden_dim=H,
+    standard = isinstance(weights.experts[0], orc.StandardExpertWeights)
+    cfg = m.create_moe_config(num_experts=len(weights.experts), expert_type="standard" if standard else "gated", input_dim=D, hidden_dim=H,
                               output_dim=O, activation=act, gate_type=gate,
                               balance_loss=balance_loss or m.SwitchTransformerLoss(alpha), z_loss_weight=z,
                               num_shared_experts=num_shared_experts, **config_extra)
     experts = []
     for e in weights.experts:
+        if standard:
+            ex = m.StandardExpert.__new__(m.StandardExpert)
+            ex.input_dim, ex.hidden_dim, ex.output_dim, ex.activation = D, H, O, act
+            ex.w1, ex.w2, ex.b1, ex.b2 = e.w1, e.w2, e.b1, e.b2
+            experts.append(ex)
+            continue
         ex = m.GatedExpert.__new__(m.GatedExpert)
         ex.input_dim, ex.hidden_dim, ex.output_dim, ex.activation = D, H, O, act
         ex.w1, ex.w2, ex.w3 = e.w1, e.w2, e.w3

@@ -33,7 +33,7 @@ def test_binding_lists_every_declared_symbol(lib_built):
 def test_config_struct_matches_header(lib_built):
     from mixtureofexperts_b200 import _lib
 
-    assert C.sizeof(_lib.MoeConfig) == 16 * 4
+    assert C.sizeof(_lib.MoeConfig) == 17 * 4
     assert C.sizeof(_lib.ForwardOutputs) == 7 * C.sizeof(C.c_void_p)
 
 
@@ -44,7 +44,7 @@ def test_invalid_configs_are_rejected_on_the_host(lib_built):
         base = dict(num_experts=8, num_shared=0, top_k=2, input_dim=64, hidden_dim=128, output_dim=64,
                     gate_kind=_lib.GATE_TOPK, activation=_lib.ACT_SILU, compute_dtype=_lib.DTYPE_F32,
                     shared_mode=_lib.SHARED_NONE, balance_alpha=0.01, z_loss_weight=0.001, index_base=1,
-                    bias_gates_only=0, capacity_factor=1.25, drop_tokens=0)
+                    bias_gates_only=0, capacity_factor=1.25, drop_tokens=0, expert_kind=0)
         base.update(kw)
         cfg = _lib.MoeConfig(**base)
         h = C.c_void_p()

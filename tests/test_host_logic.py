@@ -67,3 +67,18 @@ def test_gated_expert_init_scale(lib_built):
     # all three use sigma = sqrt(2/input_dim) (src/experts/gated.jl:16-24)
     for w in (e.w1, e.w2, e.w3):
         assert abs(float(w.std()) - (2.0 / 256) ** 0.5) < 0.01
+
+
+def test_standard_expert_init_scale_and_bias(lib_built):
+    import mixtureofexperts_b200 as m
+
+    e = m.StandardExpert(256, 512, 128, m.gelu, rng=0)
+    assert e.w1.shape == (512, 256) and e.w2.shape == (128, 512)
+    # sigma1 = sqrt(2/input_dim), sigma2 = sqrt(2/hidden_dim), zero biases (src/experts/standard.jl:21-32)
+    assert abs(float(e.w1.std()) - (2.0 / 256) ** 0.5) < 0.01
+    assert abs(float(e.w2.std()) - (2.0 / 512) ** 0.5) < 0.01
+    assert e.b1.shape == (512,) and e.b2.shape == (128,) and not e.b1.any() and not e.b2.any()
+    nb = m.StandardExpert(8, 8, 8, m.gelu, bias=False)
+    assert nb.b1 is None and nb.b2 is None
+    with pytest.raises(ValueError):
+        m.StandardExpert(8, 8, 8, m.gelu, dropout=0.1)

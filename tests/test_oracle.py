@@ -69,6 +69,30 @@ def test_gated_expert_matches_inline_matvecs():
     assert np.abs(got - want).max() < 1e-5
 
 
+@pytest.mark.parametrize("activation", ["gelu", "relu", "silu"])
+def test_standard_expert_agrees_with_float64_restatement(activation):
+    """StandardExpert (src/experts/standard.jl:38-55) through the whole layer against the
+    independent float64 restatement, and its single-expert form against inline matvecs."""
+    T, D, H, O, E = 64, 48, 80, 40, 6
+    x, w = orc.make_layer_inputs(11, T, D, H, O, E, init="normal", std=0.2, expert_kind="standard")
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation=activation,
+                        gate_type=orc.TopKGating(2))
+    out, loss, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+    o64, l64, i64, _, _ = layer_forward64(x, w.router, [(e.w1, e.w2, e.b1, e.b2) for e in w.experts], k=2,
+                                          activation=activation, alpha=cfg.balance_alpha, z_weight=cfg.z_loss_weight,
+                                          training=True)
+    assert np.array_equal(aux["indices"] - 1, i64.numpy())
+    assert rel_inf(out, o64.numpy()) < 1e-5
+    assert abs(float(loss) - float(l64)) < 1e-5 * abs(float(l64))
+    e = w.experts[0]
+    h = e.w1 @ x[0] + e.b1
+    want = e.w2 @ orc.ACTIVATIONS[activation](h) + e.b2
+    assert np.abs(orc.standard_expert_forward(e, x[:1], orc.ACTIVATIONS[activation])[0] - want).max() < 1e-5
+    e.b1 = e.b2 = None
+    assert np.abs(orc.standard_expert_forward(e, x[:1], orc.ACTIVATIONS[activation])[0]
+                  - e.w2 @ orc.ACTIVATIONS[activation](e.w1 @ x[0])).max() < 1e-5
+
+
 def test_topk_ties_go_to_lowest_index():
     logits = np.array([[0.5, 2.0, 2.0, 2.0, -1.0]], dtype=np.float32)
     idx, gates, _ = orc.compute_gates(orc.TopKGating(2), logits)

@@ -31,10 +31,11 @@ def logits64(x, w, bias=None):
 
 
 def run_case(T, D, H, O, E, gate_kind, k, S=0, *, seed=0, activation="silu", compute="f32", z=0.001,
-             num_shared_experts=0, init="normal", std=0.25, host=False, training=True, tol=None, x_bf16=None):
+             num_shared_experts=0, init="normal", std=0.25, host=False, training=True, tol=None, x_bf16=None, expert_kind="gated"):
     bf16 = compute == "bf16"
     e_router = E - num_shared_experts
-    x, w = orc.make_layer_inputs(seed, T, D, H, O, E, e_router=e_router, init=init, std=std, bf16=bf16)
+    x, w = orc.make_layer_inputs(seed, T, D, H, O, E, e_router=e_router, init=init, std=std, bf16=bf16,
+                                 expert_kind=expert_kind)
     ogate = oracle_gate(gate_kind, k, S, E)
     cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation=activation,
                         gate_type=ogate, balance_alpha=0.01, z_loss_weight=z, num_shared_experts=num_shared_experts)
@@ -357,6 +358,59 @@ def test_exact_ties_go_to_the_lowest_index():
     logits = np.array([[0.5, 2.0, 2.0, 2.0, -1.0], [1.0, 1.0, 1.0, 1.0, 1.0]], dtype=np.float32)
     di, dg, _ = m.compute_gates(m.TopKGating(2), torch.from_numpy(logits).cuda().t())
     assert di.cpu().numpy().T.tolist() == [[2, 3], [1, 2]]
+
+
+# ---- StandardExpert: w2(act.(w1 x .+ b1)) .+ b2 -------------------------------------------------
+
+@pytest.mark.parametrize("T,E,k,D,H,O,activation", [
+    (257, 8, 2, 64, 96, 48, "gelu"),          # tiled FP32 kernel, MoEConfig's default activation
+    (3, 8, 2, 36, 44, 20, "relu"),            # skinny FP32 kernel
+    (500, 4, 1, 128, 130, 70, "silu"),
+])
+@pytest.mark.parametrize("host", [False, True])
+def test_f32_standard_expert(T, E, k, D, H, O, activation, host):
+    run_case(T, D, H, O, E, "topk", k, seed=T + 7, activation=activation, expert_kind="standard", host=host)
+
+
+def test_f32_standard_expert_with_layer_blend_and_without_bias():
+    run_case(130, 64, 96, 64, 6, "topk", 2, seed=5, activation="gelu", expert_kind="standard", num_shared_experts=2)
+    import mixtureofexperts_b200 as m
+
+    T, D, H, O, E = 100, 32, 48, 24, 4
+    x, w = orc.make_layer_inputs(3, T, D, H, O, E, init="normal", std=0.25, expert_kind="standard")
+    for e in w.experts:
+        e.b1 = e.b2 = None
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="gelu",
+                        gate_type=orc.TopKGating(2))
+    o_out, _, _ = orc.moe_layer_forward(cfg, w, x, training=False)
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=m.TopKGating(2), activation="gelu")
+    out, _ = layer(np.asfortranarray(x.T))
+    assert rel_inf(out.T, o_out) < F32_TOL
+    layer.close()
+
+
+@pytest.mark.parametrize("pair", ["0", "1"])
+@pytest.mark.parametrize("T,E,k,D,H,O", [(1000, 8, 2, 512, 1024, 512), (300, 4, 1, 136, 200, 104), (3, 66, 2, 128, 256, 128)])
+def test_bf16_standard_expert_on_both_tensor_core_kernels(pair, T, E, k, D, H, O, monkeypatch):
+    monkeypatch.setenv("MOE_B200_PAIR", pair)
+    err = run_case(T, D, H, O, E, "topk", k, seed=T + E, compute="bf16", std=0.05, activation="gelu",
+                   expert_kind="standard")
+    assert err < BF16_TOL
+
+
+def test_standard_expert_setter_is_refused_on_a_gated_layer_and_dropout_is_rejected():
+    import mixtureofexperts_b200 as m
+
+    with pytest.raises(m.MoEError):
+        m.MoELayer(m.create_moe_config(num_experts=2, expert_type="standard", input_dim=8, hidden_dim=8, output_dim=8,
+                                       expert_dropout=0.1))
+    layer = m.MoELayer(m.create_moe_config(num_experts=2, expert_type="gated", input_dim=8, hidden_dim=8, output_dim=8))
+    w = np.zeros((8, 8), dtype=np.float32)
+    from mixtureofexperts_b200 import _lib
+
+    rc = _lib.lib.moe_layer_set_expert_standard(layer._handle, 0, w.ctypes.data, None, w.ctypes.data, None, 0, 0, 0)
+    assert rc == _lib.ERR_STATE
+    layer.close()
 
 
 # ---- BF16 tensor-core path ----------------------------------------------------------------------
