@@ -150,6 +150,12 @@ int moe_layer_set_router(moe_layer_t*, const float* w, const float* logit_bias,
  * comes from the noise-free logits, like the reference's second router pass. */
 int moe_layer_set_router_noise(moe_layer_t*, const float* noise, float noise_scale);
 
+/* Router.noise_weight (src/core/router.jl:20, use_noise_network = true): an (E_router x D) FP32 matrix
+ * in `layout`; once set, armed noise becomes logits + noise_scale * (noise .* softplus(noise_w x))
+ * (router.jl:33-37), the second projection riding in the same gate GEMM.  Call after
+ * moe_layer_set_router; needs 2*E_router <= 128.  NULL removes the network. */
+int moe_layer_set_router_noise_network(moe_layer_t*, const float* noise_w, int layout, int src_is_device);
+
 /* Number of values per token in indices/gates (k_tot), probs (E_probs), logits (E_router). */
 int moe_layer_dims(const moe_layer_t*, int32_t* k_tot, int32_t* e_probs, int32_t* e_router);
 
@@ -170,6 +176,15 @@ int moe_layer_forward_host(moe_layer_t*, const void* x, int x_dtype, int64_t T, 
 int moe_compute_gates(int gate_kind, int num_experts, int num_shared, int top_k, int index_base,
                       const float* logits, int64_t T,
                       int32_t* indices, float* gates, float* probs, void* cuda_stream);
+
+/* compute_gates(JitterGating(base_gate, eps), logits; training = true) (src/gating/switch.jl:20-33):
+ * the base gate on logits .* (1 .+ (2 .* u .- 1) .* eps), `jitter_u` [T][E] being the caller's
+ * uniform [0,1) draws (device).  Inside the layer the reference's Router never passes `training`
+ * to compute_gates, so a JitterGating layer routes exactly like its base gate; this operator serves
+ * direct calls. */
+int moe_compute_gates_jitter(int gate_kind, int num_experts, int num_shared, int top_k, int index_base,
+                             const float* logits, const float* jitter_u, float eps, int64_t T,
+                             int32_t* indices, float* gates, float* probs, void* cuda_stream);
 
 /* compute_loss(SwitchTransformerLoss(alpha), indices, probs) (src/balancing/losses.jl:15-36)
  * plus z_weight * mean(logsumexp(logits)^2) when logits != NULL (losses.jl:103-114).

@@ -127,7 +127,7 @@ gate_kind(::SwitchGating) = (GATE_SWITCH, 1, 0)
 gate_kind(g::SharedExpertGating) = (GATE_SHARED_TOPK, gate_kind(g.base_gate)[2], g.num_shared)
 
 mutable struct MoELayer                              # src/core/moe_layer.jl:34-63
-    experts::Vector{GatedExpert}
+    experts::Vector{Any}                             # GatedExpert or StandardExpert
     router_weight::Matrix{Float32}                   # (E_router x input_dim), Router.weight
     balance_loss::LoadBalancingLoss
     config::MoEConfig

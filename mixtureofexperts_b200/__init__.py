@@ -13,7 +13,7 @@ _EXPORTS = {
     "LIB_PATH": "_lib", "MoEError": "_lib", "version": "_lib",
     "Expert": "experts", "GatedExpert": "experts", "StandardExpert": "experts", "gelu": "experts", "identity": "experts", "relu": "experts",
     "silu": "experts", "swish": "experts",
-    "GatingMechanism": "gating", "SharedExpertGating": "gating", "SwitchGating": "gating", "TopKGating": "gating",
+    "GatingMechanism": "gating", "JitterGating": "gating", "SharedExpertGating": "gating", "SwitchGating": "gating", "TopKGating": "gating",
     "compute_gates": "gating",
     "MoEConfig": "layer", "MoELayer": "layer", "Router": "layer", "create_moe_config": "layer",
     "create_moe_layer": "layer", "load_balance_score": "layer", "reset_stats": "layer",

@@ -21,8 +21,8 @@ LAYOUT_IN_CONTIG, LAYOUT_OUT_CONTIG = 0, 1
 EXPERT_GATED, EXPERT_STANDARD = 0, 1
 
 EXPORTS = [
-    "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_expert_standard", "moe_layer_set_router", "moe_layer_set_router_noise", "moe_layer_dims",
-    "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_loss",
+    "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_expert_standard", "moe_layer_set_router", "moe_layer_set_router_noise", "moe_layer_set_router_noise_network", "moe_layer_dims",
+    "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_gates_jitter", "moe_compute_loss",
     "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_launch_count",
     "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_ep_layout", "moe_layer_destroy",
     "moe_last_error", "moe_version", "moe_route_static", "moe_route_static_scratch_bytes",
@@ -66,12 +66,14 @@ def _load():
     lib.moe_layer_create.argtypes = [C.POINTER(MoeConfig), i32, C.POINTER(vp)]
     lib.moe_layer_set_expert.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32]
     lib.moe_layer_set_expert_standard.argtypes = [vp, i32, vp, vp, vp, vp, i32, i32, i32]
+    lib.moe_layer_set_router_noise_network.argtypes = [vp, vp, i32, i32]
     lib.moe_layer_set_router.argtypes = [vp, vp, vp, i32, i32]
     lib.moe_layer_set_router_noise.argtypes = [vp, vp, f32]
     lib.moe_layer_dims.argtypes = [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.moe_layer_forward.argtypes = [vp, vp, i32, i64, i32, vp, C.POINTER(ForwardOutputs), vp]
     lib.moe_layer_forward_host.argtypes = [vp, vp, i32, i64, i32, vp, C.POINTER(ForwardOutputs)]
     lib.moe_compute_gates.argtypes = [i32, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp]
+    lib.moe_compute_gates_jitter.argtypes = [i32, i32, i32, i32, i32, vp, vp, C.c_float, i64, vp, vp, vp, vp]
     lib.moe_compute_loss.argtypes = [f32, f32, i32, i32, i32, vp, vp, vp, i32, i64, vp, vp]
     lib.moe_layer_set_profiling.argtypes = [vp, i32]
     lib.moe_layer_stage_ms.argtypes = [vp, i32, C.POINTER(C.c_float)]

@@ -39,8 +39,10 @@ struct RouterParams {
     const float* w;           // [E_router][D]
     const float* wt;          // [D_pad][E_pad] K-major zero-padded copy (launch_router_transpose)
     const float* bias;        // [E_router] or null
-    const float* noise;       // [T][E_router] standard-normal draws for training-time router noise, or null
-    float noise_scale;
+    const float* noise = nullptr;   // [T][E_router] standard-normal draws for training-time router noise, or null
+    float noise_scale = 0.f;
+    int noise_off = 0;        // > 0: columns noise_off..noise_off+E_router-1 of wt hold the router's noise
+                              // network and the draws are scaled by softplus of its logits; 0: no network
     int64_t T;
     int D;
     int E;                    // layer experts (shared included)
@@ -135,8 +137,8 @@ struct GroupGemmParams {
     int N, K, E;
     int activation;           // mode 1: activation of the gate branch
     // mode 2 epilogue extras (StandardExpert, src/experts/standard.jl:38-55): C = act(A*B0^T + bias)
-    const float* bias;        // [E][N] FP32 or null
-    int epilogue_act;         // MOE_ACT_* applied after the bias, or -1 for none
+    const float* bias = nullptr;       // [E][N] FP32 or null
+    int epilogue_act = -1;        // MOE_ACT_* applied after the bias, or -1 for none
     const int32_t* expert_offset; // [E+1]
     const int32_t* tile_prefix;   // [E+1]
     int32_t* status;
@@ -166,14 +168,16 @@ int router_tokens_per_cta(int e_router);
 int router_e_pad(int e_router);          // router rows padded to a multiple of 8 (bucketed)
 int router_d_pad(int D);                 // K rows of the K-major copy (multiple of 128)
 int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_t s);
+// wt columns 0..E-1 = w, E..2E-1 = nw (the noise network), padded to router_e_pad(2E)
+int launch_router_transpose_noise(const float* w, const float* nw, float* wt, int E, int D, cudaStream_t s);
 int launch_scan(const ScanParams& p, cudaStream_t s);
 int launch_accumulate(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E, cudaStream_t s);
 int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s);
 int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s);
 int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, int64_t rows, int num_sms,
                           cudaStream_t s);
-int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const float* logits, int64_t T,
-                      int32_t* indices, float* gates, float* probs, cudaStream_t s);
+int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const float* logits, const float* jitter_u,
+                      float eps, int64_t T, int32_t* indices, float* gates, float* probs, cudaStream_t s);
 int launch_loss_only(float alpha, float z_weight, int n_probs, int k, int index_base, const int32_t* indices,
                      const float* probs, const float* logits, int n_logits, int64_t T, float* loss,
                      cudaStream_t s);

@@ -69,6 +69,8 @@ struct moe_layer {
     float* b2 = nullptr;         // [E_local][O]
     float* router_w = nullptr;   // [E_router][D]
     float* router_wt = nullptr;  // [D_pad][E_pad] K-major zero-padded copy read by the router kernel
+    float* router_nw = nullptr;  // [E_router][D] noise network (Router.noise_weight), or null
+    float* router_wt_noise = nullptr;  // [D_pad][e_pad(2 E_router)]: router columns, then noise-network columns
     float* router_bias = nullptr;
     bool has_bias = false, router_set = false;
     const float* noise = nullptr;   // caller-owned device draws for the next training forward
@@ -282,7 +284,7 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
                 const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base, int tile_m,
                 const int32_t* seg_start = nullptr, void* const* seg_dst = nullptr, int seg_per_expert = 0) {
     const moe_config_t& c = L->cfg;
-    GroupGemmParams g;
+    GroupGemmParams g{};
     g.E = n_experts;
     g.activation = c.activation;
     g.expert_offset = expert_offset;
@@ -364,13 +366,18 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     if (L->prof_slots > 0) L->prof_cur = (int)(L->prof_calls++ % L->prof_slots);
     stage_mark(L, 0, s);
 
-    RouterParams r;
+    RouterParams r{};
     r.x = x;
     r.w = L->router_w;
     r.wt = L->router_wt;
     r.bias = L->has_bias ? L->router_bias : nullptr;
     r.noise = (training && L->noise_scale > 0.f) ? L->noise : nullptr;
     r.noise_scale = L->noise_scale;
+    r.noise_off = 0;
+    if (r.noise && L->router_nw) {   // src/core/router.jl:33-37: the draws are scaled by softplus(noise_weight x)
+        r.wt = L->router_wt_noise;
+        r.noise_off = L->E_router;
+    }
     r.T = T;
     r.D = c.input_dim;
     r.E = L->E;
@@ -401,7 +408,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     }
     stage_mark(L, 1, s);
 
-    ScanParams sp;
+    ScanParams sp{};
     sp.T = T;
     sp.E = L->E;
     sp.E_probs = L->E_probs;
@@ -435,7 +442,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     L->launches += n;
     stage_mark(L, 2, s);
 
-    PermuteParams pp;
+    PermuteParams pp{};
     pp.x = x;
     pp.xp = L->xp;
     pp.T = T;
@@ -517,7 +524,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
         if (rc) return rc;
     }
 
-    CombineParams cp;
+    CombineParams cp{};
     cp.y = peer ? plan.yb : L->y;
     cp.out = out;
     cp.T = T;
@@ -617,6 +624,8 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->router_w);
     dev_free(L->router_bias);
     dev_free(L->router_wt);
+    dev_free(L->router_nw);
+    dev_free(L->router_wt_noise);
     dev_free(L->stage_w);
     dev_free(L->expert_count);
     dev_free(L->expert_offset);
@@ -739,6 +748,12 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     const int n2 = launch_router_transpose(L->router_w, L->router_wt, L->E_router, L->cfg.input_dim, L->stream);
     if (n2 < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n2;
+    if (L->router_nw) {
+        const int n3 = launch_router_transpose_noise(L->router_w, L->router_nw, L->router_wt_noise, L->E_router,
+                                                     L->cfg.input_dim, L->stream);
+        if (n3 < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n3;
+    }
     if (logit_bias) {
         CUDA_TRY(cudaMemcpyAsync(L->router_bias, logit_bias, sizeof(float) * L->E_router,
                                  src_is_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, L->stream));
@@ -748,6 +763,44 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     }
     CUDA_TRY(cudaStreamSynchronize(L->stream));
     L->router_set = true;
+    return MOE_OK;
+}
+
+int moe_layer_set_router_noise_network(moe_layer_t* L, const float* noise_w, int layout, int src_is_device) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    CUDA_TRY(cudaSetDevice(L->device));
+    if (!noise_w) {   // back to plain Gaussian noise
+        CUDA_TRY(cudaStreamSynchronize(L->stream));
+        dev_free(L->router_nw);
+        dev_free(L->router_wt_noise);
+        L->router_nw = L->router_wt_noise = nullptr;
+        return MOE_OK;
+    }
+    if (layout != MOE_LAYOUT_IN_CONTIG && layout != MOE_LAYOUT_OUT_CONTIG) return fail(MOE_ERR_INVALID, "unknown layout");
+    if (!L->router_set) return fail(MOE_ERR_STATE, "set the router weights before its noise network");
+    if (2 * L->E_router > MAX_ROUTER_EXPERTS)
+        return fail(MOE_ERR_UNSUPPORTED, "a router noise network needs 2*%d <= %d router rows", L->E_router, MAX_ROUTER_EXPERTS);
+    if (src_is_device) CUDA_TRY(cudaDeviceSynchronize());   // see moe_layer_set_expert
+    const size_t D = L->cfg.input_dim;
+    const size_t bytes = (size_t)L->E_router * D * sizeof(float);
+    int rc;
+    if (!L->router_nw) {
+        if ((rc = dev_alloc(&L->router_nw, (size_t)L->E_router * D))) return rc;
+        if ((rc = dev_alloc(&L->router_wt_noise, (size_t)router_e_pad(2 * L->E_router) * router_d_pad((int)D)))) return rc;
+    }
+    const void* src = noise_w;
+    if (!src_is_device) {
+        if ((rc = grow(&L->stage_w, &L->stage_w_bytes, bytes))) return rc;
+        CUDA_TRY(cudaMemcpyAsync(L->stage_w, noise_w, bytes, cudaMemcpyHostToDevice, L->stream));
+        src = L->stage_w;
+    }
+    const int n = launch_transpose_convert(src, MOE_DTYPE_F32, L->router_nw, MOE_DTYPE_F32, L->E_router, (int)D,
+                                           layout == MOE_LAYOUT_OUT_CONTIG, L->stream);
+    if (n < 0) return fail(MOE_ERR_CUDA, "router repack launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    const int n2 = launch_router_transpose_noise(L->router_w, L->router_nw, L->router_wt_noise, L->E_router, (int)D, L->stream);
+    if (n2 < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n + n2;
+    CUDA_TRY(cudaStreamSynchronize(L->stream));
     return MOE_OK;
 }
 
@@ -916,8 +969,9 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     return MOE_OK;
 }
 
-int moe_compute_gates(int gate_kind, int num_experts, int num_shared, int top_k, int index_base, const float* logits,
-                      int64_t T, int32_t* indices, float* gates, float* probs, void* cuda_stream) {
+static int compute_gates_impl(int gate_kind, int num_experts, int num_shared, int top_k, int index_base,
+                              const float* logits, const float* jitter_u, float eps, int64_t T, int32_t* indices,
+                              float* gates, float* probs, void* cuda_stream) {
     if (gate_kind < MOE_GATE_TOPK || gate_kind > MOE_GATE_SHARED_TOPK) return fail(MOE_ERR_INVALID, "unknown gate_kind");
     if (num_experts < 1 || num_experts > MAX_ROUTER_EXPERTS)
         return fail(MOE_ERR_UNSUPPORTED, "num_experts must be in 1..%d", MAX_ROUTER_EXPERTS);
@@ -929,10 +983,25 @@ int moe_compute_gates(int gate_kind, int num_experts, int num_shared, int top_k,
     if (index_base != 0 && index_base != 1) return fail(MOE_ERR_INVALID, "index_base must be 0 or 1");
     if (T < 0 || (T > 0 && !logits)) return fail(MOE_ERR_INVALID, "bad logits/T");
     if (T == 0) return MOE_OK;
-    if (launch_gates_only(gate_kind, num_experts, S, k, index_base, logits, T, indices, gates, probs,
+    if (launch_gates_only(gate_kind, num_experts, S, k, index_base, logits, jitter_u, eps, T, indices, gates, probs,
                           reinterpret_cast<cudaStream_t>(cuda_stream)) < 0)
         return fail(MOE_ERR_CUDA, "compute_gates launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return MOE_OK;
+}
+
+int moe_compute_gates(int gate_kind, int num_experts, int num_shared, int top_k, int index_base, const float* logits,
+                      int64_t T, int32_t* indices, float* gates, float* probs, void* cuda_stream) {
+    return compute_gates_impl(gate_kind, num_experts, num_shared, top_k, index_base, logits, nullptr, 0.f, T, indices,
+                              gates, probs, cuda_stream);
+}
+
+int moe_compute_gates_jitter(int gate_kind, int num_experts, int num_shared, int top_k, int index_base,
+                             const float* logits, const float* jitter_u, float eps, int64_t T, int32_t* indices,
+                             float* gates, float* probs, void* cuda_stream) {
+    if (T > 0 && !jitter_u) return fail(MOE_ERR_INVALID, "jitter_u must not be null");
+    if (!(eps >= 0.f)) return fail(MOE_ERR_INVALID, "eps must be non-negative");
+    return compute_gates_impl(gate_kind, num_experts, num_shared, top_k, index_base, logits, jitter_u, eps, T, indices,
+                              gates, probs, cuda_stream);
 }
 
 int moe_compute_loss(float alpha, float z_weight, int n_probs, int k, int index_base, const int32_t* indices,

@@ -105,13 +105,14 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
                  cudaGetErrorString(cudaGetLastError()));
         return MOE_ERR_CUDA;
     }
-    RouterParams r;
+    RouterParams r{};
     r.x = x;
     r.w = router_w;
     r.wt = wt;
     r.bias = logit_bias;
     r.noise = nullptr;
     r.noise_scale = 0.f;
+    r.noise_off = 0;
     r.T = T;
     r.D = input_dim;
     r.E = num_experts;
@@ -138,7 +139,7 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
         snprintf(g_static_err, sizeof(g_static_err), "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         return MOE_ERR_CUDA;
     }
-    ScanParams sp;
+    ScanParams sp{};
     sp.T = T;
     sp.E = num_experts;
     sp.E_probs = num_experts;

@@ -25,6 +25,7 @@ struct GateCtx {
     int idx_base;     // base added to the ids stored through `idx` (0 inside the layer)
     const float* noise;   // [T][E_router] standard-normal draws or null; scaled by noise_scale
     float noise_scale;
+    int noise_net;        // draws are multiplied by softplus(noise-network logit) (src/core/router.jl:34-37)
     const float* bias;
     int32_t* idx;
     float* gate;
@@ -53,9 +54,10 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 // One token, one warp.  lg[j] is the raw logit of router column lane + 32*j.
 // Accumulators (per warp, lane-owned columns): s_psum[e] += prob, returns lse^2 and entropy.
 template <int NJ>
-__device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ], int lane,
-                                           int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc) {
-    // Training-time router noise (src/core/router.jl:32-41): logits + noise_scale * randn feed the
+__device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ],
+                                           const float (&nl)[NJ], int lane, int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc) {
+    // Training-time router noise (src/core/router.jl:32-41): logits + noise_scale * randn (times
+    // softplus(noise_weight x) when the router has a noise network, nl[] = those logits) feed the
     // gate and are the logits the router returns; the z-loss is computed by a second, noise-free
     // router pass in the reference (src/core/moe_layer.jl:117-121), hence from the clean logits.
     float lsel[NJ], lprob[NJ], lclean[NJ];
@@ -65,7 +67,13 @@ __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const fl
         const int e = lane + 32 * j;
         const bool in = e < c.E_router;
         const float b = (in && c.bias) ? c.bias[e] : 0.f;
-        const float nz = (in && c.noise) ? c.noise_scale * c.noise[t * c.E_router + e] : 0.f;
+        float nz = 0.f;
+        if (in && c.noise) {
+            float draw = c.noise[t * c.E_router + e];
+            // NNlib.softplus(x) = log1p(exp(-|x|)) + relu(x)
+            if (c.noise_net) draw *= log1pf(expf(-fabsf(nl[j]))) + fmaxf(nl[j], 0.f);
+            nz = c.noise_scale * draw;
+        }
         const float noisy = lg_in[j] + nz;
         lsel[j] = noisy + b;
         lprob[j] = c.bias_gates_only ? noisy : lsel[j];
@@ -231,6 +239,7 @@ __device__ __forceinline__ GateCtx make_ctx(const RouterParams& p) {
     c.idx_base = 0;
     c.noise = p.noise;
     c.noise_scale = p.noise_scale;
+    c.noise_net = p.noise_off > 0;
     c.bias = p.bias;
     c.idx = p.idx;
     c.gate = p.gate;
@@ -438,18 +447,23 @@ router_kernel(const RouterParams p) {
     for (int tok = warp; tok < RT_BT; tok += NWARPS) {
         const int64_t t = tok0 + tok;
         if (t >= p.T) break;
-        float lg[NJ];
+        float lg[NJ], nl[NJ];
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             const int e = lane + 32 * j;
-            float s = 0.f;
+            float s = 0.f, sn = 0.f;
             if (e < E_PAD) {
 #pragma unroll
                 for (int q = 0; q < KS; ++q) s += sm.red[((size_t)q * RT_BT + tok) * E_PAD + e];
             }
+            if (p.noise_off > 0 && e < p.E_router) {
+#pragma unroll
+                for (int q = 0; q < KS; ++q) sn += sm.red[((size_t)q * RT_BT + tok) * E_PAD + p.noise_off + e];
+            }
             lg[j] = s;
+            nl[j] = sn;
         }
-        gate_token<NJ>(c, t, lg, lane, s_cnt, s_psum[warp], lse2, ent);
+        gate_token<NJ>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
     }
     if (lane == 0) {
         s_lse2[warp] = lse2;
@@ -484,23 +498,43 @@ __global__ void router_transpose_kernel(const float* w, float* wt, int E, int D,
     }
 }
 
+// the same with the noise network's rows behind the router's: column E + e = nw[e]
+__global__ void router_transpose_noise_kernel(const float* w, const float* nw, float* wt, int E, int D, int E_pad,
+                                              int D_pad) {
+    const size_t n = (size_t)E_pad * D_pad;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int k = (int)(i / E_pad), e = (int)(i % E_pad);
+        float v = 0.f;
+        if (k < D && e < E) v = w[(size_t)e * D + k];
+        else if (k < D && e < 2 * E) v = nw[(size_t)(e - E) * D + k];
+        wt[i] = v;
+    }
+}
+
 // compute_gates as a stand-alone operator on given logits: one warp per token.
-__global__ void __launch_bounds__(ROUTER_THREADS) gates_only_kernel(GateCtx c, const float* logits, int64_t T) {
+__global__ void __launch_bounds__(ROUTER_THREADS) gates_only_kernel(GateCtx c, const float* logits, const float* jitter_u,
+                                                                     float eps, int64_t T) {
     __shared__ int s_cnt[MAX_EXPERTS];
     __shared__ float s_psum[ROUTER_WARPS][MAX_EXPERTS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t t = (int64_t)blockIdx.x * ROUTER_WARPS + warp;
     if (t >= T) return;
     constexpr int NJ = MAX_ROUTER_EXPERTS / 32;
-    float lg[NJ];
+    float lg[NJ], nl[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int e = lane + 32 * j;
         lg[j] = (e < c.E_router) ? logits[t * c.E_router + e] : 0.f;
+        // JitterGating (src/gating/switch.jl:28-31): logits .* (1 .+ (2 .* rand .- 1) .* eps), each step rounded
+        if (jitter_u && e < c.E_router) {
+            const float u = jitter_u[t * c.E_router + e];
+            lg[j] = __fmul_rn(lg[j], __fadd_rn(1.0f, __fmul_rn(__fsub_rn(__fmul_rn(2.0f, u), 1.0f), eps)));
+        }
+        nl[j] = 0.f;
     }
     float lse2 = 0.f;
     double ent = 0.0;
-    gate_token<NJ>(c, t, lg, lane, s_cnt, s_psum[warp], lse2, ent);
+    gate_token<NJ>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
 }
 
 template <int E_PAD, int BK, int KS, typename XT>
@@ -544,9 +578,17 @@ int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
+int launch_router_transpose_noise(const float* w, const float* nw, float* wt, int E, int D, cudaStream_t s) {
+    const int e_pad = router_e_pad(2 * E), d_pad = router_d_pad(D);
+    const size_t n = (size_t)e_pad * d_pad;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    router_transpose_noise_kernel<<<blocks, 256, 0, s>>>(w, nw, wt, E, D, e_pad, d_pad);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s) {
-    // <E_PAD, BK, KS>: 16 * E_PAD/8 * KS threads
-    switch (router_e_pad(p.E_router)) {
+    // <E_PAD, BK, KS>: 16 * E_PAD/8 * KS threads; with a noise network the GEMM is 2*E_router wide
+    switch (router_e_pad(p.noise_off > 0 ? 2 * p.E_router : p.E_router)) {
         case 8: return launch_router_e<8, 128, 16>(p, x_dtype, num_cta, s);
         case 16: return launch_router_e<16, 128, 8>(p, x_dtype, num_cta, s);
         case 24: return launch_router_e<24, 128, 4>(p, x_dtype, num_cta, s);
@@ -561,8 +603,8 @@ int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t 
     }
 }
 
-int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const float* logits, int64_t T,
-                      int32_t* indices, float* gates, float* probs, cudaStream_t s) {
+int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const float* logits, const float* jitter_u,
+                      float eps, int64_t T, int32_t* indices, float* gates, float* probs, cudaStream_t s) {
     // Scratch-free variant: idx/gate go straight to the caller's arrays.
     GateCtx c;
     const bool shared = gate_kind == MOE_GATE_SHARED_TOPK;
@@ -582,6 +624,7 @@ int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const 
     c.idx_base = index_base;
     c.noise = nullptr;
     c.noise_scale = 0.f;
+    c.noise_net = 0;
     c.idx = indices;
     c.gate = gates;
     c.u_idx = nullptr;
@@ -589,7 +632,7 @@ int launch_gates_only(int gate_kind, int E, int S, int k, int index_base, const 
     c.u_probs = probs;
     c.u_logits = nullptr;
     const int blocks = (int)((T + ROUTER_WARPS - 1) / ROUTER_WARPS);
-    gates_only_kernel<<<blocks, ROUTER_THREADS, 0, s>>>(c, logits, T);
+    gates_only_kernel<<<blocks, ROUTER_THREADS, 0, s>>>(c, logits, jitter_u, eps, T);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 

@@ -98,8 +98,8 @@ class Router:
         self.gate_type = gate_type
         self.noise_scale = float(noise_scale)
         self.use_fp32 = bool(use_fp32)
-        if use_noise_network:
-            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "the router noise network is not accelerated (use_noise_network)")
+        if use_noise_network:    # a second Dense(input_dim, num_experts, bias=false) (src/core/router.jl:20)
+            self.noise_weight = g.uniform(-lim, lim, size=(num_experts, input_dim)).astype(np.float32)
 
 
 def _is_torch(x) -> bool:
@@ -308,6 +308,14 @@ class MoELayer:
             if n != self.e_router:
                 raise _lib.MoEError(_lib.ERR_INVALID, f"router bias must have {self.e_router} entries")
         _lib.check(_lib.lib.moe_layer_set_router(self._handle, p, bias_ptr, lay, dev))
+        nw = getattr(self.router, "noise_weight", None)
+        if nw is not None:
+            pn, dn, layn, devn, keep_n = _weight_ptr_layout(nw)
+            if dn != _lib.DTYPE_F32:
+                raise _lib.MoEError(_lib.ERR_INVALID, "router noise weights must be float32")
+            _lib.check(_lib.lib.moe_layer_set_router_noise_network(self._handle, pn, layn, devn))
+        else:
+            _lib.check(_lib.lib.moe_layer_set_router_noise_network(self._handle, None, 0, 0))
 
     # -- forward ---------------------------------------------------------------------------
     def __call__(self, x, training: bool = False, return_stats: bool = False, return_routing: bool = False,

@@ -96,6 +96,13 @@ class SharedExpertGating:
     num_experts: int
 
 
+@dataclass
+class JitterGating:
+    """src/gating/switch.jl:20-23 (positional: base_gate, ε)"""
+    base_gate: object
+    eps: float
+
+
 def compute_gates_topk(k: int, logits: np.ndarray):
     """compute_gates(::TopKGating, logits) (src/gating/topk.jl:24-44).
     logits (T, E) -> indices (T, k) int64 1-based, gates (T, k) float32, probs (T, E)."""
@@ -134,8 +141,15 @@ def compute_gates_shared(gate: SharedExpertGating, logits: np.ndarray):
     return indices, gates, probs
 
 
-def compute_gates(gate, logits: np.ndarray):
-    """Dispatch of compute_gates (src/gating/base.jl:22)."""
+def compute_gates(gate, logits: np.ndarray, training: bool = False, jitter_u: Optional[np.ndarray] = None):
+    """Dispatch of compute_gates (src/gating/base.jl:22).  `training` / `jitter_u` (the rand(Float32)
+    draws) only reach JitterGating (src/gating/switch.jl:25-33), whose jitter is evaluated in Float32."""
+    if isinstance(gate, JitterGating):
+        if training:
+            f = np.float32
+            jit = f(1.0) + (f(2.0) * jitter_u.astype(f) - f(1.0)) * f(gate.eps)
+            logits = logits * jit.astype(logits.dtype)
+        return compute_gates(gate.base_gate, logits)
     if isinstance(gate, TopKGating):
         return compute_gates_topk(gate.k, logits)
     if isinstance(gate, SwitchGating):
@@ -274,16 +288,26 @@ class MoEConfig:
 class MoEWeights:
     router: np.ndarray                     # (E_router, D) float32  (Router.weight, router.jl:18)
     experts: List[GatedExpertWeights]
+    noise_weight: Optional[np.ndarray] = None   # (E_router, D) float32  (Router.noise_weight, router.jl:20)
+
+
+def softplus(x: np.ndarray) -> np.ndarray:
+    """NNlib.softplus: log1p(exp(-|x|)) + relu(x)."""
+    return np.log1p(np.exp(-np.abs(x))) + np.maximum(x, 0)
 
 
 def router_forward(cfg: MoEConfig, w: MoEWeights, x: np.ndarray, dtype=np.float32, training: bool = False):
-    """(router::Router)(x; training) (src/core/router.jl:25-46), without a noise network."""
+    """(router::Router)(x; training) (src/core/router.jl:25-46); cfg.router_noise holds the randn draws."""
     xr = x.astype(dtype) if cfg.use_fp32_router or x.dtype != dtype else x
     logits = xr @ w.router.astype(dtype).T
     if cfg.router_bias is not None:
         logits = logits + cfg.router_bias.astype(dtype)
     if training and cfg.noise_scale > 0:
-        logits = logits + (cfg.router_noise.astype(dtype) * dtype(cfg.noise_scale))     # router.jl:38-40
+        if w.noise_weight is not None:                                                  # router.jl:33-37
+            noise = cfg.router_noise.astype(dtype) * softplus(xr @ w.noise_weight.astype(dtype).T)
+            logits = logits + dtype(cfg.noise_scale) * noise
+        else:
+            logits = logits + (cfg.router_noise.astype(dtype) * dtype(cfg.noise_scale))     # router.jl:38-40
     indices, gates, probs = compute_gates(cfg.gate_type, logits)
     return indices, gates, probs, logits
 

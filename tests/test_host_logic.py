@@ -82,3 +82,13 @@ def test_standard_expert_init_scale_and_bias(lib_built):
     assert nb.b1 is None and nb.b2 is None
     with pytest.raises(ValueError):
         m.StandardExpert(8, 8, 8, m.gelu, dropout=0.1)
+
+
+def test_router_noise_network_init(lib_built):
+    import mixtureofexperts_b200 as m
+
+    r = m.Router(64, 8, m.TopKGating(2), noise_scale=0.1, use_noise_network=True, rng=0)
+    lim = (6.0 / (64 + 8)) ** 0.5                       # Flux Dense default init, like Router.weight
+    assert r.noise_weight.shape == (8, 64) and np.abs(r.noise_weight).max() <= lim
+    assert not np.array_equal(r.noise_weight, r.weight)
+    assert m.Router(64, 8, m.TopKGating(2)).noise_weight is None

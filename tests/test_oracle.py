@@ -93,6 +93,38 @@ def test_standard_expert_agrees_with_float64_restatement(activation):
                   - e.w2 @ orc.ACTIVATIONS[activation](e.w1 @ x[0])).max() < 1e-5
 
 
+def test_noise_network_softplus_scaling():
+    """router.jl:33-37: logits + noise_scale * (randn .* softplus(noise_weight x)), softplus as NNlib's."""
+    T, D, E = 20, 16, 4
+    x, w = orc.make_layer_inputs(3, T, D, 8, 8, E, init="normal", std=0.25)
+    rng = np.random.default_rng(0)
+    w.noise_weight = rng.standard_normal((E, D)).astype(np.float32)
+    noise = rng.standard_normal((T, E)).astype(np.float32)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=8, output_dim=8, gate_type=orc.TopKGating(2),
+                        noise_scale=0.3, router_noise=noise)
+    lg = orc.router_forward(cfg, w, x, training=True)[3]
+    want = x.astype(np.float64) @ w.router.T.astype(np.float64) + 0.3 * noise * np.log1p(
+        np.exp(x.astype(np.float64) @ w.noise_weight.T.astype(np.float64)))
+    assert rel_inf(lg, want) < 1e-5
+    assert np.array_equal(orc.router_forward(cfg, w, x, training=False)[3], x @ w.router.T)
+    assert abs(float(orc.softplus(np.float32(0))) - np.log(2)) < 1e-7 and orc.softplus(np.float32(100)) == 100
+
+
+def test_jitter_gating_only_acts_when_training():
+    rng = np.random.default_rng(1)
+    logits = rng.standard_normal((50, 6)).astype(np.float32)
+    u = rng.random((50, 6), dtype=np.float32)
+    g = orc.JitterGating(orc.TopKGating(2), 0.5)
+    base = orc.compute_gates(orc.TopKGating(2), logits)
+    off = orc.compute_gates(g, logits)
+    assert all(np.array_equal(a, b) for a, b in zip(base, off))
+    on = orc.compute_gates(g, logits, training=True, jitter_u=u)
+    want = orc.compute_gates(orc.TopKGating(2), logits * (1 + (2 * u - 1) * np.float32(0.5)))
+    assert np.array_equal(on[0], want[0]) and rel_inf(on[2], want[2]) < 1e-6
+    # jitter stays inside [1-eps, 1+eps)
+    assert np.abs((1 + (2 * u - 1) * 0.5) - 1).max() <= 0.5
+
+
 def test_topk_ties_go_to_lowest_index():
     logits = np.array([[0.5, 2.0, 2.0, 2.0, -1.0]], dtype=np.float32)
     idx, gates, _ = orc.compute_gates(orc.TopKGating(2), logits)

@@ -239,6 +239,61 @@ def test_training_time_router_noise_with_given_draws(host):
     layer.close()
 
 
+@pytest.mark.parametrize("E,k,host", [(8, 2, False), (8, 2, True), (33, 3, False), (64, 4, False)])
+def test_router_noise_network(E, k, host):
+    """use_noise_network (src/core/router.jl:33-37): logits + noise_scale * (randn .* softplus(noise_weight x)).
+    The noise projection rides in the gate GEMM (2E columns); E = 33 and 64 cross its column buckets."""
+    T, D, H, O = 260, 72, 64, 40
+    x, w = orc.make_layer_inputs(31 + E, T, D, H, O, E, init="normal", std=0.25)
+    rng = np.random.default_rng(E)
+    w.noise_weight = (rng.standard_normal((E, D)) * 0.3).astype(np.float32)
+    noise = rng.standard_normal((T, E)).astype(np.float32)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(k), balance_alpha=0.01, z_loss_weight=0.001, noise_scale=0.5,
+                        router_noise=noise)
+    o_out, o_loss, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+    plain = orc.MoEWeights(router=w.router, experts=w.experts)
+    assert (orc.moe_layer_forward(cfg, plain, x, training=True)[2]["indices"] != aux["indices"]).any()
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=device_gate("topk", k), noise_scale=0.5)
+    layer.router.noise_scale = 0.5
+    layer.router.noise_weight = w.noise_weight
+    layer.sync_router()
+    xin = np.asfortranarray(x.T) if host else torch.from_numpy(x).cuda().t()
+    out, loss, routing = layer(xin, training=True, return_routing=True, router_noise=noise.T)
+    if not host:
+        out, loss = out.cpu().numpy(), float(loss.item())
+        routing = {k_: v.cpu().numpy() for k_, v in routing.items()}
+    lg64 = x.astype(np.float64) @ w.router.astype(np.float64).T + 0.5 * noise.astype(np.float64) * orc.softplus(
+        x.astype(np.float64) @ w.noise_weight.astype(np.float64).T)
+    excused = check_indices(routing["indices"].T, aux["indices"], lg64, k)
+    assert rel_inf(routing["logits"].T, aux["logits"]) < F32_TOL
+    if not excused:
+        assert rel_inf(routing["gates"].T, aux["gates"]) < F32_TOL
+        assert rel_inf(out.T, o_out) < F32_TOL
+        assert abs(float(loss) - float(o_loss)) < F32_TOL * abs(float(o_loss))
+    # inference reads neither the draws nor the network
+    clean_idx = orc.moe_layer_forward(cfg, w, x, training=False)[2]["indices"]
+    rt2 = layer(xin, training=False, return_routing=True)[2]
+    idx2 = rt2["indices"] if host else rt2["indices"].cpu().numpy()
+    assert np.array_equal(idx2.T, clean_idx)
+    # removing the network falls back to plain Gaussian noise
+    layer.router.noise_weight = None
+    layer.sync_router()
+    rt3 = layer(xin, training=True, return_routing=True, router_noise=noise.T)[2]
+    idx3 = rt3["indices"] if host else rt3["indices"].cpu().numpy()
+    assert np.array_equal(idx3.T, orc.moe_layer_forward(cfg, plain, x, training=True)[2]["indices"])
+    layer.close()
+
+
+def test_router_noise_network_is_refused_beyond_64_router_rows():
+    import mixtureofexperts_b200 as m
+
+    cfg = m.create_moe_config(num_experts=66, expert_type="gated", input_dim=16, hidden_dim=16, output_dim=16,
+                              gate_type=m.TopKGating(2), noise_scale=0.1, use_noise_network=True)
+    with pytest.raises(m.MoEError):
+        m.MoELayer(cfg)
+
+
 def test_empty_batch():
     x, w = orc.make_layer_inputs(1, 1, 64, 96, 64, 4, init="normal", std=0.25)
     layer = make_device_layer(w, D=64, H=96, O=64, gate=device_gate("topk", 2))
@@ -350,6 +405,37 @@ def test_compute_gates_and_compute_loss_operators():
     wz = orc.z_loss(0.001, logits)
     gz = m.compute_loss(m.ZLoss(0.001), lt.t())
     assert abs(float(gz.item()) - float(wz)) < F32_TOL * float(wz)
+
+
+def test_jitter_gating_operator_and_layer():
+    """JitterGating (src/gating/switch.jl:20-33): with training=true the base gate sees
+    logits .* (1 .+ (2u .- 1) .* eps); inside a layer the router never passes the keyword, so
+    the layer routes like the base gate."""
+    import mixtureofexperts_b200 as m
+
+    rng = np.random.default_rng(12)
+    logits = (rng.standard_normal((500, 12)) * 2).astype(np.float32)
+    u = rng.random((500, 12), dtype=np.float32)
+    lt, ut = torch.from_numpy(logits).cuda(), torch.from_numpy(u).cuda()
+    gate, ogate = m.JitterGating(m.TopKGating(2), 0.3), orc.JitterGating(orc.TopKGating(2), 0.3)
+    oi, og, op = orc.compute_gates(ogate, logits, training=True, jitter_u=u)
+    di, dg, dp = m.compute_gates(gate, lt.t(), training=True, jitter=ut.t())
+    assert (oi != orc.compute_gates(ogate, logits)[0]).any()              # the jitter does move some choices
+    assert np.array_equal(di.cpu().numpy().T, oi)
+    assert rel_inf(dg.cpu().numpy().T, og) < F32_TOL and rel_inf(dp.cpu().numpy().T, op) < F32_TOL
+    di0 = m.compute_gates(gate, lt.t())[0]                                 # training=false: the base gate
+    assert np.array_equal(di0.cpu().numpy().T, orc.compute_gates(orc.TopKGating(2), logits)[0])
+    di1 = m.compute_gates(gate, lt.t(), training=True)[0]                  # draws made on the device
+    assert di1.shape == di.shape and int(di1.min()) >= 1 and int(di1.max()) <= 12
+    # a layer configured with JitterGating equals the same layer with its base gate, training or not
+    x, w = orc.make_layer_inputs(8, 120, 64, 96, 48, 8, init="normal", std=0.25)
+    la = make_device_layer(w, D=64, H=96, O=48, gate=m.JitterGating(m.TopKGating(2), 0.3))
+    lb = make_device_layer(w, D=64, H=96, O=48, gate=m.TopKGating(2))
+    xin = torch.from_numpy(x).cuda().t()
+    (oa, lossa), (ob, lossb) = la(xin, training=True), lb(xin, training=True)
+    assert torch.equal(oa, ob) and float(lossa.item()) == float(lossb.item())
+    la.close()
+    lb.close()
 
 
 def test_exact_ties_go_to_the_lowest_index():
