@@ -150,6 +150,17 @@ int moe_layer_set_router(moe_layer_t*, const float* w, const float* logit_bias,
  * comes from the noise-free logits, like the reference's second router pass. */
 int moe_layer_set_router_noise(moe_layer_t*, const float* noise, float noise_scale);
 
+/* AuxiliaryFreeLoss.update_bias! (src/balancing/auxiliary_free.jl:36-71) on the device: once enabled,
+ * every training forward ends with a one-block kernel that turns the call's per-expert counts into
+ * the momentum update of the logit bias (given to moe_layer_set_router) and mean-centres it, so
+ * the next call selects with the new bias and no count ever travels to the host.  `bias_momentum`
+ * (host, [E_router], NULL = zeros) and `update_counter` seed the state; update_freq as in the
+ * reference.  Not with expert parallelism or num_shared_experts > 0.  enable = 0 switches it off. */
+int moe_layer_set_aux_free(moe_layer_t*, int enable, float learning_rate, float momentum, int update_freq,
+                           const float* bias_momentum, int64_t update_counter);
+/* Reads the state back into HOST arrays (each nullable); synchronises the device. */
+int moe_layer_aux_free_state(moe_layer_t*, float* bias, float* bias_momentum, int64_t* update_counter);
+
 /* Router.noise_weight (src/core/router.jl:20, use_noise_network = true): an (E_router x D) FP32 matrix
  * in `layout`; once set, armed noise becomes logits + noise_scale * (noise .* softplus(noise_w x))
  * (router.jl:33-37), the second projection riding in the same gate GEMM.  Call after

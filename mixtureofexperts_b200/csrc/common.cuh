@@ -171,6 +171,9 @@ int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_
 // wt columns 0..E-1 = w, E..2E-1 = nw (the noise network), padded to router_e_pad(2E)
 int launch_router_transpose_noise(const float* w, const float* nw, float* wt, int E, int D, cudaStream_t s);
 int launch_scan(const ScanParams& p, cudaStream_t s);
+// AuxiliaryFreeLoss.update_bias! on the device: bias/momentum [E] updated in place from expert_count [E]
+int launch_aux_free_update(const int32_t* expert_count, int E, float* bias, float* bias_momentum, float learning_rate,
+                           float momentum, cudaStream_t s);
 int launch_accumulate(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E, cudaStream_t s);
 int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s);
 int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s);

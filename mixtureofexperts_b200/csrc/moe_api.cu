@@ -73,6 +73,12 @@ struct moe_layer {
     float* router_wt_noise = nullptr;  // [D_pad][e_pad(2 E_router)]: router columns, then noise-network columns
     float* router_bias = nullptr;
     bool has_bias = false, router_set = false;
+    // AuxiliaryFreeLoss.update_bias! on the device (moe_layer_set_aux_free)
+    bool aux_free = false;
+    float aux_lr = 0.f, aux_momentum = 0.f;
+    int aux_freq = 1;
+    int64_t aux_counter = 0;
+    float* bias_momentum = nullptr;   // [E_router]
     const float* noise = nullptr;   // caller-owned device draws for the next training forward
     float noise_scale = 0.f;
     std::vector<char> expert_set;
@@ -537,6 +543,17 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     if (n < 0) return fail(MOE_ERR_CUDA, "combine launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
     stage_mark(L, 6, s);
+    // compute_loss(::AuxiliaryFreeLoss) first updates the bias the next call selects with
+    // (src/balancing/auxiliary_free.jl:73-83); partial (chunked) calls are updated by their caller
+    if (L->aux_free && training && !partial_sums) {
+        ++L->aux_counter;
+        if (L->aux_counter % L->aux_freq == 0) {
+            n = launch_aux_free_update(L->expert_count, L->E_router, L->router_bias, L->bias_momentum, L->aux_lr,
+                                       L->aux_momentum, s);
+            if (n < 0) return fail(MOE_ERR_CUDA, "bias update launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+            L->launches += n;
+        }
+    }
     if (peer) {
         ep_mark(L->ep, 3, s);
         if ((rc = ep_finish_loss(L->ep, training, opt->loss, opt->routing_entropy, s, &L->launches, g_err, sizeof(g_err))))
@@ -624,6 +641,7 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->router_w);
     dev_free(L->router_bias);
     dev_free(L->router_wt);
+    dev_free(L->bias_momentum);
     dev_free(L->router_nw);
     dev_free(L->router_wt_noise);
     dev_free(L->stage_w);
@@ -766,12 +784,53 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     return MOE_OK;
 }
 
+int moe_layer_set_aux_free(moe_layer_t* L, int enable, float learning_rate, float momentum, int update_freq,
+                           const float* bias_momentum, int64_t update_counter) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    if (!enable) {
+        L->aux_free = false;
+        return MOE_OK;
+    }
+    if (update_freq < 1) return fail(MOE_ERR_INVALID, "update_freq must be at least 1");
+    if (L->ep) return fail(MOE_ERR_UNSUPPORTED, "the device bias update is not offered with expert parallelism");
+    if (L->cfg.shared_mode == MOE_SHARED_LAYER_BLEND)
+        return fail(MOE_ERR_UNSUPPORTED, "the device bias update is not offered with num_shared_experts > 0");
+    if (!L->has_bias) return fail(MOE_ERR_STATE, "give the bias to moe_layer_set_router first");
+    CUDA_TRY(cudaSetDevice(L->device));
+    int rc;
+    if (!L->bias_momentum && (rc = dev_alloc(&L->bias_momentum, (size_t)L->E_router))) return rc;
+    if (bias_momentum)
+        CUDA_TRY(cudaMemcpyAsync(L->bias_momentum, bias_momentum, sizeof(float) * L->E_router, cudaMemcpyHostToDevice, L->stream));
+    else
+        CUDA_TRY(cudaMemsetAsync(L->bias_momentum, 0, sizeof(float) * L->E_router, L->stream));
+    CUDA_TRY(cudaStreamSynchronize(L->stream));
+    L->aux_lr = learning_rate;
+    L->aux_momentum = momentum;
+    L->aux_freq = update_freq;
+    L->aux_counter = update_counter;
+    L->aux_free = true;
+    return MOE_OK;
+}
+
+int moe_layer_aux_free_state(moe_layer_t* L, float* bias, float* bias_momentum, int64_t* update_counter) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    if (!L->aux_free) return fail(MOE_ERR_STATE, "the device bias update is not enabled (moe_layer_set_aux_free)");
+    CUDA_TRY(cudaSetDevice(L->device));
+    CUDA_TRY(cudaDeviceSynchronize());   // updates queued on the callers' streams
+    if (bias) CUDA_TRY(cudaMemcpy(bias, L->router_bias, sizeof(float) * L->E_router, cudaMemcpyDeviceToHost));
+    if (bias_momentum)
+        CUDA_TRY(cudaMemcpy(bias_momentum, L->bias_momentum, sizeof(float) * L->E_router, cudaMemcpyDeviceToHost));
+    if (update_counter) *update_counter = L->aux_counter;
+    return MOE_OK;
+}
+
 int moe_layer_set_router_noise_network(moe_layer_t* L, const float* noise_w, int layout, int src_is_device) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");
     CUDA_TRY(cudaSetDevice(L->device));
     if (!noise_w) {   // back to plain Gaussian noise
         CUDA_TRY(cudaStreamSynchronize(L->stream));
-        dev_free(L->router_nw);
+        dev_free(L->bias_momentum);
+    dev_free(L->router_nw);
         dev_free(L->router_wt_noise);
         L->router_nw = L->router_wt_noise = nullptr;
         return MOE_OK;
@@ -863,7 +922,7 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     int env_chunks = 0;   // MOE_B200_HOST_CHUNKS = n: n equal chunks (1 = off); unset: the default schedule
     // (not with the capacity constraint, whose capacity and first-come order span the whole batch)
     if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192 && !(L->cfg.drop_tokens && training) &&
-        !(L->noise && training)) {
+        !(L->noise && training) && !(L->aux_free && training)) {
         const char* e = getenv("MOE_B200_HOST_CHUNKS");
         env_chunks = e ? atoi(e) : 0;
         nchunks = env_chunks > 0 ? env_chunks : 5;

@@ -183,7 +183,52 @@ __global__ void accumulate_kernel(float* acc, const float* tmp, int n, int64_t* 
     if (tacc && i < E) tacc[i] += ttmp[i];
 }
 
+// update_bias! (src/balancing/auxiliary_free.jl:36-71) from this call's per-expert counts.  One
+// block; thread e owns expert e.  Arithmetic types follow Julia's promotion: the gradient and the
+// momentum blend are Float64 (Int/Int target), rounded into the Float32 vectors; the bias step and
+// the mean-centring are Float32.
+__global__ void aux_free_update_kernel(const int32_t* expert_count, int E, float* bias, float* bias_momentum,
+                                       float learning_rate, float momentum) {
+    __shared__ int s_cnt[MAX_EXPERTS];
+    __shared__ float s_bias[MAX_EXPERTS];
+    __shared__ long long s_total;
+    __shared__ float s_mean;
+    const int e = threadIdx.x;
+    if (e < E) s_cnt[e] = expert_count[e];
+    __syncthreads();
+    if (e == 0) {
+        long long t = 0;
+        for (int i = 0; i < E; ++i) t += s_cnt[i];
+        s_total = t;
+    }
+    __syncthreads();
+    const long long total = s_total;
+    if (total == 0) return;
+    if (e < E) {
+        const double target = (double)total / (double)E;
+        const double grad = ((double)(float)s_cnt[e] - target) / (double)total;
+        const float keep = __fmul_rn(momentum, bias_momentum[e]);
+        const float bm = (float)((double)keep + (double)__fsub_rn(1.0f, momentum) * grad);
+        bias_momentum[e] = bm;
+        s_bias[e] = __fsub_rn(bias[e], __fmul_rn(learning_rate, bm));
+    }
+    __syncthreads();
+    if (e == 0) {
+        float sum = 0.f;
+        for (int i = 0; i < E; ++i) sum = __fadd_rn(sum, s_bias[i]);
+        s_mean = __fdiv_rn(sum, (float)E);
+    }
+    __syncthreads();
+    if (e < E) bias[e] = __fsub_rn(s_bias[e], s_mean);
+}
+
 }  // namespace
+
+int launch_aux_free_update(const int32_t* expert_count, int E, float* bias, float* bias_momentum, float learning_rate,
+                           float momentum, cudaStream_t s) {
+    aux_free_update_kernel<<<1, MAX_EXPERTS, 0, s>>>(expert_count, E, bias, bias_momentum, learning_rate, momentum);
+    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
 
 int launch_accumulate(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E, cudaStream_t s) {
     const int m = n > E ? n : E;

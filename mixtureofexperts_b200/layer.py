@@ -179,6 +179,9 @@ class MoELayer:
             _lib.SHARED_LAYER_BLEND if config.num_shared_experts > 0 else _lib.SHARED_NONE)
         num_shared = gate_shared or config.num_shared_experts
         self.balance_loss = config.balance_loss
+        if isinstance(self.balance_loss, AuxiliaryFreeLoss) and self.balance_loss.num_experts != config.num_experts:
+            # update_bias! indexes its count vector with layer expert ids (auxiliary_free.jl:48-53)
+            raise _lib.MoEError(_lib.ERR_INVALID, "AuxiliaryFreeLoss must be built for config.num_experts experts")
         if isinstance(self.balance_loss, AuxiliaryFreeLoss):
             alpha = self.balance_loss.complementary_weight if self.balance_loss.use_complementary_loss else 0.0
         elif isinstance(self.balance_loss, SwitchTransformerLoss):
@@ -222,7 +225,10 @@ class MoELayer:
         self._stats = {"tokens_per_expert": np.zeros(config.num_experts, dtype=np.int64),
                        "routing_entropy": [], "capacity_overflow": 0}
         self._pending = []          # device-side (tokens_per_expert, entropy) of calls not yet folded in
+        self._aux_on_device = False
         self.sync_weights()
+        if isinstance(self.balance_loss, AuxiliaryFreeLoss):
+            self._attach_aux_free(expert_parallel is not None)
 
     @property
     def training_stats(self) -> dict:
@@ -256,6 +262,37 @@ class MoELayer:
             _lib.check(_lib.lib.moe_layer_set_expert(self._handle, e, p1, p2, p3, d1, l1, dev1))
         self.sync_router()
 
+    def _attach_aux_free(self, expert_parallel: bool) -> None:
+        """Move AuxiliaryFreeLoss's state into the device handle (update_bias! then runs at the end of
+        every training forward on the GPU); with expert parallelism or num_shared_experts > 0 the
+        update stays on the host, fed by the call's expert counts."""
+        bl = self.balance_loss
+        if expert_parallel or self.config.num_shared_experts > 0:
+            return
+        mom = np.ascontiguousarray(bl._bias_momentum, dtype=np.float32)
+        _lib.check(_lib.lib.moe_layer_set_aux_free(self._handle, 1, bl.learning_rate, bl.momentum, bl.update_freq,
+                                                   mom.ctypes.data, bl._update_counter))
+        self._aux_on_device = True
+
+        def state():
+            n = self.e_router
+            b, m_ = np.empty(n, dtype=np.float32), np.empty(n, dtype=np.float32)
+            cnt = C.c_int64()
+            _lib.check(_lib.lib.moe_layer_aux_free_state(self._handle, b.ctypes.data, m_.ctypes.data, C.byref(cnt)))
+            return b, m_, int(cnt.value)
+
+        def push():
+            bl._device_state = None              # sync_router reads the host copy just assigned
+            try:
+                self.sync_router()
+                mom2 = np.ascontiguousarray(bl._bias_momentum, dtype=np.float32)
+                _lib.check(_lib.lib.moe_layer_set_aux_free(self._handle, 1, bl.learning_rate, bl.momentum,
+                                                           bl.update_freq, mom2.ctypes.data, bl._update_counter))
+            finally:
+                bl._device_state = state
+
+        bl._device_state, bl._device_push = state, push
+
     def _bias_ptr(self, b, n: int, on_device: int):
         """Pointer to a float32 copy of bias vector ``b`` in the memory kind of the weights."""
         if b is None:
@@ -285,7 +322,9 @@ class MoELayer:
             raise _lib.MoEError(_lib.ERR_INVALID, "router weights must be float32")
         bias_ptr, keep_b = None, None
         bias = getattr(self.router, "bias", None)
-        if isinstance(self.balance_loss, AuxiliaryFreeLoss):
+        if isinstance(self.balance_loss, AuxiliaryFreeLoss) and self.config.num_shared_experts == 0:
+            # forward_standard alone selects with the biased logits (src/core/moe_layer.jl:137-140);
+            # forward_with_shared_experts (:158-185) only updates the bias
             bias = self.balance_loss.bias
         if bias is not None:
             if _is_torch(bias):
@@ -332,7 +371,7 @@ class MoELayer:
         T = int(x.shape[1])
         aux_free = isinstance(self.balance_loss, AuxiliaryFreeLoss) and training
         noise_keep = self._arm_router_noise(T, training, router_noise)
-        want_stats = cfg.num_shared_experts == 0 or aux_free
+        want_stats = cfg.num_shared_experts == 0 or (aux_free and not self._aux_on_device)
         if _is_torch(x) and x.is_cuda:
             out, loss, extra = self._forward_torch(x, T, training, want_stats, return_routing, out)
         else:
@@ -345,10 +384,17 @@ class MoELayer:
             self._pending.append((extra["tokens_per_expert"], extra["routing_entropy"]))
             if len(self._pending) > 256:
                 _ = self.training_stats
-        if aux_free:
-            # compute_loss(::AuxiliaryFreeLoss) updates the bias first (auxiliary_free.jl:73-83)
-            self.balance_loss.update_bias(extra["tokens_per_expert"].cpu().numpy())
-            self.sync_router()
+        if aux_free and not self._aux_on_device:
+            # compute_loss(::AuxiliaryFreeLoss) updates the bias first (auxiliary_free.jl:73-83); the
+            # device handle does it itself unless the configuration keeps the update on the host
+            tpe = extra["tokens_per_expert"]
+            tpe = np.array(tpe.cpu().numpy() if _is_torch(tpe) else tpe)
+            # forward_with_shared_experts hands compute_loss the routed ids shifted past the shared
+            # experts (moe_layer.jl:176-179), so those never count
+            tpe[:cfg.num_shared_experts] = 0
+            self.balance_loss.update_bias(tpe)
+            if cfg.num_shared_experts == 0:
+                self.sync_router()
         ret = (out, loss)
         if return_stats:
             ret = ret + (self.training_stats,)
@@ -499,6 +545,10 @@ class MoELayer:
 
     def close(self) -> None:
         if getattr(self, "_handle", None) is not None and self._handle.value:
+            bl = getattr(self, "balance_loss", None)
+            if getattr(self, "_aux_on_device", False) and bl._device_state is not None:
+                bl._pull()                        # the loss object keeps the final state
+                bl._device_state = bl._device_push = None
             _lib.lib.moe_layer_destroy(self._handle)
             self._handle = C.c_void_p()
 

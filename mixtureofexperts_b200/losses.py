@@ -1,7 +1,7 @@
 """Load-balancing losses with the reference's names (src/balancing/)."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import numpy as np
 
@@ -24,44 +24,82 @@ class ZLoss(LoadBalancingLoss):
     beta: float = 0.001
 
 
-@dataclass
 class AuxiliaryFreeLoss(LoadBalancingLoss):
     """AuxiliaryFreeLoss(num_experts; ...) (src/balancing/auxiliary_free.jl:11-34).  The layer
-    adds ``bias`` to the router logits before selecting experts (moe_layer.jl:137-140); the
-    momentum update of the bias (auxiliary_free.jl:36-71) runs on the host from the per-call
-    expert counts."""
-    num_experts: int
-    bias_init: float = 0.0
-    learning_rate: float = 0.01
-    momentum: float = 0.9
-    update_freq: int = 1
-    use_complementary_loss: bool = True
-    complementary_weight: float = 0.001
-    bias: np.ndarray = field(default=None)
-    bias_momentum: np.ndarray = field(default=None)
-    update_counter: int = 0
+    adds ``bias`` to the router logits before selecting experts (moe_layer.jl:137-140).
 
-    def __post_init__(self):
-        if self.bias is None:
-            self.bias = np.full(self.num_experts, self.bias_init, dtype=np.float32)
-        if self.bias_momentum is None:
-            self.bias_momentum = np.zeros(self.num_experts, dtype=np.float32)
+    Once a MoELayer holds this loss, ``bias``, ``bias_momentum`` and ``update_counter`` live in
+    the layer's device handle, where every training forward updates them (update_bias!,
+    auxiliary_free.jl:36-71) without a host round trip; reading an attribute here fetches the
+    current device state, assigning ``bias`` pushes it.  Unattached (or attached to a layer whose
+    configuration keeps the update on the host) the state is plain NumPy and ``update_bias`` applies
+    the same update from per-expert counts."""
+
+    def __init__(self, num_experts: int, bias_init: float = 0.0, learning_rate: float = 0.01, momentum: float = 0.9,
+                 update_freq: int = 1, use_complementary_loss: bool = True, complementary_weight: float = 0.001,
+                 bias=None, bias_momentum=None, update_counter: int = 0):
+        self.num_experts = int(num_experts)
+        self.bias_init = float(bias_init)
+        self.learning_rate = float(learning_rate)
+        self.momentum = float(momentum)
+        self.update_freq = int(update_freq)
+        self.use_complementary_loss = bool(use_complementary_loss)
+        self.complementary_weight = float(complementary_weight)
+        self._bias = (np.full(self.num_experts, self.bias_init, dtype=np.float32) if bias is None
+                      else np.array(bias, dtype=np.float32))
+        self._bias_momentum = (np.zeros(self.num_experts, dtype=np.float32) if bias_momentum is None
+                               else np.array(bias_momentum, dtype=np.float32))
+        self._update_counter = int(update_counter)
+        self._device_state = None       # callable () -> (bias, momentum, counter) while a layer owns the state
+        self._device_push = None        # callable () pushing the host copy to that layer
+
+    def _pull(self) -> None:
+        if self._device_state is not None:
+            self._bias, self._bias_momentum, self._update_counter = self._device_state()
+
+    @property
+    def bias(self) -> np.ndarray:
+        self._pull()
+        return self._bias
+
+    @bias.setter
+    def bias(self, value) -> None:
+        self._pull()
+        self._bias = np.array(value, dtype=np.float32)
+        if self._device_push is not None:
+            self._device_push()
+
+    @property
+    def bias_momentum(self) -> np.ndarray:
+        self._pull()
+        return self._bias_momentum
+
+    @property
+    def update_counter(self) -> int:
+        self._pull()
+        return self._update_counter
 
     def update_bias(self, expert_counts) -> None:
-        """update_bias! (src/balancing/auxiliary_free.jl:36-71) from per-expert counts."""
-        self.update_counter += 1
-        if self.update_counter % self.update_freq != 0:
-            return
-        counts = np.asarray(expert_counts, dtype=np.float32)
-        total = float(counts.sum())
-        if total == 0:
-            return
-        target = total / self.num_experts
-        grad = (counts - np.float32(target)) / np.float32(total)
-        self.bias_momentum = (np.float32(self.momentum) * self.bias_momentum
-                              + np.float32(1 - self.momentum) * grad).astype(np.float32)
-        self.bias = (self.bias - np.float32(self.learning_rate) * self.bias_momentum).astype(np.float32)
-        self.bias = (self.bias - self.bias.mean(dtype=np.float32)).astype(np.float32)
+        """update_bias! (src/balancing/auxiliary_free.jl:36-71) from per-expert counts, on the
+        host.  Julia's promotion is kept: Int/Int target and the gradient are Float64, the
+        momentum blend is rounded into the Float32 vector, the bias step and centring are Float32."""
+        self._pull()
+        self._update_counter += 1
+        if self._update_counter % self.update_freq == 0:
+            counts = np.asarray(expert_counts, dtype=np.float32)
+            total = int(counts.sum(dtype=np.float64))
+            if total != 0:
+                f = np.float32
+                grad = (counts.astype(np.float64) - total / self.num_experts) / total
+                keep = (f(self.momentum) * self._bias_momentum).astype(np.float32)
+                self._bias_momentum = (keep.astype(np.float64) + np.float64(f(1) - f(self.momentum)) * grad).astype(f)
+                b = (self._bias - f(self.learning_rate) * self._bias_momentum).astype(f)
+                mean = f(0)
+                for v in b:
+                    mean = f(mean + v)
+                self._bias = (b - f(mean / f(self.num_experts))).astype(f)
+        if self._device_push is not None:
+            self._device_push()
 
 
 def compute_loss(loss_fn, expert_indices, router_probs=None):

@@ -164,6 +164,46 @@ def compute_gates(gate, logits: np.ndarray, training: bool = False, jitter_u: Op
 # --------------------------------------------------------------------------------------
 
 
+@dataclass
+class AuxFreeState:
+    """The mutable fields of AuxiliaryFreeLoss (src/balancing/auxiliary_free.jl:11-34)."""
+    bias: np.ndarray
+    bias_momentum: np.ndarray
+    learning_rate: float = 0.01
+    momentum: float = 0.9
+    update_freq: int = 1
+    update_counter: int = 0
+
+
+def aux_free_update_bias(st: AuxFreeState, indices: np.ndarray) -> None:
+    """update_bias! (src/balancing/auxiliary_free.jl:36-71), loop for loop, with Julia's promotion:
+    target_count (Int/Int) and gradient are Float64; momentum*bias_momentum is Float32, the blend is
+    Float64 and is rounded on assignment into the Float32 vector; bias -= lr*momentum and
+    bias .-= mean(bias) are Float32."""
+    f = np.float32
+    st.update_counter += 1
+    if st.update_counter % st.update_freq != 0:
+        return
+    n = st.bias.size
+    counts = np.zeros(n, dtype=np.float32)
+    total = 0
+    for idx in indices.reshape(-1):
+        if idx > 0:
+            counts[idx - 1] += f(1)
+            total += 1
+    if total == 0:
+        return
+    target = total / n
+    for i in range(n):
+        grad = (float(counts[i]) - target) / total
+        st.bias_momentum[i] = f(float(f(st.momentum) * st.bias_momentum[i]) + float(f(1) - f(st.momentum)) * grad)
+        st.bias[i] = f(st.bias[i] - f(f(st.learning_rate) * st.bias_momentum[i]))
+    mean = f(0)
+    for v in st.bias:
+        mean = f(mean + v)
+    st.bias[:] = st.bias - f(mean / f(n))
+
+
 def switch_transformer_loss(alpha: float, indices: np.ndarray, probs: np.ndarray) -> np.float32:
     """compute_loss(::SwitchTransformerLoss, indices, probs) (src/balancing/losses.jl:15-36)."""
     N = probs.shape[1]
@@ -275,6 +315,8 @@ class MoEConfig:
     # AuxiliaryFreeLoss hook (src/core/moe_layer.jl:137-140): bias added to logits before a
     # second compute_gates; the probabilities used by the loss stay unbiased.
     aux_free_bias: Optional[np.ndarray] = None
+    # the whole AuxiliaryFreeLoss: its bias selects like aux_free_bias and a training call updates it
+    aux_free_state: Optional[AuxFreeState] = None
     # A bias that is part of the logits themselves (a router Dense with bias).
     router_bias: Optional[np.ndarray] = None
     # Router.noise_scale (src/core/router.jl:32-41): logits += noise_scale * randn when training; the
@@ -364,12 +406,15 @@ def forward_standard(cfg: MoEConfig, w: MoEWeights, x: np.ndarray, training: boo
     act = ACTIVATIONS[cfg.activation]
     output = np.zeros((T, cfg.output_dim), dtype=dtype)
     indices, gates, probs, logits = router_forward(cfg, w, x, dtype, training)
-    if cfg.aux_free_bias is not None:
-        biased = logits + cfg.aux_free_bias.astype(logits.dtype)      # auxiliary_free.jl:90-92
+    aux_bias = cfg.aux_free_state.bias if cfg.aux_free_state is not None else cfg.aux_free_bias
+    if aux_bias is not None:
+        biased = logits + aux_bias.astype(logits.dtype)               # auxiliary_free.jl:90-92
         indices, gates, _ = compute_gates(cfg.gate_type, biased)
     if cfg.drop_tokens and training:
         indices, gates = apply_capacity_constraint(indices, gates, cfg.capacity_factor, cfg.num_experts)
     process_expert_forward(output, w.experts, x.astype(dtype), indices, gates, act)
+    if training and cfg.aux_free_state is not None:
+        aux_free_update_bias(cfg.aux_free_state, indices)            # compute_loss, auxiliary_free.jl:73-75
     loss = switch_transformer_loss(cfg.balance_alpha, indices, probs) if training else np.float32(0)
     stats = {
         "tokens_per_expert": np.bincount(indices.reshape(-1), minlength=cfg.num_experts + 1)[1:cfg.num_experts + 1],

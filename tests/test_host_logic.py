@@ -59,6 +59,22 @@ def test_aux_free_bias_update(lib_built):
     assert loss.bias[0] < 0 and abs(float(loss.bias.sum())) < 1e-6 and (loss.bias[1:] > 0).all()
 
 
+def test_aux_free_host_update_equals_the_oracle(lib_built):
+    import mixtureofexperts_b200 as m
+    from oracle import moe_oracle as orc
+
+    rng = np.random.default_rng(0)
+    loss = m.AuxiliaryFreeLoss(6, learning_rate=0.5, momentum=0.7, update_freq=2)
+    st = orc.AuxFreeState(bias=np.zeros(6, dtype=np.float32), bias_momentum=np.zeros(6, dtype=np.float32),
+                          learning_rate=0.5, momentum=0.7, update_freq=2)
+    for _ in range(7):
+        idx = rng.integers(0, 7, size=(40, 2))                  # 0 = dropped slot
+        orc.aux_free_update_bias(st, idx)
+        loss.update_bias(np.bincount(idx.reshape(-1), minlength=7)[1:])
+        assert np.array_equal(loss.bias, st.bias) and np.array_equal(loss.bias_momentum, st.bias_momentum)
+    assert loss.update_counter == 7
+
+
 def test_gated_expert_init_scale(lib_built):
     import mixtureofexperts_b200 as m
 

@@ -125,6 +125,25 @@ def test_jitter_gating_only_acts_when_training():
     assert np.abs((1 + (2 * u - 1) * 0.5) - 1).max() <= 0.5
 
 
+def test_aux_free_update_bias_restatement():
+    """update_bias! (src/balancing/auxiliary_free.jl:36-71): overloaded experts get a falling bias, the
+    bias stays mean-centred, update_freq skips calls, an all-dropped batch changes nothing."""
+    st = orc.AuxFreeState(bias=np.zeros(4, dtype=np.float32), bias_momentum=np.zeros(4, dtype=np.float32),
+                          learning_rate=0.01, momentum=0.9, update_freq=2)
+    idx = np.array([[1, 2], [1, 3], [1, 4], [1, 2]])
+    orc.aux_free_update_bias(st, idx)
+    assert st.update_counter == 1 and not st.bias.any()              # skipped by update_freq
+    orc.aux_free_update_bias(st, idx)
+    # counts (4,2,1,1) of 8, target 2: gradient (0.25, 0, -0.125, -0.125); momentum = 0.1*gradient
+    assert np.allclose(st.bias_momentum, [0.025, 0, -0.0125, -0.0125], atol=1e-7)
+    raw = -0.01 * st.bias_momentum
+    assert np.allclose(st.bias, raw - raw.mean(), atol=1e-8) and abs(float(st.bias.sum())) < 1e-7
+    before = st.bias.copy()
+    orc.aux_free_update_bias(st, np.zeros((4, 2), dtype=np.int64))
+    orc.aux_free_update_bias(st, np.zeros((4, 2), dtype=np.int64))
+    assert np.array_equal(st.bias, before)
+
+
 def test_topk_ties_go_to_lowest_index():
     logits = np.array([[0.5, 2.0, 2.0, 2.0, -1.0]], dtype=np.float32)
     idx, gates, _ = orc.compute_gates(orc.TopKGating(2), logits)

@@ -153,6 +153,77 @@ def test_aux_free_bias_selects_but_does_not_change_probs():
     layer.close()
 
 
+@pytest.mark.parametrize("update_freq,drop,host", [(1, False, False), (2, False, False), (1, True, False), (1, False, True)])
+def test_aux_free_bias_update_runs_on_the_device(update_freq, drop, host):
+    """AuxiliaryFreeLoss over several training steps: the bias the device handle updates after each
+    call (update_bias!, src/balancing/auxiliary_free.jl:36-71) follows the oracle's, and so do
+    the experts each later step selects with it.  A large learning rate makes the bias matter."""
+    import mixtureofexperts_b200 as m
+
+    T, D, H, O, E, steps = 96, 48, 64, 40, 8, 6
+    _, w = orc.make_layer_inputs(21, T, D, H, O, E, init="normal", std=0.25)
+    w.router[0] *= 3.0                                        # a popular expert to push against
+    st = orc.AuxFreeState(bias=np.zeros(E, dtype=np.float32), bias_momentum=np.zeros(E, dtype=np.float32),
+                          learning_rate=2.0, momentum=0.5, update_freq=update_freq)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(2), balance_alpha=0.001, z_loss_weight=0.001, aux_free_state=st,
+                        drop_tokens=drop, capacity_factor=2.5)
+    bl = m.AuxiliaryFreeLoss(E, learning_rate=2.0, momentum=0.5, update_freq=update_freq)
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=m.TopKGating(2), balance_loss=bl, drop_tokens=drop,
+                              capacity_factor=2.5)
+    assert layer._aux_on_device
+    first_idx = None
+    for step in range(steps):
+        x = np.random.default_rng(100 + step).standard_normal((T, D)).astype(np.float32)
+        o_out, o_loss, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+        xin = np.asfortranarray(x.T) if host else torch.from_numpy(x).cuda().t()
+        out, loss, routing = layer(xin, training=True, return_routing=True)
+        idx = routing["indices"] if host else routing["indices"].cpu().numpy()
+        assert np.array_equal(idx.T, aux["indices"]), f"step {step}"
+        assert rel_inf(out if host else out.cpu().numpy(), o_out.T) < F32_TOL
+        assert abs(float(loss) - float(o_loss)) < F32_TOL * abs(float(o_loss))
+        assert rel_inf(bl.bias, st.bias) < F32_TOL and rel_inf(bl.bias_momentum, st.bias_momentum) < F32_TOL
+        assert bl.update_counter == st.update_counter == step + 1
+        assert abs(float(bl.bias.sum())) < 1e-5
+        first_idx = aux["indices"] if first_idx is None else first_idx
+    assert np.abs(st.bias).max() > 0.05 and st.bias[0] < 0            # the popular expert was pushed down
+    # an inference call neither updates nor counts
+    layer(torch.from_numpy(x).cuda().t(), training=False)
+    assert bl.update_counter == steps
+    # assigning the bias pushes it to the device; the momentum survives
+    mom = bl.bias_momentum.copy()
+    bl.bias = np.arange(E, dtype=np.float32)
+    assert np.array_equal(bl.bias, np.arange(E, dtype=np.float32)) and np.array_equal(bl.bias_momentum, mom)
+    layer.close()
+    assert np.array_equal(bl.bias, np.arange(E, dtype=np.float32))    # the loss object keeps the final state
+
+
+def test_aux_free_update_stays_on_the_host_with_layer_shared_experts():
+    """forward_with_shared_experts (src/core/moe_layer.jl:158-185) never selects with the bias but
+    still hands the shifted routed ids to compute_loss, which updates it."""
+    import mixtureofexperts_b200 as m
+
+    T, D, H, O, E, S = 64, 32, 48, 32, 6, 2
+    x, w = orc.make_layer_inputs(4, T, D, H, O, E, e_router=E - S, init="normal", std=0.25)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(2), balance_alpha=0.001, num_shared_experts=S)
+    o_out, _, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+    start = np.array([3, -1, 2, -2, 1, -3], dtype=np.float32)
+    st = orc.AuxFreeState(bias=start.copy(), bias_momentum=np.zeros(E, dtype=np.float32), learning_rate=1.0)
+    orc.aux_free_update_bias(st, aux["indices"])
+    bl = m.AuxiliaryFreeLoss(E, learning_rate=1.0, bias=start)
+    layer = make_device_layer(w, D=D, H=H, O=O, gate=m.TopKGating(2), balance_loss=bl, num_shared_experts=S)
+    assert not layer._aux_on_device
+    out, _, routing = layer(torch.from_numpy(x).cuda().t(), training=True, return_routing=True)
+    assert np.array_equal(routing["indices"].cpu().numpy().T, aux["indices"])       # the bias did not select
+    assert rel_inf(out.cpu().numpy().T, o_out) < F32_TOL
+    assert bl.update_counter == 1 and np.array_equal(bl.bias, st.bias)
+    layer.close()
+    with pytest.raises(m.MoEError):
+        make_device_layer(w, D=D, H=H, O=O, gate=m.TopKGating(2), balance_loss=m.AuxiliaryFreeLoss(E - S),
+                          num_shared_experts=S)
+
+
 def test_router_bias_skews_routing_like_config4():
     """A per-expert logit bias N(0,1.5) that is part of the logits (the skew of the DeepSeek-style benchmark configuration)."""
     T, D, H, O, E, S, k = 300, 64, 96, 64, 18, 2, 6
