@@ -137,6 +137,17 @@ int moe_layer_set_expert(moe_layer_t*, int expert, const void* w1, const void* w
 int moe_layer_set_expert_standard(moe_layer_t*, int expert, const void* w1, const float* b1, const void* w2,
                                   const float* b2, int src_dtype, int layout, int src_is_device);
 
+/* Weight image: everything serialize_moe_layer stores for one MoE layer (router_weight and every
+ * expert's w1/w2/w3, src/llama2/utils.jl:258-303; plus biases and the noise network where the layer
+ * has them) as ONE host blob in the library's own device layout and compute dtype.  A 128-byte
+ * header ("MOEB200W", version, dtype, expert kind, dims, section offsets) is followed by 256-byte
+ * aligned sections.  Import is a plain host->device copy per section, no repacking: it needs a
+ * handle created with the same config (and the same expert-parallel split) and replaces
+ * moe_layer_set_expert / moe_layer_set_router.  `bytes` is the size of the caller's buffer. */
+int64_t moe_layer_weights_image_bytes(moe_layer_t*);          /* -1 on error (weights not all set) */
+int moe_layer_export_weights(moe_layer_t*, void* dst_host, int64_t bytes);
+int moe_layer_import_weights(moe_layer_t*, const void* src_host, int64_t bytes);
+
 /* Router.weight (src/core/router.jl:14-23): FP32 (E_router x D), E_router = E - S.
  * (E_router = E in GATING mode: the first S rows are present but unused by the gate.)
  * logit_bias: optional FP32 [E_router] added to the logits (see bias_gates_only). */

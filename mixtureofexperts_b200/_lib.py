@@ -21,7 +21,7 @@ LAYOUT_IN_CONTIG, LAYOUT_OUT_CONTIG = 0, 1
 EXPERT_GATED, EXPERT_STANDARD = 0, 1
 
 EXPORTS = [
-    "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_expert_standard", "moe_layer_set_router", "moe_layer_set_router_noise", "moe_layer_set_aux_free", "moe_layer_aux_free_state", "moe_layer_set_router_noise_network", "moe_layer_dims",
+    "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_expert_standard", "moe_layer_set_router", "moe_layer_set_router_noise", "moe_layer_weights_image_bytes", "moe_layer_export_weights", "moe_layer_import_weights", "moe_layer_set_aux_free", "moe_layer_aux_free_state", "moe_layer_set_router_noise_network", "moe_layer_dims",
     "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_gates_jitter", "moe_compute_loss",
     "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_launch_count",
     "moe_layer_device_status", "moe_ep_unique_id", "moe_ep_init", "moe_ep_layout", "moe_layer_destroy",
@@ -69,6 +69,10 @@ def _load():
     lib.moe_layer_set_router_noise_network.argtypes = [vp, vp, i32, i32]
     lib.moe_layer_set_aux_free.argtypes = [vp, i32, C.c_float, C.c_float, i32, vp, i64]
     lib.moe_layer_aux_free_state.argtypes = [vp, vp, vp, vp]
+    lib.moe_layer_weights_image_bytes.argtypes = [vp]
+    lib.moe_layer_weights_image_bytes.restype = i64
+    lib.moe_layer_export_weights.argtypes = [vp, vp, i64]
+    lib.moe_layer_import_weights.argtypes = [vp, vp, i64]
     lib.moe_layer_set_router.argtypes = [vp, vp, vp, i32, i32]
     lib.moe_layer_set_router_noise.argtypes = [vp, vp, f32]
     lib.moe_layer_dims.argtypes = [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]

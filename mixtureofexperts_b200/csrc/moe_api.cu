@@ -784,6 +784,158 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     return MOE_OK;
 }
 
+// ---- weight image: the layer's device-resident weights as one relocatable host blob ---------------------
+namespace {
+
+struct WeightImageHeader {       // 128 bytes, little-endian like the device
+    char magic[8];               // "MOEB200W"
+    int32_t version;             // 1
+    int32_t compute_dtype, expert_kind;
+    int32_t e_lo, e_hi;          // experts held (all of them without expert parallelism)
+    int32_t input_dim, hidden_dim, output_dim;
+    int32_t e_router, has_bias, has_noise_net;
+    int32_t reserved0;
+    int64_t total_bytes;
+    int64_t off_w1, off_w3, off_w2, off_b1, off_b2, off_router, off_bias, off_noise;   // 0 = absent
+};
+static_assert(sizeof(WeightImageHeader) == 128, "weight image header layout");
+
+struct WeightImageSection {
+    int64_t WeightImageHeader::*off;
+    void* ptr;
+    size_t bytes;
+};
+
+// the sections present for this handle, in file order, and the header describing them
+int weight_image_plan(moe_layer* L, WeightImageHeader* h, WeightImageSection (&sec)[8]) {
+    const size_t el = dtype_size(L->cfg.compute_dtype);
+    const size_t n = (size_t)(L->e_hi - L->e_lo);
+    const size_t D = L->cfg.input_dim, H = L->cfg.hidden_dim, O = L->cfg.output_dim, R = L->E_router;
+    const bool standard = L->cfg.expert_kind == MOE_EXPERT_STANDARD;
+    memset(h, 0, sizeof(*h));
+    memcpy(h->magic, "MOEB200W", 8);
+    h->version = 1;
+    h->compute_dtype = L->cfg.compute_dtype;
+    h->expert_kind = L->cfg.expert_kind;
+    h->e_lo = L->e_lo;
+    h->e_hi = L->e_hi;
+    h->input_dim = (int)D;
+    h->hidden_dim = (int)H;
+    h->output_dim = (int)O;
+    h->e_router = (int)R;
+    h->has_bias = L->has_bias ? 1 : 0;
+    h->has_noise_net = L->router_nw ? 1 : 0;
+    const WeightImageSection all[8] = {
+        {&WeightImageHeader::off_w1, L->w1, n * H * D * el},
+        {&WeightImageHeader::off_w3, standard ? nullptr : L->w3, n * H * D * el},
+        {&WeightImageHeader::off_w2, L->w2, n * O * H * el},
+        {&WeightImageHeader::off_b1, standard ? L->b1 : nullptr, n * H * sizeof(float)},
+        {&WeightImageHeader::off_b2, standard ? L->b2 : nullptr, n * O * sizeof(float)},
+        {&WeightImageHeader::off_router, L->router_w, R * D * sizeof(float)},
+        {&WeightImageHeader::off_bias, L->has_bias ? L->router_bias : nullptr, R * sizeof(float)},
+        {&WeightImageHeader::off_noise, L->router_nw, R * D * sizeof(float)},
+    };
+    int64_t off = sizeof(WeightImageHeader);
+    for (int i = 0; i < 8; ++i) {
+        sec[i] = all[i];
+        if (!sec[i].ptr) continue;
+        off = (off + 255) & ~(int64_t)255;
+        h->*(sec[i].off) = off;
+        off += (int64_t)sec[i].bytes;
+    }
+    h->total_bytes = off;
+    return MOE_OK;
+}
+
+}  // namespace
+
+int64_t moe_layer_weights_image_bytes(moe_layer_t* L) {
+    if (!L) {
+        fail(MOE_ERR_INVALID, "null handle");
+        return -1;
+    }
+    if (check_ready(L)) return -1;
+    WeightImageHeader h;
+    WeightImageSection sec[8];
+    weight_image_plan(L, &h, sec);
+    return h.total_bytes;
+}
+
+int moe_layer_export_weights(moe_layer_t* L, void* dst, int64_t bytes) {
+    if (!L || !dst) return fail(MOE_ERR_INVALID, "null argument");
+    int rc = check_ready(L);
+    if (rc) return rc;
+    WeightImageHeader h;
+    WeightImageSection sec[8];
+    weight_image_plan(L, &h, sec);
+    if (bytes < h.total_bytes) return fail(MOE_ERR_INVALID, "the image needs %lld bytes, got %lld", (long long)h.total_bytes, (long long)bytes);
+    CUDA_TRY(cudaSetDevice(L->device));
+    CUDA_TRY(cudaDeviceSynchronize());   // bias updates queued on the callers' streams
+    memset(dst, 0, (size_t)h.total_bytes);
+    memcpy(dst, &h, sizeof(h));
+    for (const WeightImageSection& s : sec)
+        if (s.ptr) CUDA_TRY(cudaMemcpy((char*)dst + h.*(s.off), s.ptr, s.bytes, cudaMemcpyDeviceToHost));
+    return MOE_OK;
+}
+
+int moe_layer_import_weights(moe_layer_t* L, const void* src, int64_t bytes) {
+    if (!L || !src) return fail(MOE_ERR_INVALID, "null argument");
+    if (bytes < (int64_t)sizeof(WeightImageHeader)) return fail(MOE_ERR_INVALID, "not a weight image: too short");
+    WeightImageHeader in;
+    memcpy(&in, src, sizeof(in));
+    if (memcmp(in.magic, "MOEB200W", 8) != 0) return fail(MOE_ERR_INVALID, "not a weight image: bad magic");
+    if (in.version != 1) return fail(MOE_ERR_UNSUPPORTED, "weight image version %d is not supported", in.version);
+    CUDA_TRY(cudaSetDevice(L->device));
+    int rc = ensure_weights(L);
+    if (rc) return rc;
+    if (in.compute_dtype != L->cfg.compute_dtype || in.expert_kind != L->cfg.expert_kind || in.e_lo != L->e_lo ||
+        in.e_hi != L->e_hi || in.input_dim != L->cfg.input_dim || in.hidden_dim != L->cfg.hidden_dim ||
+        in.output_dim != L->cfg.output_dim || in.e_router != L->E_router)
+        return fail(MOE_ERR_INVALID,
+                    "the weight image (dtype %d, kind %d, experts %d..%d, %d/%d/%d, %d router rows) does not match "
+                    "this layer (dtype %d, kind %d, experts %d..%d, %d/%d/%d, %d router rows)",
+                    in.compute_dtype, in.expert_kind, in.e_lo, in.e_hi - 1, in.input_dim, in.hidden_dim, in.output_dim,
+                    in.e_router, L->cfg.compute_dtype, L->cfg.expert_kind, L->e_lo, L->e_hi - 1, L->cfg.input_dim,
+                    L->cfg.hidden_dim, L->cfg.output_dim, L->E_router);
+    if (in.has_noise_net && 2 * L->E_router > MAX_ROUTER_EXPERTS)
+        return fail(MOE_ERR_UNSUPPORTED, "a router noise network needs 2*%d <= %d router rows", L->E_router, MAX_ROUTER_EXPERTS);
+    // the image decides whether the bias and the noise network exist; lay the handle out like it first
+    if (in.has_noise_net && !L->router_nw) {
+        const size_t D = L->cfg.input_dim;
+        if ((rc = dev_alloc(&L->router_nw, (size_t)L->E_router * D))) return rc;
+        if ((rc = dev_alloc(&L->router_wt_noise, (size_t)router_e_pad(2 * L->E_router) * router_d_pad((int)D)))) return rc;
+    } else if (!in.has_noise_net && L->router_nw) {
+        CUDA_TRY(cudaDeviceSynchronize());
+        dev_free(L->router_nw);
+        dev_free(L->router_wt_noise);
+        L->router_nw = L->router_wt_noise = nullptr;
+    }
+    L->has_bias = in.has_bias != 0;
+    WeightImageHeader want;
+    WeightImageSection sec[8];
+    weight_image_plan(L, &want, sec);
+    if (in.total_bytes != want.total_bytes || bytes < in.total_bytes)
+        return fail(MOE_ERR_INVALID, "weight image is %lld bytes (buffer %lld), this layer's is %lld",
+                    (long long)in.total_bytes, (long long)bytes, (long long)want.total_bytes);
+    for (const WeightImageSection& s : sec) {
+        if (!s.ptr) continue;
+        if (in.*(s.off) != want.*(s.off)) return fail(MOE_ERR_INVALID, "weight image sections are laid out differently");
+        CUDA_TRY(cudaMemcpyAsync(s.ptr, (const char*)src + in.*(s.off), s.bytes, cudaMemcpyHostToDevice, L->stream));
+    }
+    int n = launch_router_transpose(L->router_w, L->router_wt, L->E_router, L->cfg.input_dim, L->stream);
+    if (n < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n;
+    if (L->router_nw) {
+        n = launch_router_transpose_noise(L->router_w, L->router_nw, L->router_wt_noise, L->E_router, L->cfg.input_dim, L->stream);
+        if (n < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n;
+    }
+    CUDA_TRY(cudaStreamSynchronize(L->stream));
+    L->expert_set.assign(L->expert_set.size(), 1);
+    L->router_set = true;
+    return MOE_OK;
+}
+
 int moe_layer_set_aux_free(moe_layer_t* L, int enable, float learning_rate, float momentum, int update_freq,
                            const float* bias_momentum, int64_t update_counter) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");

@@ -158,10 +158,12 @@ class MoELayer:
     Extra keywords (no counterpart in the reference): ``device`` (CUDA ordinal),
     ``compute_dtype`` ("f32": FP32 FMA path, 1e-5 parity class; "bf16": tcgen05 tensor cores),
     ``experts`` / ``router`` to inject pre-built weights, ``rng`` to seed the default init,
-    ``weights_on_device`` to draw the default expert weights on the GPU."""
+    ``weights_on_device`` to draw the default expert weights on the GPU, ``weight_image`` (bytes
+    or a uint8 array made by ``export_weights``) to load every weight with plain copies instead:
+    the layer then keeps no host copy of experts or router."""
 
     def __init__(self, config: MoEConfig, *, device: int = 0, compute_dtype: str = "f32", experts=None, router=None,
-                 rng=None, weights_on_device: bool = False, expert_parallel=None):
+                 rng=None, weights_on_device: bool = False, expert_parallel=None, weight_image=None):
         self.config = config
         self.device = int(device)
         self.compute_dtype = compute_dtype
@@ -209,6 +211,16 @@ class MoELayer:
             per = config.num_experts // world
             self.expert_range = range(rank * per, (rank + 1) * per)
 
+        if weight_image is not None:
+            self._expert_factory, self.experts, self.router = None, [None] * config.num_experts, None
+            self._stats = {"tokens_per_expert": np.zeros(config.num_experts, dtype=np.int64),
+                           "routing_entropy": [], "capacity_overflow": 0}
+            self._pending = []
+            self._aux_on_device = False
+            self.import_weights(weight_image)
+            if isinstance(self.balance_loss, AuxiliaryFreeLoss):
+                self._attach_aux_free(expert_parallel is not None)
+            return
         if experts is None:
             dev = f"cuda:{self.device}" if weights_on_device else None
             make = GatedExpert if self.gated else StandardExpert
@@ -242,9 +254,28 @@ class MoELayer:
         return self._stats
 
     # -- weights ---------------------------------------------------------------------------
+    def export_weights(self) -> np.ndarray:
+        """The layer's device-resident weights (experts, router, bias, noise network) as one uint8
+        array in the library's own layout and compute dtype: what serialize_moe_layer
+        (src/llama2/utils.jl:258-303) stores for a layer, ready to be loaded without repacking."""
+        n = int(_lib.lib.moe_layer_weights_image_bytes(self._handle))
+        if n < 0:
+            raise _lib.MoEError(_lib.ERR_STATE, _lib.lib.moe_last_error().decode("utf-8", "replace"))
+        img = np.empty(n, dtype=np.uint8)
+        _lib.check(_lib.lib.moe_layer_export_weights(self._handle, img.ctypes.data, n))
+        return img
+
+    def import_weights(self, image) -> None:
+        """Load an ``export_weights`` image made by a layer of the same configuration."""
+        img = np.frombuffer(image, dtype=np.uint8) if isinstance(image, (bytes, bytearray, memoryview)) else \
+            np.ascontiguousarray(image, dtype=np.uint8)
+        _lib.check(_lib.lib.moe_layer_import_weights(self._handle, img.ctypes.data, img.size))
+
     def sync_weights(self) -> None:
         """Copy (and repack) the experts' and the router's current weights into the device
         handle; call again after mutating them."""
+        if self.router is None:
+            raise _lib.MoEError(_lib.ERR_STATE, "this layer was loaded from a weight image: it has no host weights to sync")
         for e in self.expert_range:
             ex = self._expert_factory(e) if self._expert_factory else self.experts[e]
             p1, d1, l1, dev1, k1 = _weight_ptr_layout(ex.w1)
@@ -316,6 +347,8 @@ class MoELayer:
         return ptr, keep
 
     def sync_router(self) -> None:
+        if self.router is None:
+            raise _lib.MoEError(_lib.ERR_STATE, "this layer was loaded from a weight image: it has no host weights to sync")
         w = self.router.weight
         p, d, lay, dev, keep = _weight_ptr_layout(w)
         if d != _lib.DTYPE_F32:

@@ -15,7 +15,10 @@ once per layer instead of once per token; generation then proceeds token by toke
 """
 from __future__ import annotations
 
+import json
 import math
+import struct
+import time
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -126,6 +129,8 @@ class MoETransformerLayerWeights:
     moe_router_weight: Optional[np.ndarray] = None     # (E, dim)   reference: (dim x E)
     moe_config: Optional[MoEConfig] = None
     _device_layer: Optional[MoELayer] = field(default=None, repr=False)
+    # a loaded model holds the layer as a weight image (MoELayer.export_weights) until first use
+    _weight_image: Optional[np.ndarray] = field(default=None, repr=False)
 
 
 @dataclass
@@ -257,7 +262,10 @@ def count_parameters(model: MoELanguageModel) -> int:
     for l in model.layers:
         ll = l.llama_layer
         n += sum(a.size for a in (ll.rms_att_weight, ll.rms_ffn_weight, ll.wq, ll.wk, ll.wv, ll.wo))
-        if l.use_moe:
+        if l.use_moe and l.moe_experts is None:      # loaded from a weight image: count from the shapes
+            mc = l.moe_config
+            n += mc.num_experts * (mc.input_dim + mc.hidden_dim * (2 * mc.input_dim + mc.output_dim))
+        elif l.use_moe:
             n += l.moe_router_weight.size + sum(e.w1.size + e.w2.size + e.w3.size for e in l.moe_experts)
         else:
             n += ll.w1.size + ll.w2.size + ll.w3.size
@@ -270,8 +278,8 @@ def count_active_parameters(model: MoELanguageModel) -> int:
     for l in model.layers:
         ll = l.llama_layer
         n += sum(a.size for a in (ll.rms_att_weight, ll.rms_ffn_weight, ll.wq, ll.wk, ll.wv, ll.wo))
-        per = ll.w1.size + ll.w2.size + ll.w3.size
-        n += (l.moe_router_weight.size + model.config.moe_top_k * per) if l.use_moe else per
+        per = 3 * model.config.dim * model.config.hidden_dim
+        n += (model.config.moe_num_experts * model.config.dim + model.config.moe_top_k * per) if l.use_moe else per
     return int(n)
 
 
@@ -280,6 +288,10 @@ def count_active_parameters(model: MoELanguageModel) -> int:
 def _device_layer(model: MoELanguageModel, l: MoETransformerLayerWeights) -> MoELayer:
     """The layer's libmoe_b200 handle, built on first use from the Llama2-layout weights (which
     are (out, in) C-order arrays, i.e. MOE_LAYOUT_IN_CONTIG: no transpose on the way in)."""
+    if l._device_layer is None and l._weight_image is not None:
+        l._device_layer = MoELayer(l.moe_config, device=model.device, compute_dtype=model.compute_dtype,
+                                   weight_image=l._weight_image)
+        l._weight_image = None
     if l._device_layer is None:
         cfg = l.moe_config
         experts = []
@@ -440,3 +452,166 @@ def sample_moe(model: MoELanguageModel, prompt: str = "", *, temperature: float 
     if verbose:
         print(text)
     return text
+
+
+# ---- save / load (src/llama2/utils.jl:22-113) -------------------------------------------------
+
+MODEL_MAGIC = b"MOEB200M"
+_LAYER_ARRAYS = ("rms_att_weight", "rms_ffn_weight", "wq", "wk", "wv", "wo")
+_FFN_ARRAYS = ("w1", "w2", "w3")
+
+
+def _gate_to_dict(g) -> dict:
+    return {"name": type(g).__name__, "k": int(getattr(g, "k", 1))}
+
+
+def _gate_from_dict(d: dict):
+    """reconstruct_gate_type (src/llama2/utils.jl): by type name and top_k."""
+    from .gating import SwitchGating
+
+    if d["name"] == "TopKGating":
+        return TopKGating(int(d["k"]))
+    if d["name"] == "SwitchGating":
+        return SwitchGating()
+    raise _lib.MoEError(_lib.ERR_UNSUPPORTED, f"gate {d['name']} cannot be restored")
+
+
+def serialize_config(config: MoELlamaConfig) -> dict:
+    """serialize_config (src/llama2/utils.jl:119-153): the same keys for the fields this package has."""
+    c = config.llama_config
+    loss = config.moe_balance_loss
+    return {
+        "dim": c.dim, "hidden_dim": c.hidden_dim, "n_layers": c.n_layers, "n_heads": c.n_heads,
+        "n_kv_heads": c.n_kv_heads, "vocab_size": c.vocab_size, "seq_len": c.seq_len,
+        "rope_freq_base": float(getattr(c, "rope_freq_base", 10000.0)), "rope_is_neox": bool(getattr(c, "rope_is_neox", False)),
+        "moe_layers": list(config.moe_layers), "moe_num_experts": config.moe_num_experts, "moe_top_k": config.moe_top_k,
+        "moe_expert_type": config.moe_expert_type, "expert_init_strategy": config.expert_init_strategy,
+        "expert_init_noise": float(config.expert_init_noise), "z_loss_weight": float(config.z_loss_weight),
+        "gate_type_name": type(config.moe_gate_type).__name__, "gate": _gate_to_dict(config.moe_gate_type),
+        "balance_loss_name": type(loss).__name__, "balance_loss_alpha": float(getattr(loss, "alpha", 0.01)),
+    }
+
+
+def deserialize_config(d: dict) -> MoELlamaConfig:
+    """deserialize_config (src/llama2/utils.jl:160-206)."""
+    fields_ = {k: d[k] for k in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size", "seq_len")}
+    for opt in ("rope_freq_base", "rope_is_neox"):
+        if opt in ModelConfig.__dataclass_fields__:
+            fields_[opt] = d[opt]
+    if d["balance_loss_name"] != "SwitchTransformerLoss":
+        raise _lib.MoEError(_lib.ERR_UNSUPPORTED, f"balance loss {d['balance_loss_name']} cannot be restored")
+    return MoELlamaConfig(llama_config=ModelConfig(**fields_), moe_layers=[int(v) for v in d["moe_layers"]],
+                          moe_num_experts=int(d["moe_num_experts"]), moe_top_k=int(d["moe_top_k"]),
+                          moe_expert_type=d["moe_expert_type"], moe_gate_type=_gate_from_dict(d["gate"]),
+                          moe_balance_loss=SwitchTransformerLoss(float(d["balance_loss_alpha"])),
+                          expert_init_strategy=d["expert_init_strategy"], expert_init_noise=float(d["expert_init_noise"]),
+                          z_loss_weight=float(d["z_loss_weight"]))
+
+
+def _write_container(filename: str, header: dict, arrays: dict) -> None:
+    """File = MODEL_MAGIC, u32 version, u64 JSON length, JSON, then every array's raw bytes at the
+    256-byte aligned offset its JSON entry names."""
+    index, off = {}, 0
+    for name, a in arrays.items():
+        a = np.ascontiguousarray(a)
+        arrays[name] = a
+        index[name] = {"dtype": a.dtype.str, "shape": list(a.shape), "offset": off, "nbytes": int(a.nbytes)}
+        off = (off + a.nbytes + 255) & ~255
+    blob = json.dumps(dict(header, arrays=index)).encode("utf-8")
+    head = MODEL_MAGIC + struct.pack("<IQ", 1, len(blob)) + blob
+    base = (len(head) + 255) & ~255
+    with open(filename, "wb") as f:
+        f.write(head)
+        f.write(b"\0" * (base - len(head)))
+        for name, a in arrays.items():
+            f.seek(base + index[name]["offset"])
+            f.write(a.tobytes() if a.nbytes < (1 << 20) else memoryview(a).cast("B"))
+        f.truncate(base + off)
+
+
+def _read_container(filename: str):
+    with open(filename, "rb") as f:
+        magic = f.read(8)
+        if magic != MODEL_MAGIC:
+            raise ValueError(f"{filename} is not a saved MoE model (bad magic)")
+        version, n = struct.unpack("<IQ", f.read(12))
+        if version != 1:
+            raise ValueError(f"saved model version {version} is not supported")
+        header = json.loads(f.read(n).decode("utf-8"))
+        base = (20 + n + 255) & ~255
+        arrays = {}
+        for name, e in header.pop("arrays").items():
+            f.seek(base + e["offset"])
+            buf = f.read(e["nbytes"])
+            if len(buf) != e["nbytes"]:
+                raise ValueError(f"{filename} is truncated at array {name}")
+            arrays[name] = np.frombuffer(buf, dtype=np.dtype(e["dtype"])).reshape(e["shape"])
+    return header, arrays
+
+
+def save_moe_model(model: MoELanguageModel, filename: str, *, format: str = "device") -> None:
+    """save_moe_model(model, filename) (src/llama2/utils.jl:22-36).  The reference writes Julia's
+    Serialization format; here the file is a self-describing container whose MoE layers are stored
+    as device weight images (``MoELayer.export_weights``: the library's own layout in the model's
+    compute dtype), so ``load_moe_model`` brings a layer back with plain copies.  The dense
+    weights are float32 arrays.  ``format="both"`` also writes ``<name>_metadata.json`` like the
+    reference's ``:both``."""
+    fmt = str(format).lstrip(":")
+    if fmt not in ("device", "julia", "json", "both"):
+        raise ValueError(f"unknown format {format!r}")
+    header = {
+        "config": serialize_config(model.config),
+        "metadata": {"model_type": "MoELanguageModel", "save_timestamp": time.strftime("%Y-%m-%dT%H:%M:%S"),
+                     "library_version": _lib.version(), "compute_dtype": model.compute_dtype},
+        "statistics": {"total_parameters": count_parameters(model), "active_parameters": count_active_parameters(model)},
+        "layers": [{"layer_index": i + 1, "use_moe": bool(l.use_moe)} for i, l in enumerate(model.layers)],
+    }
+    if fmt in ("json", "both"):
+        stem = filename.rsplit(".", 1)[0] if "." in filename.rsplit("/", 1)[-1] else filename
+        with open(stem + "_metadata.json", "w") as f:
+            json.dump(header, f, indent=1)
+        if fmt == "json":
+            return
+    arrays = {"token_embedding_table": model.token_embedding_table, "rms_final_weight": model.rms_final_weight,
+              "output_weight": model.output_weight}
+    for i, l in enumerate(model.layers):
+        for name in _LAYER_ARRAYS:
+            arrays[f"layers.{i}.{name}"] = getattr(l.llama_layer, name)
+        if l.use_moe:
+            arrays[f"layers.{i}.moe_image"] = (l._weight_image if l._device_layer is None and l._weight_image is not None
+                                               else _device_layer(model, l).export_weights())
+        else:
+            for name in _FFN_ARRAYS:
+                arrays[f"layers.{i}.{name}"] = getattr(l.llama_layer, name)
+    _write_container(filename, header, arrays)
+
+
+def load_moe_model(filename: str, *, device: int = 0) -> MoELanguageModel:
+    """load_moe_model(filename) (src/llama2/utils.jl:73-113): the model comes back with its MoE
+    layers as weight images; each becomes a device handle on first use, without the experts ever
+    existing as host arrays (``moe_experts`` is None for such a layer)."""
+    header, arrays = _read_container(filename)
+    for key in ("config", "metadata", "layers"):               # validate_save_data
+        if key not in header:
+            raise ValueError(f"{filename}: missing section {key!r}")
+    cfg = deserialize_config(header["config"])
+    c = cfg.llama_config
+    empty = np.zeros((0, 0), dtype=np.float32)
+    layers = []
+    for i, meta in enumerate(header["layers"]):
+        dense = {name: np.array(arrays[f"layers.{i}.{name}"]) for name in _LAYER_ARRAYS}
+        if not meta["use_moe"]:
+            dense.update({name: np.array(arrays[f"layers.{i}.{name}"]) for name in _FFN_ARRAYS})
+            layers.append(MoETransformerLayerWeights(llama_layer=TransformerLayerWeights(**dense), use_moe=False))
+            continue
+        dense.update({name: empty for name in _FFN_ARRAYS})
+        layer_cfg = MoEConfig(num_experts=cfg.moe_num_experts, expert_type=cfg.moe_expert_type, input_dim=c.dim,
+                              hidden_dim=c.hidden_dim, output_dim=c.dim, activation=silu, gate_type=cfg.moe_gate_type,
+                              top_k=cfg.moe_top_k, balance_loss=cfg.moe_balance_loss, z_loss_weight=cfg.z_loss_weight)
+        layers.append(MoETransformerLayerWeights(llama_layer=TransformerLayerWeights(**dense), use_moe=True,
+                                                 moe_config=layer_cfg, _weight_image=np.array(arrays[f"layers.{i}.moe_image"])))
+    return MoELanguageModel(config=cfg, tokenizer=CharTokenizer(c.vocab_size),
+                            token_embedding_table=np.array(arrays["token_embedding_table"]),
+                            rms_final_weight=np.array(arrays["rms_final_weight"]),
+                            output_weight=np.array(arrays["output_weight"]), layers=layers, device=device,
+                            compute_dtype=header["metadata"].get("compute_dtype", "f32"))

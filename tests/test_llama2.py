@@ -138,3 +138,127 @@ def test_sample_moe_generates_and_is_deterministic():
     assert len(c) > 0
     with pytest.raises(ValueError):
         m.sample_moe(mm, "", bos_token=False)
+
+
+def test_model_container_round_trip(lib_built, tmp_path):
+    """The file format of save_moe_model / load_moe_model on its own: header JSON plus aligned raw
+    arrays, truncation and foreign files are refused."""
+    from mixtureofexperts_b200 import llama2
+
+    arrays = {"a": np.arange(12, dtype=np.float32).reshape(3, 4), "img": np.arange(1000, dtype=np.uint8),
+              "empty": np.zeros((0, 0), dtype=np.float32), "big": np.ones((600, 500), dtype=np.float32)}
+    path = str(tmp_path / "m.moeb200")
+    llama2._write_container(path, {"config": {"x": 1}, "metadata": {}, "layers": []}, dict(arrays))
+    header, got = llama2._read_container(path)
+    assert header["config"] == {"x": 1} and set(got) == set(arrays)
+    for k_, v in arrays.items():
+        assert got[k_].dtype == v.dtype and got[k_].shape == v.shape and np.array_equal(got[k_], v)
+    raw = open(path, "rb").read()
+    assert raw[:8] == b"MOEB200M" and len(raw) % 256 == 0
+    open(path, "wb").write(raw[:len(raw) // 2])
+    with pytest.raises(ValueError):
+        llama2._read_container(path)
+    open(path, "wb").write(b"not a model file at all")
+    with pytest.raises(ValueError):
+        llama2.load_moe_model(path)
+
+
+def test_config_serialisation_round_trip(lib_built):
+    import mixtureofexperts_b200 as m
+    from mixtureofexperts_b200 import llama2
+
+    mm = m.convert_to_moe(small_model(m), [2], num_experts=4, top_k=1, gate_type=m.SwitchGating(), seed=1,
+                          balance_loss=m.SwitchTransformerLoss(0.05), z_loss_weight=0.0)
+    d = llama2.serialize_config(mm.config)
+    # the reference's keys (src/llama2/utils.jl:119-153)
+    for key in ("dim", "hidden_dim", "n_layers", "moe_layers", "moe_num_experts", "moe_top_k", "moe_expert_type",
+                "expert_init_strategy", "expert_init_noise", "z_loss_weight", "gate_type_name", "balance_loss_name"):
+        assert key in d
+    back = llama2.deserialize_config(d)
+    assert back.llama_config == mm.config.llama_config and back.moe_layers == [2] and back.moe_top_k == 1
+    assert isinstance(back.moe_gate_type, m.SwitchGating) and back.moe_balance_loss.alpha == 0.05
+    assert back.z_loss_weight == 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("compute_dtype", ["f32", "bf16"])
+def test_save_and_load_moe_model_round_trip(compute_dtype, tmp_path):
+    """save_moe_model / load_moe_model (src/llama2/utils.jl:22-113): the loaded model, whose MoE layers
+    come back as device weight images, produces bit-identical logits and expert choices; the weight
+    image of a layer is refused by a layer of another shape."""
+    import json
+
+    import mixtureofexperts_b200 as m
+
+    lm = small_model(m, seed=3)
+    mm = m.convert_to_moe(lm, [1, 3], num_experts=4, top_k=2, seed=4, compute_dtype=compute_dtype)
+    toks = np.random.default_rng(5).integers(0, 300, 20)
+    st = m.MoERunState(mm, 20)
+    want = m.moe_transformer(toks, mm, st)
+    path = str(tmp_path / "model.moeb200")
+    m.save_moe_model(mm, path, format="both")
+    meta = json.load(open(str(tmp_path / "model_metadata.json")))
+    assert meta["metadata"]["model_type"] == "MoELanguageModel" and meta["config"]["moe_layers"] == [1, 3]
+    assert meta["statistics"]["total_parameters"] == m.count_parameters(mm)
+    back = m.load_moe_model(path)
+    assert [l.use_moe for l in back.layers] == [True, False, True] and back.compute_dtype == compute_dtype
+    assert back.layers[0].moe_experts is None and back.layers[0]._weight_image is not None
+    assert m.count_parameters(back) == m.count_parameters(mm)
+    assert m.count_active_parameters(back) == m.count_active_parameters(mm)
+    st2 = m.MoERunState(back, 20)
+    got = m.moe_transformer(toks, back, st2)
+    assert np.array_equal(got, want)
+    for li in (0, 2):
+        assert np.array_equal(st2.selected_experts[li], st.selected_experts[li])
+    assert back.layers[0]._weight_image is None                     # handed to the device on first use
+    # saving the loaded model again writes the same weight images
+    path2 = str(tmp_path / "again.moeb200")
+    m.save_moe_model(back, path2)
+    from mixtureofexperts_b200 import llama2
+
+    a, b = llama2._read_container(path)[1], llama2._read_container(path2)[1]
+    assert all(np.array_equal(a[k_], b[k_]) for k_ in a)
+    # a layer of another shape refuses the image
+    other = m.MoELayer(m.create_moe_config(num_experts=4, expert_type="gated", input_dim=64, hidden_dim=80,
+                                           output_dim=64, activation=m.silu, gate_type=m.TopKGating(2)),
+                       compute_dtype=compute_dtype)
+    with pytest.raises(m.MoEError):
+        other.import_weights(a["layers.0.moe_image"])
+    with pytest.raises(m.MoEError):
+        other.import_weights(b"garbage" * 40)
+    other.close()
+
+
+@pytest.mark.gpu
+def test_weight_image_carries_standard_experts_bias_and_noise_network():
+    import mixtureofexperts_b200 as m
+
+    cfg = m.create_moe_config(num_experts=6, expert_type="standard", input_dim=40, hidden_dim=56, output_dim=24,
+                              activation=m.gelu, gate_type=m.TopKGating(2), noise_scale=0.2, use_noise_network=True)
+    src = m.MoELayer(cfg, rng=3)
+    for e in src.experts:
+        e.b1[:] = np.random.default_rng(1).standard_normal(56).astype(np.float32)
+        e.b2[:] = 0.5
+    src.router.bias = np.linspace(-1, 1, 6).astype(np.float32)
+    src.sync_weights()
+    img = src.export_weights()
+    assert bytes(img[:8]) == b"MOEB200W" and img.size % 1 == 0
+    dst = m.MoELayer(cfg, weight_image=img)
+    assert dst.router is None and dst.experts == [None] * 6
+    import torch
+
+    x = torch.randn((40, 77), device="cuda")
+    noise = torch.randn((6, 77), device="cuda")
+    a = src(x, training=True, router_noise=noise)
+    src.router.noise_scale = dst_scale = 0.2
+    # the loaded layer has no host router object: arm the noise through the C ABI like the layer does
+    from mixtureofexperts_b200 import _lib
+
+    nz = noise.t().contiguous()
+    torch.cuda.synchronize()
+    _lib.check(_lib.lib.moe_layer_set_router_noise(dst._handle, nz.data_ptr(), dst_scale))
+    b = dst(x, training=True)
+    assert torch.equal(a[0], b[0]) and float(a[1].item()) == float(b[1].item())
+    assert np.array_equal(dst.export_weights(), img)
+    src.close()
+    dst.close()
