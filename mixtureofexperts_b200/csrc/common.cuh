@@ -24,7 +24,7 @@ enum : int32_t {
 constexpr int ROUTER_THREADS = 256;
 constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
 constexpr int ROUTER_MAX_WARPS = 18;    // largest router CTA: 576 threads
-constexpr int ROUTER_TOKENS_PER_CTA = 64;
+constexpr int ROUTER_TOKENS_PER_CTA = 64;   // largest token tile; router_tokens_per_cta() picks per batch
 constexpr int MAX_ROUTER_EXPERTS = 128; // upper bound on router rows
 constexpr int MAX_EXPERTS = 256;        // upper bound on experts per layer
 constexpr int MAX_KTOT = 16;            // upper bound on selected experts per token
@@ -54,7 +54,7 @@ struct RouterParams {
     int shared_mode;
     int bias_gates_only;
     int index_base;
-    int tokens_per_cta;       // ROUTER_TOKENS_PER_CTA
+    int tokens_per_cta;       // 64, 32 or 16 (router_tokens_per_cta)
     int want_entropy;
     // internal results
     int32_t* idx;             // [T][k_tot] layer expert id, 0-based
@@ -163,8 +163,8 @@ __device__ __forceinline__ T* group_gemm_out_row(const GroupGemmParams& p, int e
 }
 
 // ---- launchers (each returns the number of kernels it launched, or <0 on a launch error) ---
-int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s);
-int router_tokens_per_cta(int e_router);
+int launch_router(const RouterParams& p, int x_dtype, int num_cta, int num_sms, cudaStream_t s);
+int router_tokens_per_cta(int64_t T, int num_sms);   // 64, 32 or 16
 int router_e_pad(int e_router);          // router rows padded to a multiple of 8 (bucketed)
 int router_d_pad(int D);                 // K rows of the K-major copy (multiple of 128)
 int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_t s);

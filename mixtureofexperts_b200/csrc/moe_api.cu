@@ -57,7 +57,6 @@ struct moe_layer {
     int device = 0;
     int num_sms = 0;
     int E = 0, S = 0, k = 0, k_tot = 0, E_router = 0, E_probs = 0;
-    int tokens_per_cta = 0;
     // expert range held by this handle ([0,E) unless expert-parallel)
     int e_lo = 0, e_hi = 0;
 
@@ -121,6 +120,9 @@ struct moe_layer {
     static constexpr int MAX_CHUNKS = 8;
     cudaStream_t s_in = nullptr, s_out = nullptr;
     cudaEvent_t ev_in[MAX_CHUNKS] = {}, ev_done[MAX_CHUNKS] = {};
+    // MOE_B200_HOST_TIMELINE=1: timed events around every chunk's copies, printed to stderr per call
+    bool timeline = false;
+    cudaEvent_t ev_t0 = nullptr, ev_in0[MAX_CHUNKS] = {}, ev_out1[MAX_CHUNKS] = {};
     float* chunk_acc = nullptr;      // [E + E_probs + 3] summed statistics of the chunks
     float* chunk_tmp = nullptr;
     int64_t* chunk_tpe_acc = nullptr;  // [E]
@@ -218,7 +220,7 @@ int ensure_workspace(moe_layer* L, int64_t T) {
     CUDA_TRY(cudaDeviceSynchronize());
     free_workspace(L);
     const int64_t P = T * L->k_tot;
-    const int64_t num_cta = (T + L->tokens_per_cta - 1) / L->tokens_per_cta;
+    const int64_t num_cta = (T + 15) / 16;   // the smallest token tile router_tokens_per_cta() may pick
     const size_t el = dtype_size(L->cfg.compute_dtype);
     int rc;
     if ((rc = dev_alloc(&L->idx, (size_t)P))) return rc;
@@ -368,7 +370,8 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     if ((rc = ensure_workspace(L, T > 0 ? T : 1))) return rc;
     if (!L->ep && L->plan_dirty && (rc = ensure_plan(L, L->xp, L->h, L->P_cap))) return rc;
 
-    const int num_cta = (int)((T + L->tokens_per_cta - 1) / L->tokens_per_cta);
+    const int tokens_per_cta = router_tokens_per_cta(T, L->num_sms);
+    const int num_cta = (int)((T + tokens_per_cta - 1) / tokens_per_cta);
     if (L->prof_slots > 0) L->prof_cur = (int)(L->prof_calls++ % L->prof_slots);
     stage_mark(L, 0, s);
 
@@ -395,7 +398,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     r.shared_mode = c.shared_mode;
     r.bias_gates_only = c.bias_gates_only;
     r.index_base = c.index_base;
-    r.tokens_per_cta = L->tokens_per_cta;
+    r.tokens_per_cta = tokens_per_cta;
     r.want_entropy = opt->routing_entropy != nullptr || partial_want_entropy;
     r.idx = L->idx;
     r.gate = L->gate;
@@ -408,7 +411,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     r.u_logits = opt->logits;
     int n = 0;
     if (num_cta > 0) {
-        n = launch_router(r, x_dtype, num_cta, s);
+        n = launch_router(r, x_dtype, num_cta, L->num_sms, s);
         if (n < 0) return fail(MOE_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += n;
     }
@@ -455,7 +458,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     pp.D = c.input_dim;
     pp.E = L->E;
     pp.k_tot = L->k_tot;
-    pp.tokens_per_cta = L->tokens_per_cta;
+    pp.tokens_per_cta = tokens_per_cta;
     pp.idx = L->idx;
     pp.cta_base = L->cta_counts;
     pp.expert_offset = L->expert_offset;
@@ -605,7 +608,6 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     L->k_tot = L->k + L->S;
     L->E_router = cfg->shared_mode == MOE_SHARED_LAYER_BLEND ? L->E - L->S : L->E;
     L->E_probs = L->E_router;
-    L->tokens_per_cta = router_tokens_per_cta(L->E_router);
     L->e_lo = 0;
     L->e_hi = L->E;
     auto cleanup = [&](int code) {
@@ -659,6 +661,12 @@ int moe_layer_destroy(moe_layer_t* L) {
     if (L->s_in) cudaStreamDestroy(L->s_in);
     if (L->s_out) cudaStreamDestroy(L->s_out);
     for (auto& e : L->ev_in)
+        if (e) cudaEventDestroy(e);
+    for (auto e : {L->ev_t0})
+        if (e) cudaEventDestroy(e);
+    for (auto& e : L->ev_in0)
+        if (e) cudaEventDestroy(e);
+    for (auto& e : L->ev_out1)
         if (e) cudaEventDestroy(e);
     for (auto& e : L->ev_done)
         if (e) cudaEventDestroy(e);
@@ -1085,8 +1093,16 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         if (!L->s_in) {
             CUDA_TRY(cudaStreamCreateWithFlags(&L->s_in, cudaStreamNonBlocking));
             CUDA_TRY(cudaStreamCreateWithFlags(&L->s_out, cudaStreamNonBlocking));
-            for (auto& e : L->ev_in) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-            for (auto& e : L->ev_done) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            const char* tl = getenv("MOE_B200_HOST_TIMELINE");
+            L->timeline = tl && atoi(tl) > 0;
+            const unsigned ev_flags = L->timeline ? cudaEventDefault : cudaEventDisableTiming;
+            for (auto& e : L->ev_in) CUDA_TRY(cudaEventCreateWithFlags(&e, ev_flags));
+            for (auto& e : L->ev_done) CUDA_TRY(cudaEventCreateWithFlags(&e, ev_flags));
+            if (L->timeline) {
+                CUDA_TRY(cudaEventCreate(&L->ev_t0));
+                for (auto& e : L->ev_in0) CUDA_TRY(cudaEventCreate(&e));
+                for (auto& e : L->ev_out1) CUDA_TRY(cudaEventCreate(&e));
+            }
             if ((rc = dev_alloc(&L->chunk_acc, (size_t)nsum))) return rc;
             if ((rc = dev_alloc(&L->chunk_tmp, (size_t)nsum))) return rc;
             if ((rc = dev_alloc(&L->chunk_tpe_acc, (size_t)L->E))) return rc;
@@ -1113,9 +1129,11 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         const size_t xrow = (size_t)L->cfg.input_dim * dtype_size(x_dtype), orow = (size_t)L->cfg.output_dim * 4;
         CUDA_TRY(cudaMemsetAsync(L->chunk_acc, 0, sizeof(float) * nsum, s));
         CUDA_TRY(cudaMemsetAsync(L->chunk_tpe_acc, 0, sizeof(int64_t) * L->E, s));
+        if (L->timeline) CUDA_TRY(cudaEventRecord(L->ev_t0, L->s_in));
         for (int c = 0; c + 1 < (int)bounds.size(); ++c) {
             const int64_t t0 = bounds[c];
             const int64_t n = bounds[c + 1] - t0;
+            if (L->timeline) CUDA_TRY(cudaEventRecord(L->ev_in0[c], L->s_in));
             CUDA_TRY(cudaMemcpyAsync((char*)L->hx + t0 * xrow, (const char*)x + t0 * xrow, n * xrow,
                                      cudaMemcpyHostToDevice, L->s_in));
             CUDA_TRY(cudaEventRecord(L->ev_in[c], L->s_in));
@@ -1140,6 +1158,7 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
             if (d.gates) CUDA_TRY(cudaMemcpyAsync(opt->gates + t0 * ku, dc.gates, (size_t)n * ku * 4, cudaMemcpyDeviceToHost, L->s_out));
             if (d.probs) CUDA_TRY(cudaMemcpyAsync(opt->probs + t0 * ep, dc.probs, (size_t)n * ep * 4, cudaMemcpyDeviceToHost, L->s_out));
             if (d.logits) CUDA_TRY(cudaMemcpyAsync(opt->logits + t0 * er, dc.logits, (size_t)n * er * 4, cudaMemcpyDeviceToHost, L->s_out));
+            if (L->timeline) CUDA_TRY(cudaEventRecord(L->ev_out1[c], L->s_out));
         }
         if (launch_finish_loss(L->chunk_acc, L->E, L->E_probs, L->k_tot, L->cfg.balance_alpha, L->cfg.z_loss_weight,
                                training, d.loss, d.routing_entropy, s) < 0)
@@ -1151,6 +1170,17 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         if (d.routing_entropy) CUDA_TRY(cudaMemcpyAsync(opt->routing_entropy, d.routing_entropy, 4, cudaMemcpyDeviceToHost, s));
         CUDA_TRY(cudaStreamSynchronize(L->s_out));
         CUDA_TRY(cudaStreamSynchronize(s));
+        if (L->timeline) {
+            for (int c = 0; c + 1 < (int)bounds.size(); ++c) {
+                float a = 0, b = 0, dn = 0, o = 0;
+                cudaEventElapsedTime(&a, L->ev_t0, L->ev_in0[c]);
+                cudaEventElapsedTime(&b, L->ev_t0, L->ev_in[c]);
+                cudaEventElapsedTime(&dn, L->ev_t0, L->ev_done[c]);
+                cudaEventElapsedTime(&o, L->ev_t0, L->ev_out1[c]);
+                fprintf(stderr, "[moe_b200 timeline] chunk %d tokens %lld: copy-in %.3f..%.3f ms, compute done %.3f, copy-out done %.3f\n",
+                        c, (long long)(bounds[c + 1] - bounds[c]), a, b, dn, o);
+            }
+        }
         int32_t stc = 0;
         CUDA_TRY(cudaMemcpy(&stc, L->status, sizeof(stc), cudaMemcpyDeviceToHost));
         if (stc != DEV_OK) {

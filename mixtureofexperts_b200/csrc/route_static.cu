@@ -20,6 +20,7 @@ static __device__ __align__(256) unsigned char g_route_scratch[SCRATCH_BYTES];
 // address a kernel can use comes from cudaGetSymbolAddress, once per device.
 constexpr int MAX_DEVICES = 64;
 void* g_scratch_ptr[MAX_DEVICES] = {nullptr};
+int g_num_sms[MAX_DEVICES] = {0};
 
 thread_local char g_static_err[256] = "";
 
@@ -56,7 +57,7 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
     if (T < 1 || input_dim < 1) return fail(MOE_ERR_INVALID, "T and input_dim must be positive");
     if (!x || !router_w || !indices || !gates) return fail(MOE_ERR_INVALID, "x, router_w, indices and gates must not be null");
 
-    const int tpc = router_tokens_per_cta(num_experts);
+    const int tpc = ROUTER_TOKENS_PER_CTA;   // the largest tile: the fewest per-CTA rows of scratch
     const int64_t num_cta64 = (T + tpc - 1) / tpc;
     const size_t b_counts = align256((size_t)num_cta64 * num_experts * sizeof(int32_t));
     const size_t b_psum = align256((size_t)num_cta64 * (num_experts + 1) * sizeof(float));
@@ -84,6 +85,8 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
             return MOE_ERR_CUDA;
         }
         g_scratch_ptr[dev] = ptr;
+        if (cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_num_sms[dev] < 1)
+            g_num_sms[dev] = 1;
     }
     unsigned char* base = reinterpret_cast<unsigned char*>(g_scratch_ptr[dev]);
     int32_t* cta_counts = reinterpret_cast<int32_t*>(base);
@@ -135,7 +138,7 @@ int moe_route_static(int gate_kind, int num_experts, int num_shared, int top_k, 
     r.u_gate = gates;
     r.u_probs = probs;
     r.u_logits = nullptr;
-    if (launch_router(r, x_dtype, (int)num_cta64, s) < 0) {
+    if (launch_router(r, x_dtype, (int)num_cta64, g_num_sms[dev], s) < 0) {
         snprintf(g_static_err, sizeof(g_static_err), "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         return MOE_ERR_CUDA;
     }

@@ -269,37 +269,41 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-constexpr int RT_BT = ROUTER_TOKENS_PER_CTA;  // 64 tokens per CTA
-constexpr int RT_STAGES = 3;
 
 template <typename XT> struct XElt;
 template <> struct XElt<float> { static constexpr int PER16 = 4; };
 template <> struct XElt<__nv_bfloat16> { static constexpr int PER16 = 8; };
 
-// One pipeline stage: a [64 tokens][BK (+16 bytes pad)] tile of x in its own dtype and the
+// One pipeline stage: a [16*NI tokens][BK (+16 bytes pad)] tile of x in its own dtype and the
 // [BK][E_PAD] block of the K-major router matrix.
-template <int E_PAD, int BK, typename XT>
+template <int E_PAD, int BK, typename XT, int NI>
 struct RouterStage {
     static constexpr int ROW_ELTS = BK + XElt<XT>::PER16;   // padded row, stays 16-byte aligned
-    XT x[RT_BT][ROW_ELTS];
+    XT x[16 * NI][ROW_ELTS];
     float w[BK][E_PAD];
 };
 
-template <int E_PAD, int BK, int KS, typename XT>
+// ring depth: small token tiles keep more chunks in flight (the same bytes per CTA)
+template <int NI> struct RouterRing { static constexpr int STAGES = NI == 4 ? 3 : (NI == 2 ? 4 : 6); };
+
+template <int E_PAD, int BK, int KS, typename XT, int NI>
 union RouterSmem {
-    RouterStage<E_PAD, BK, XT> st[RT_STAGES];
-    float red[KS * RT_BT * E_PAD];  // [KS][64][E_PAD]
+    RouterStage<E_PAD, BK, XT, NI> st[RouterRing<NI>::STAGES];
+    float red[KS * 16 * NI * E_PAD];  // [KS][tokens][E_PAD]
 };
 
-// Gate GEMM as a register-tiled FP32 FMA kernel: a CTA owns 64 tokens x E_PAD router rows; a
-// thread owns 4 tokens x 8 rows and 1/KS of every K chunk (16 * E_PAD/8 * KS threads), so the
+// Gate GEMM as a register-tiled FP32 FMA kernel: a CTA owns 16*NI tokens x E_PAD router rows
+// (NI = 4, 2 or 1: small batches and narrow routers take small tiles, so that enough CTAs exist to
+// keep every SM's memory pipeline busy); a thread owns NI tokens x 8 rows and 1/KS of every K chunk (16 * E_PAD/8 * KS threads), so the
 // per-thread FP32 chain stays short; an inner accumulator is folded into an outer one every
 // ~256 products (two-level summation) and the KS partials are added in a fixed order.  x (in
 // its own dtype) and the K-major router matrix ([K][E_PAD], built once per set_router) stream
 // through a 3-stage cp.async ring; every token row contributes BK contiguous elements per chunk.
-template <int E_PAD, int BK, int KS, typename XT>
+template <int E_PAD, int BK, int KS, typename XT, int NI>
 __global__ void __launch_bounds__(16 * (E_PAD / 8) * KS, (16 * (E_PAD / 8) * KS <= 320 ? 2 : 1))
 router_kernel(const RouterParams p) {
+    constexpr int RT_BT = 16 * NI;
+    constexpr int RT_STAGES = RouterRing<NI>::STAGES;
     constexpr int EG = E_PAD / 8;
     constexpr int TG = 16;
     constexpr int NTHREADS = TG * EG * KS;
@@ -310,10 +314,10 @@ router_kernel(const RouterParams p) {
     constexpr int PER16 = XElt<XT>::PER16;
     constexpr int UPR = BK / PER16;                    // 16-byte units per token row per chunk
     constexpr int XUNITS = RT_BT * UPR;
-    using Stage = RouterStage<E_PAD, BK, XT>;
+    using Stage = RouterStage<E_PAD, BK, XT, NI>;
     static_assert(KPT >= 2 && KPT % 2 == 0, "tile configuration");
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    RouterSmem<E_PAD, BK, KS, XT>& sm = *reinterpret_cast<RouterSmem<E_PAD, BK, KS, XT>*>(smem_raw);
+    RouterSmem<E_PAD, BK, KS, XT, NI>& sm = *reinterpret_cast<RouterSmem<E_PAD, BK, KS, XT, NI>*>(smem_raw);
     __shared__ int s_cnt[MAX_EXPERTS];
     __shared__ float s_psum[NWARPS][MAX_EXPERTS];
     __shared__ float s_lse2[NWARPS];
@@ -359,9 +363,9 @@ router_kernel(const RouterParams p) {
         cp_async_commit();   // always commit, so that group counting stays uniform
     };
 
-    float acc[4][8], outer[4][8];
+    float acc[NI][8], outer[NI][8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < NI; ++i)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             acc[i][j] = 0.f;
@@ -378,9 +382,9 @@ router_kernel(const RouterParams p) {
 #pragma unroll
         for (int kk = 0; kk < KPT; kk += 2) {
             const int k = ks * KPT + kk;
-            float x0[4], x1[4];
+            float x0[NI], x1[NI];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 if constexpr (sizeof(XT) == 2) {
                     const uint32_t w2 = *reinterpret_cast<const uint32_t*>(&st.x[i * 16 + tg][k]);
                     x0[i] = __uint_as_float(w2 << 16);
@@ -396,7 +400,7 @@ router_kernel(const RouterParams p) {
             const float4 b0 = *reinterpret_cast<const float4*>(&st.w[k + 1][eg * 4]);
             const float4 b1 = *reinterpret_cast<const float4*>(&st.w[k + 1][E_PAD / 2 + eg * 4]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 acc[i][0] = fmaf(x0[i], a0.x, acc[i][0]);
                 acc[i][1] = fmaf(x0[i], a0.y, acc[i][1]);
                 acc[i][2] = fmaf(x0[i], a0.z, acc[i][2]);
@@ -417,7 +421,7 @@ router_kernel(const RouterParams p) {
         }
         if ((c % FOLD) == FOLD - 1) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < NI; ++i)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     outer[i][j] += acc[i][j];
@@ -429,7 +433,7 @@ router_kernel(const RouterParams p) {
     __syncthreads();   // the ring is dead from here on; its memory becomes the reduction buffer
     // partial sums of this thread's K slices -> shared [ks][token][row]
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < NI; ++i) {
         const int tok = i * 16 + tg;
         float* dst = &sm.red[((size_t)ks * RT_BT + tok) * E_PAD];
 #pragma unroll
@@ -537,10 +541,10 @@ __global__ void __launch_bounds__(ROUTER_THREADS) gates_only_kernel(GateCtx c, c
     gate_token<NJ>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
 }
 
-template <int E_PAD, int BK, int KS, typename XT>
-int launch_router_t(const RouterParams& p, int num_cta, cudaStream_t s) {
-    auto kern = router_kernel<E_PAD, BK, KS, XT>;
-    const size_t smem = sizeof(RouterSmem<E_PAD, BK, KS, XT>);
+template <int E_PAD, int BK, int KS, typename XT, int NI>
+int launch_router_n(const RouterParams& p, int num_cta, cudaStream_t s) {
+    auto kern = router_kernel<E_PAD, BK, KS, XT, NI>;
+    const size_t smem = sizeof(RouterSmem<E_PAD, BK, KS, XT, NI>);
     static bool attr_done = false;   // per instantiation
     if (!attr_done) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
@@ -548,6 +552,16 @@ int launch_router_t(const RouterParams& p, int num_cta, cudaStream_t s) {
     }
     kern<<<num_cta, 16 * (E_PAD / 8) * KS, smem, s>>>(p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
+}
+
+template <int E_PAD, int BK, int KS, typename XT>
+int launch_router_t(const RouterParams& p, int num_cta, cudaStream_t s) {
+    switch (p.tokens_per_cta) {
+        case 64: return launch_router_n<E_PAD, BK, KS, XT, 4>(p, num_cta, s);
+        case 32: return launch_router_n<E_PAD, BK, KS, XT, 2>(p, num_cta, s);
+        case 16: return launch_router_n<E_PAD, BK, KS, XT, 1>(p, num_cta, s);
+        default: return -1;
+    }
 }
 
 template <int E_PAD, int BK, int KS>
@@ -558,7 +572,13 @@ int launch_router_e(const RouterParams& p, int x_dtype, int num_cta, cudaStream_
 
 }  // namespace
 
-int router_tokens_per_cta(int) { return ROUTER_TOKENS_PER_CTA; }
+// Token tile of the router and permute kernels for a batch of T tokens: the largest of 64/32/16
+// that still gives every SM a CTA, so that small batches do not leave SMs idle.
+int router_tokens_per_cta(int64_t T, int num_sms) {
+    for (int bt = ROUTER_TOKENS_PER_CTA; bt > 16; bt >>= 1)
+        if ((T + bt - 1) / bt >= (int64_t)num_sms) return bt;
+    return 16;
+}
 
 // Router rows are padded to one of these widths (multiples of 8 = the per-thread row tile).
 int router_e_pad(int e_router) {
@@ -586,7 +606,7 @@ int launch_router_transpose_noise(const float* w, const float* nw, float* wt, in
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
-int launch_router(const RouterParams& p, int x_dtype, int num_cta, cudaStream_t s) {
+int launch_router(const RouterParams& p, int x_dtype, int num_cta, int num_sms, cudaStream_t s) {
     // <E_PAD, BK, KS>: 16 * E_PAD/8 * KS threads; with a noise network the GEMM is 2*E_router wide
     switch (router_e_pad(p.noise_off > 0 ? 2 * p.E_router : p.E_router)) {
         case 8: return launch_router_e<8, 128, 16>(p, x_dtype, num_cta, s);
