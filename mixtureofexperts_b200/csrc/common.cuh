@@ -90,6 +90,7 @@ struct ScanParams {
     float* u_entropy;
     // expert-parallel: when non-null the loss is finished later from all ranks' sums
     float* ep_sums;           // [E + E_probs + 3]: counts, prob sums, sum lse^2, T, entropy sum
+    int sums_accumulate;      // 1: add into ep_sums / u_tokens_per_expert (chunks of one batch) instead of storing
 };
 
 struct PermuteParams {
@@ -174,7 +175,6 @@ int launch_scan(const ScanParams& p, cudaStream_t s);
 // AuxiliaryFreeLoss.update_bias! on the device: bias/momentum [E] updated in place from expert_count [E]
 int launch_aux_free_update(const int32_t* expert_count, int E, float* bias, float* bias_momentum, float learning_rate,
                            float momentum, cudaStream_t s);
-int launch_accumulate(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E, cudaStream_t s);
 int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s);
 int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s);
 int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, int64_t rows, int num_sms,

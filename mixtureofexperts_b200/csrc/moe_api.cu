@@ -124,9 +124,7 @@ struct moe_layer {
     bool timeline = false;
     cudaEvent_t ev_t0 = nullptr, ev_in0[MAX_CHUNKS] = {}, ev_out1[MAX_CHUNKS] = {};
     float* chunk_acc = nullptr;      // [E + E_probs + 3] summed statistics of the chunks
-    float* chunk_tmp = nullptr;
     int64_t* chunk_tpe_acc = nullptr;  // [E]
-    int64_t* chunk_tpe_tmp = nullptr;
 
     // profiling: a ring of event sets, one set per forward call
     int prof_slots = 0;
@@ -446,6 +444,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     sp.u_tokens_per_expert = opt->tokens_per_expert;
     sp.u_entropy = (L->ep || partial_sums) ? nullptr : opt->routing_entropy;
     sp.ep_sums = L->ep ? ep_sums_buffer(L->ep) : partial_sums;
+    sp.sums_accumulate = (!L->ep && partial_sums) ? 1 : 0;
     n = launch_scan(sp, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "scan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
@@ -671,9 +670,7 @@ int moe_layer_destroy(moe_layer_t* L) {
     for (auto& e : L->ev_done)
         if (e) cudaEventDestroy(e);
     dev_free(L->chunk_acc);
-    dev_free(L->chunk_tmp);
     dev_free(L->chunk_tpe_acc);
-    dev_free(L->chunk_tpe_tmp);
     delete L;
     return MOE_OK;
 }
@@ -989,8 +986,7 @@ int moe_layer_set_router_noise_network(moe_layer_t* L, const float* noise_w, int
     CUDA_TRY(cudaSetDevice(L->device));
     if (!noise_w) {   // back to plain Gaussian noise
         CUDA_TRY(cudaStreamSynchronize(L->stream));
-        dev_free(L->bias_momentum);
-    dev_free(L->router_nw);
+        dev_free(L->router_nw);
         dev_free(L->router_wt_noise);
         L->router_nw = L->router_wt_noise = nullptr;
         return MOE_OK;
@@ -1104,9 +1100,7 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
                 for (auto& e : L->ev_out1) CUDA_TRY(cudaEventCreate(&e));
             }
             if ((rc = dev_alloc(&L->chunk_acc, (size_t)nsum))) return rc;
-            if ((rc = dev_alloc(&L->chunk_tmp, (size_t)nsum))) return rc;
             if ((rc = dev_alloc(&L->chunk_tpe_acc, (size_t)L->E))) return rc;
-            if ((rc = dev_alloc(&L->chunk_tpe_tmp, (size_t)L->E))) return rc;
         }
         // Chunk boundaries (multiples of 64 tokens).  By default small first and last chunks: only the
         // copy-in of the first and the copy-out of the last chunk are not hidden behind compute.
@@ -1143,13 +1137,10 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
             if (d.gates) dc.gates = d.gates + t0 * ku;
             if (d.probs) dc.probs = d.probs + t0 * ep;
             if (d.logits) dc.logits = d.logits + t0 * er;
-            dc.tokens_per_expert = L->chunk_tpe_tmp;
+            dc.tokens_per_expert = L->chunk_tpe_acc;       // the scan kernel adds every chunk's sums in place
             if ((rc = forward_device(L, (char*)L->hx + t0 * xrow, x_dtype, n, training, L->hout + t0 * L->cfg.output_dim,
-                                     &dc, s, L->chunk_tmp, d.routing_entropy != nullptr)))
+                                     &dc, s, L->chunk_acc, d.routing_entropy != nullptr)))
                 return rc;
-            if (launch_accumulate(L->chunk_acc, L->chunk_tmp, nsum, L->chunk_tpe_acc, L->chunk_tpe_tmp, L->E, s) < 0)
-                return fail(MOE_ERR_CUDA, "accumulate launch failed");
-            L->launches += 1;
             CUDA_TRY(cudaEventRecord(L->ev_done[c], s));
             CUDA_TRY(cudaStreamWaitEvent(L->s_out, L->ev_done[c], 0));
             CUDA_TRY(cudaMemcpyAsync((char*)out + t0 * orow, (char*)L->hout + t0 * orow, n * orow, cudaMemcpyDeviceToHost,

@@ -33,12 +33,21 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_loss_kernel(const ScanParam
     // (i) per expert: exclusive prefix of the per-CTA counts, in CTA (= token) order
     for (int e = warp; e < p.E; e += NW) {
         int run = 0;
-        for (int c0 = 0; c0 < p.num_cta; c0 += 32) {
-            const int c = c0 + lane;
-            const int v = (c < p.num_cta) ? p.cta_counts[(size_t)c * p.E + e] : 0;
-            const int inc = warp_incl_scan(v, lane);
-            if (c < p.num_cta) p.cta_counts[(size_t)c * p.E + e] = run + inc - v;
-            run += __shfl_sync(0xffffffffu, inc, 31);
+        // eight independent loads in flight per lane, then the scans (the loads dominate: L2 latency)
+        for (int c0 = 0; c0 < p.num_cta; c0 += 256) {
+            int v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = c0 + j * 32 + lane;
+                v[j] = (c < p.num_cta) ? p.cta_counts[(size_t)c * p.E + e] : 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = c0 + j * 32 + lane;
+                const int inc = warp_incl_scan(v[j], lane);
+                if (c < p.num_cta) p.cta_counts[(size_t)c * p.E + e] = run + inc - v[j];
+                run += __shfl_sync(0xffffffffu, inc, 31);
+            }
         }
         // with a capacity constraint an expert keeps its first `capacity` pairs (token order)
         if (lane == 0) s_count[e] = (p.capacity >= 0 && run > p.capacity) ? p.capacity : run;
@@ -74,14 +83,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_loss_kernel(const ScanParam
         p.expert_offset[p.E] = off;
         p.tile_prefix[p.E] = tiles;
     }
+    // sums_accumulate: this call is one chunk of a batch; chunks run in order on one stream, so the
+    // running sums have a fixed order of additions
+    const bool add = p.sums_accumulate != 0;
     for (int e = threadIdx.x; e < p.E; e += SCAN_THREADS)
-        if (p.u_tokens_per_expert) p.u_tokens_per_expert[e] = (int64_t)s_count[e];
+        if (p.u_tokens_per_expert) p.u_tokens_per_expert[e] = (add ? p.u_tokens_per_expert[e] : 0) + (int64_t)s_count[e];
     if (p.ep_sums) {
-        for (int e = threadIdx.x; e < p.E; e += SCAN_THREADS) p.ep_sums[e] = (float)s_count[e];
-        for (int e = threadIdx.x; e <= p.E_probs; e += SCAN_THREADS) p.ep_sums[p.E + e] = s_psum[e];
+        for (int e = threadIdx.x; e < p.E; e += SCAN_THREADS) p.ep_sums[e] = (add ? p.ep_sums[e] : 0.f) + (float)s_count[e];
+        for (int e = threadIdx.x; e <= p.E_probs; e += SCAN_THREADS)
+            p.ep_sums[p.E + e] = (add ? p.ep_sums[p.E + e] : 0.f) + s_psum[e];
         if (threadIdx.x == 0) {
-            p.ep_sums[p.E + p.E_probs + 1] = (float)p.T;
-            p.ep_sums[p.E + p.E_probs + 2] = (float)s_ent;
+            const int a = p.E + p.E_probs + 1;
+            p.ep_sums[a] = (add ? p.ep_sums[a] : 0.f) + (float)p.T;
+            p.ep_sums[a + 1] = (add ? p.ep_sums[a + 1] : 0.f) + (float)s_ent;
         }
     }
 
@@ -176,13 +190,6 @@ __global__ void __launch_bounds__(SCAN_THREADS) loss_only_kernel(float alpha, fl
     }
 }
 
-// acc += tmp for the per-chunk loss sums and expert counts of a chunked host forward
-__global__ void accumulate_kernel(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) acc[i] += tmp[i];
-    if (tacc && i < E) tacc[i] += ttmp[i];
-}
-
 // update_bias! (src/balancing/auxiliary_free.jl:36-71) from this call's per-expert counts.  One
 // block; thread e owns expert e.  Arithmetic types follow Julia's promotion: the gradient and the
 // momentum blend are Float64 (Int/Int target), rounded into the Float32 vectors; the bias step and
@@ -227,12 +234,6 @@ __global__ void aux_free_update_kernel(const int32_t* expert_count, int E, float
 int launch_aux_free_update(const int32_t* expert_count, int E, float* bias, float* bias_momentum, float learning_rate,
                            float momentum, cudaStream_t s) {
     aux_free_update_kernel<<<1, MAX_EXPERTS, 0, s>>>(expert_count, E, bias, bias_momentum, learning_rate, momentum);
-    return cudaGetLastError() == cudaSuccess ? 1 : -1;
-}
-
-int launch_accumulate(float* acc, const float* tmp, int n, int64_t* tacc, const int64_t* ttmp, int E, cudaStream_t s) {
-    const int m = n > E ? n : E;
-    accumulate_kernel<<<(m + 255) / 256, 256, 0, s>>>(acc, tmp, n, tacc, ttmp, E);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 

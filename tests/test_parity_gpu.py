@@ -411,6 +411,22 @@ def test_chunked_host_call_equals_device_call(gate_kind, E, S, k):
     assert np.array_equal(st_h["tokens_per_expert"], 2 * counts_d)
     assert abs(st_h["routing_entropy"][-1] - ent_d) < 1e-6
     assert layer.device_status() == 0
+    # repeated calls: same results, same number of kernels counted per call
+    n0 = layer.launch_count()
+    per_call = None
+    for rep in range(3):
+        out_r, loss_r, rt_r = layer(np.asfortranarray(x.T), training=True, return_routing=True)
+        assert np.array_equal(out_r, out_h) and float(loss_r) == float(loss_h), rep
+        assert np.array_equal(rt_r["indices"], rt_h["indices"]) and np.array_equal(rt_r["gates"], rt_h["gates"])
+        n1 = layer.launch_count()
+        assert per_call in (None, n1 - n0), (rep, per_call, n1 - n0)
+        per_call, n0 = n1 - n0, n1
+    # other arguments (no routing outputs, inference) and new input values on the same handle
+    x2 = np.asfortranarray((x * 0.5).T)
+    want2 = layer(torch.from_numpy(np.ascontiguousarray(x2.T)).cuda().t(), training=False)[0].cpu().numpy()
+    for rep in range(3):
+        assert np.array_equal(layer(x2, training=False)[0], want2), rep
+    assert layer.device_status() == 0
     layer.close()
 
 
