@@ -19,7 +19,7 @@ _EXPORTS = {
     "create_moe_layer": "layer", "load_balance_score": "layer", "reset_stats": "layer",
     "AuxiliaryFreeLoss": "losses", "LoadBalancingLoss": "losses", "SwitchTransformerLoss": "losses",
     "ZLoss": "losses", "compute_loss": "losses",
-    "convert_to_moe": "llama2", "sample_moe": "llama2", "save_moe_model": "llama2", "load_moe_model": "llama2", "moe_transformer": "llama2", "MoERunState": "llama2",
+    "convert_to_moe": "llama2", "sample_moe": "llama2", "save_moe_model": "llama2", "usage_balance_score": "llama2", "expert_stats_lines": "llama2", "load_moe_model": "llama2", "moe_transformer": "llama2", "MoERunState": "llama2",
     "MoELanguageModel": "llama2", "MoEExpertWeights": "llama2", "LanguageModel": "llama2", "ModelConfig": "llama2",
     "random_language_model": "llama2", "count_parameters": "llama2", "count_active_parameters": "llama2",
 }

@@ -545,10 +545,13 @@ template <int E_PAD, int BK, int KS, typename XT, int NI>
 int launch_router_n(const RouterParams& p, int num_cta, cudaStream_t s) {
     auto kern = router_kernel<E_PAD, BK, KS, XT, NI>;
     const size_t smem = sizeof(RouterSmem<E_PAD, BK, KS, XT, NI>);
-    static bool attr_done = false;   // per instantiation
-    if (!attr_done) {
+    // the attribute belongs to a (kernel, device) pair: one flag per instantiation and device
+    static bool attr_done[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (!attr_done[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
-        attr_done = true;
+        attr_done[dev] = true;
     }
     kern<<<num_cta, 16 * (E_PAD / 8) * KS, smem, s>>>(p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;

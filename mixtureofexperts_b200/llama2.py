@@ -257,30 +257,61 @@ def convert_to_moe(model: LanguageModel, moe_layers: Sequence[int], *, num_exper
 
 
 def count_parameters(model: MoELanguageModel) -> int:
-    """count_parameters (src/llama2/utils.jl): every weight, all experts included."""
+    """count_parameters (src/llama2/conversion.jl:512-550): every weight, all experts included.  Like
+    the reference, a MoE layer contributes its attention weights, router and experts but not its
+    rms_ffn_weight (the reference's own run of stories42M with layers [2,4] x 4 experts prints
+    70757888, which only comes out this way)."""
     n = model.token_embedding_table.size + model.rms_final_weight.size + model.output_weight.size
+    c = model.config
+    per = 3 * c.dim * c.hidden_dim
     for l in model.layers:
         ll = l.llama_layer
-        n += sum(a.size for a in (ll.rms_att_weight, ll.rms_ffn_weight, ll.wq, ll.wk, ll.wv, ll.wo))
-        if l.use_moe and l.moe_experts is None:      # loaded from a weight image: count from the shapes
-            mc = l.moe_config
-            n += mc.num_experts * (mc.input_dim + mc.hidden_dim * (2 * mc.input_dim + mc.output_dim))
-        elif l.use_moe:
-            n += l.moe_router_weight.size + sum(e.w1.size + e.w2.size + e.w3.size for e in l.moe_experts)
+        n += sum(a.size for a in (ll.rms_att_weight, ll.wq, ll.wk, ll.wv, ll.wo))
+        if l.use_moe:
+            n += c.moe_num_experts * c.dim + c.moe_num_experts * per
         else:
-            n += ll.w1.size + ll.w2.size + ll.w3.size
+            n += ll.rms_ffn_weight.size + ll.w1.size + ll.w2.size + ll.w3.size
     return int(n)
 
 
 def count_active_parameters(model: MoELanguageModel) -> int:
-    """Parameters touched per token: top_k of the experts in a MoE layer."""
+    """count_active_parameters (src/llama2/conversion.jl:557-600): top_k of the experts of a MoE layer."""
     n = model.token_embedding_table.size + model.rms_final_weight.size + model.output_weight.size
+    c = model.config
+    per = 3 * c.dim * c.hidden_dim
     for l in model.layers:
         ll = l.llama_layer
-        n += sum(a.size for a in (ll.rms_att_weight, ll.rms_ffn_weight, ll.wq, ll.wk, ll.wv, ll.wo))
-        per = 3 * model.config.dim * model.config.hidden_dim
-        n += (model.config.moe_num_experts * model.config.dim + model.config.moe_top_k * per) if l.use_moe else per
+        n += sum(a.size for a in (ll.rms_att_weight, ll.wq, ll.wk, ll.wv, ll.wo))
+        if l.use_moe:
+            n += c.moe_num_experts * c.dim + c.moe_top_k * per
+        else:
+            n += ll.rms_ffn_weight.size + ll.w1.size + ll.w2.size + ll.w3.size
     return int(n)
+
+
+def usage_balance_score(usage_counts, num_experts: int) -> float:
+    """The score print_expert_stats prints per MoE layer (src/llama2/generation.jl:318-324):
+    1 - max|count - total/num_experts| / (total/num_experts)."""
+    counts = np.asarray(usage_counts, dtype=np.float64)
+    expected = counts.sum() / num_experts
+    return float(1.0 - np.abs(counts - expected).max() / expected)
+
+
+def expert_stats_lines(state: "MoERunState", model: MoELanguageModel, threshold: float = 0.0) -> List[str]:
+    """The text of print_expert_stats (src/llama2/generation.jl:298-330) for the calls made with
+    ``state`` so far, one list entry per line."""
+    lines = ["", "--- Expert Usage Statistics ---"]
+    for layer_idx in sorted(state.expert_usage):
+        counts = state.expert_usage[layer_idx]
+        total = int(counts.sum())
+        lines += [f"Layer {layer_idx}:", f"  Total expert activations: {total}"]
+        for e, cnt in enumerate(counts, start=1):
+            if cnt > 0 and cnt / total * 100 >= threshold * 100:
+                lines.append(f"    Expert {e:2d}: {int(cnt):4d} activations ({cnt / total * 100:.1f}%)")
+        if total > 0:
+            lines.append(f"  Load balance score: {usage_balance_score(counts, model.config.moe_num_experts):.3f} (1.0 = perfect)")
+        lines.append("")
+    return lines
 
 
 # ---- inference (src/llama2/inference.jl, attention.jl) ---------------------------------------
@@ -352,6 +383,7 @@ class MoERunState:
         self.logits = None
         self.expert_load_counts = np.zeros(c.moe_num_experts, dtype=np.int64)
         self.selected_experts = {}          # layer index -> (T, k) 1-based ids of the last call
+        self.expert_usage = {}              # 1-based layer number -> activations per expert (stats[:expert_usage])
         self.inference_stats = {"total_tokens": 0, "moe_layer_calls": 0, "expert_activations": 0}
 
 
@@ -394,6 +426,8 @@ def moe_transformer(tokens: Sequence[int], model: MoELanguageModel, state: MoERu
             idx = np.ascontiguousarray(routing["indices"].T)
             state.selected_experts[li] = idx
             np.add.at(state.expert_load_counts, idx.ravel() - 1, 1)
+            usage = state.expert_usage.setdefault(li + 1, np.zeros(c.moe_num_experts, dtype=np.int64))
+            np.add.at(usage, idx.ravel() - 1, 1)
             state.inference_stats["moe_layer_calls"] += m
             state.inference_stats["expert_activations"] += idx.size
         else:

@@ -30,6 +30,15 @@ CASES = {
     # Switch (top-1) gating with gelu
     "switch_gelu": dict(seed=79, T=33, D=48, H=80, O=48, E=4, gate=("switch", 1), z=0.0, init="normal",
                         activation="gelu"),
+    # StandardExpert (bias + gelu), the MoEConfig default expert type
+    "standard_gelu": dict(seed=80, T=37, D=48, H=72, O=40, E=6, gate=("topk", 2), z=0.001, init="normal",
+                          activation="gelu", expert_kind="standard"),
+    # drop_tokens with capacity_factor 1.0: late pairs of popular experts are dropped, gates renormalised
+    "capacity": dict(seed=81, T=90, D=32, H=48, O=32, E=4, gate=("topk", 2), z=0.001, init="normal",
+                     drop_tokens=True, capacity_factor=1.0),
+    # training-time router noise through the noise network: logits + 0.5 * (randn .* softplus(noise_weight x))
+    "noise_net": dict(seed=82, T=50, D=40, H=48, O=32, E=8, gate=("topk", 2), z=0.001, init="normal",
+                      noise_scale=0.5, noise_net=True),
 }
 
 
@@ -38,7 +47,14 @@ def build(case):
     E = c["E"]
     nsh = c.get("num_shared_experts", 0)
     x, w = orc.make_layer_inputs(c["seed"], c["T"], c["D"], c["H"], c["O"], E, e_router=E - nsh,
-                                 init=c["init"], std=0.3 if c["init"] == "normal" else 0.02)
+                                 init=c["init"], std=0.3 if c["init"] == "normal" else 0.02,
+                                 expert_kind=c.get("expert_kind", "gated"))
+    noise = None
+    if c.get("noise_scale", 0) > 0:
+        rng = np.random.Generator(np.random.PCG64(c["seed"] + 1000))
+        noise = rng.standard_normal((c["T"], E - nsh), dtype=np.float32)
+        if c.get("noise_net"):
+            w.noise_weight = rng.standard_normal((E - nsh, c["D"]), dtype=np.float32) * np.float32(0.3)
     g = c["gate"]
     if g[0] == "topk":
         gate = orc.TopKGating(g[1])
@@ -48,7 +64,9 @@ def build(case):
         gate = orc.SharedExpertGating(g[2], orc.TopKGating(g[1]), E)
     cfg = orc.MoEConfig(num_experts=E, input_dim=c["D"], hidden_dim=c["H"], output_dim=c["O"],
                         activation=c.get("activation", "silu"), gate_type=gate, balance_alpha=0.01,
-                        z_loss_weight=c["z"], num_shared_experts=nsh)
+                        z_loss_weight=c["z"], num_shared_experts=nsh, drop_tokens=c.get("drop_tokens", False),
+                        capacity_factor=c.get("capacity_factor", 1.25), noise_scale=c.get("noise_scale", 0.0),
+                        router_noise=noise)
     return c, cfg, x, w
 
 

@@ -90,3 +90,42 @@ def test_product_package_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.lower() or f == "ep.h" or "the oracle for this path" in text.lower(), f
+
+
+def test_header_compiles_as_c_and_a_c_caller_links(lib_built, tmp_path):
+    """The boundary is a C ABI: the header must be plain C99, and a C program linked against the
+    library must be able to call it (host-only calls here: version, a rejected config, error text)."""
+    import shutil
+    import subprocess
+
+    from mixtureofexperts_b200 import _lib
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("gcc not available")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    inc = os.path.join(root, "include")
+    src = tmp_path / "caller.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <string.h>
+#include "moe_b200.h"
+int main(void) {
+    moe_config_t cfg;
+    moe_layer_t* h = 0;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.num_experts = 4; cfg.top_k = 9;            /* top_k > num_experts: refused on the host */
+    cfg.input_dim = 8; cfg.hidden_dim = 8; cfg.output_dim = 8;
+    int rc = moe_layer_create(&cfg, 0, &h);
+    printf("%s|%d|%d|%s\n", moe_version(), (int)sizeof(moe_config_t), rc, moe_last_error());
+    return (rc == MOE_ERR_INVALID && h == 0) ? 0 : 1;
+}
+''')
+    exe = tmp_path / "caller"
+    lib_dir = os.path.dirname(_lib.LIB_PATH)
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", inc, str(src), "-o", str(exe),
+                    "-L", lib_dir, "-lmoe_b200", f"-Wl,-rpath,{lib_dir}"], check=True, capture_output=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    version, size, rc, msg = r.stdout.strip().split("|", 3)
+    assert version == _lib.version() and int(size) == C.sizeof(_lib.MoeConfig) and "top_k" in msg

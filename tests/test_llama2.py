@@ -262,3 +262,51 @@ def test_weight_image_carries_standard_experts_bias_and_noise_network():
     assert np.array_equal(dst.export_weights(), img)
     src.close()
     dst.close()
+
+
+def test_known_answers_of_the_reference_log(lib_built):
+    """Numbers the reference itself printed when it converted and ran stories42M (dim 512, hidden
+    1376, 8 layers, vocab 32000; MoE at layers [2, 4], 4 gated experts, top-2), recorded in its
+    test_moe_output.txt: parameter counts (lines 39-40, 90-93) and the expert-usage report
+    (lines 70-78).  They depend on shapes and counts only, so they pin the host logic exactly."""
+    import mixtureofexperts_b200 as m
+
+    cfg = m.ModelConfig(dim=512, hidden_dim=1376, n_layers=8, n_heads=8, n_kv_heads=8, vocab_size=32000, seq_len=1024)
+    lm = m.random_language_model(cfg, seed=0)
+    original = sum(a.size for l in lm.weights.layers for a in l.__dict__.values()) + \
+        lm.weights.token_embedding_table.size + lm.weights.rms_final_weight.size + lm.weights.output_weight.size
+    assert original == 58073600
+    mm = m.convert_to_moe(lm, [2, 4], num_experts=4, top_k=2, expert_init_strategy="perturb", seed=1)
+    assert m.count_parameters(mm) == 70757888
+    assert m.count_active_parameters(mm) == 62303744
+    assert f"{m.count_active_parameters(mm) / m.count_parameters(mm) * 100:.1f}%" == "88.1%"
+
+    st = m.MoERunState.__new__(m.MoERunState)
+    st.expert_usage = {2: np.array([334, 616, 469, 629]), 4: np.array([334, 616, 469, 629])}
+    assert f"{m.usage_balance_score(st.expert_usage[2], 4):.3f}" == "0.652"
+    lines = m.expert_stats_lines(st, mm)
+    want = ["Layer 2:", "  Total expert activations: 2048", "    Expert  1:  334 activations (16.3%)",
+            "    Expert  2:  616 activations (30.1%)", "    Expert  3:  469 activations (22.9%)",
+            "    Expert  4:  629 activations (30.7%)", "  Load balance score: 0.652 (1.0 = perfect)"]
+    at = lines.index("Layer 2:")
+    assert lines[at:at + len(want)] == want
+    assert "Layer 4:" in lines
+
+
+@pytest.mark.parametrize("neox", [False, True])
+def test_rope_properties_of_the_reference_script(lib_built, neox):
+    """test_moeLlama2_integration.jl:255-270: RoPE at position 1 is the identity, changes the input at
+    later positions, and differs between positions; norms of the rotated pairs are kept."""
+    import mixtureofexperts_b200 as m
+    from mixtureofexperts_b200 import llama2
+
+    cfg = m.ModelConfig(dim=64, hidden_dim=96, n_layers=1, n_heads=4, n_kv_heads=4, vocab_size=300, seq_len=16,
+                        rope_is_neox=neox)
+    v = np.random.default_rng(0).standard_normal((1, 64)).astype(np.float32)
+    at = lambda pos: llama2._rope_rows(v, pos - 1, 4, cfg)          # 1-based position like the reference
+    assert np.allclose(at(1), v, atol=1e-5)
+    assert not np.allclose(at(5), v, atol=1e-6)
+    assert not np.allclose(at(5), at(10), atol=1e-6)
+    assert abs(float(np.linalg.norm(at(7))) - float(np.linalg.norm(v))) < 1e-4
+    both = llama2._rope_rows(np.repeat(v, 3, axis=0), 4, 4, cfg)     # rows at consecutive positions 5, 6, 7
+    assert np.allclose(both[0], at(5)[0], atol=1e-6) and np.allclose(both[2], at(7)[0], atol=1e-6)

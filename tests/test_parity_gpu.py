@@ -84,10 +84,16 @@ def test_golden_fixture(case, host):
     S = g[2] if g[0] == "shared" else 0
     k = 1 if g[0] == "switch" else g[1]
     nsh = c.get("num_shared_experts", 0)
+    extra = {key: c[key] for key in ("drop_tokens", "capacity_factor", "noise_scale") if key in c}
     layer = make_device_layer(w, D=c["D"], H=c["H"], O=c["O"], gate=device_gate(g[0], k, S, c["E"]),
-                              activation=c.get("activation", "silu"), z=c["z"], num_shared_experts=nsh)
+                              activation=c.get("activation", "silu"), z=c["z"], num_shared_experts=nsh, **extra)
+    if cfg.noise_scale > 0:
+        layer.router.noise_scale = cfg.noise_scale
+        layer.router.noise_weight = w.noise_weight
+        layer.sync_router()
     xin = np.asfortranarray(x.T) if host else torch.from_numpy(x).cuda().t()
-    out, loss, routing = layer(xin, training=True, return_routing=True)
+    out, loss, routing = layer(xin, training=True, return_routing=True,
+                               router_noise=None if cfg.router_noise is None else cfg.router_noise.T)
     if not host:
         out, loss = out.cpu().numpy(), float(loss.item())
         routing = {k_: v.cpu().numpy() for k_, v in routing.items()}
