@@ -85,10 +85,14 @@ class ClockSampler:
 
     def _run(self):
         nv = self.nv
+        try:
+            mx = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)    # constant: asked once
+        except Exception as exc:  # noqa: BLE001
+            self.err = str(exc)
+            return
         while not self.stop_flag.is_set():
             try:
                 sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
-                mx = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)
                 pw = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
                 rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
                     nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)

@@ -73,7 +73,22 @@ __device__ __forceinline__ void copy_row<__nv_bfloat16, __nv_bfloat16>(const __n
 }
 template <>
 __device__ __forceinline__ void copy_row<float, __nv_bfloat16>(const float* s, __nv_bfloat16* const* d, int n,
-                                                               int D, int lane, bool) {
+                                                               int D, int lane, bool vec) {
+    if (vec) {
+        // 8 columns per lane: two 16-byte loads, round to nearest even, one 16-byte store per destination
+        for (int c = lane * 8; c < D; c += 32 * 8) {
+            const float4 a = *reinterpret_cast<const float4*>(s + c), b = *reinterpret_cast<const float4*>(s + c + 4);
+            const __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w),
+                                 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+            uint4 v;
+            v.x = *reinterpret_cast<const uint32_t*>(&p0);
+            v.y = *reinterpret_cast<const uint32_t*>(&p1);
+            v.z = *reinterpret_cast<const uint32_t*>(&p2);
+            v.w = *reinterpret_cast<const uint32_t*>(&p3);
+            for (int j = 0; j < n; ++j) st16(d[j] + c, v);
+        }
+        return;
+    }
     for (int c = lane; c < D; c += 32) {
         const __nv_bfloat16 v = __float2bfloat16_rn(s[c]);
         for (int j = 0; j < n; ++j) d[j][c] = v;
@@ -232,7 +247,41 @@ __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombinePara
     float* out = p.out + (size_t)t * p.O;
     const bool vec = (p.O % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-    if (vec) {
+    bool done = false;
+    if constexpr (sizeof(YT) == 2) {
+        // BF16 rows: 16-byte loads (8 columns per thread), four rows in flight; the sum over a
+        // token's experts keeps the ascending-expert order of the narrow path below
+        if (vec && p.O % 8 == 0) {
+            for (int c = threadIdx.x * 8; c < p.O; c += COMB_THREADS * 8) {
+                float acc[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                for (int j0 = 0; j0 < n; j0 += 4) {
+                    uint4 q[4];
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj)
+                        if (j0 + jj < n) q[jj] = *reinterpret_cast<const uint4*>(s_ptr[j0 + jj] + c);
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        if (j0 + jj < n) {
+                            const float g = s_gate[j0 + jj];
+                            const uint32_t u[4] = {q[jj].x, q[jj].y, q[jj].z, q[jj].w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                acc[2 * i] += g * __uint_as_float(u[i] << 16);
+                                acc[2 * i + 1] += g * __uint_as_float(u[i] & 0xffff0000u);
+                            }
+                        }
+                    }
+                }
+                *reinterpret_cast<float4*>(out + c) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(out + c + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+            done = true;
+        }
+    }
+    if (done) {
+    } else if (vec) {
         for (int c = threadIdx.x * 4; c < p.O; c += COMB_THREADS * 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int j = 0; j < n; ++j) {
