@@ -364,7 +364,8 @@ def main():
         if w["dtype"] == "bf16" and stages.get("gemm1", 0) > 0 and world == 1:
             ach = f_g1 / (stages["gemm1"] * 1e-3) / 1e12
             peak = peaks["bf16_tflops_sustained"]
-            roof = {"bound": "tensor", "kernel": "group_gemm_tc_kernel<1> (x W1^T, x W3^T, act*up)",
+            gemm_kernel = "group_gemm_tc2_kernel<1>, CTA pairs" if layer.tile_rows(T) == 256 else "group_gemm_tc_kernel<1>"
+            roof = {"bound": "tensor", "kernel": gemm_kernel + " (x W1^T, x W3^T, act*up)",
                     "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                     "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (kernel timed inside a long step); burst {peaks['bf16_tflops']}",
                     "traffic": traffic, "traffic_unit": "bytes per launch",

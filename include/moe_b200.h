@@ -224,6 +224,11 @@ int moe_compute_loss(float alpha, float z_weight, int n_probs, int k, int index_
 int moe_layer_set_profiling(moe_layer_t*, int slots);
 int moe_layer_stage_ms(moe_layer_t*, int calls_back, float ms[7]);
 
+/* Rows per m-tile of the expert GEMMs a forward of T local tokens takes on one GPU: 256 = CTA-pair
+ * tensor-core kernel, 128 = single-CTA tensor-core kernel, 16 = FP32 kernels (no counterpart in the
+ * reference: a profiling aid).  Negative = error. */
+int moe_layer_tile_rows(moe_layer_t*, int64_t T);
+
 /* Number of kernel launches of this library issued through the handle since creation. */
 int64_t moe_layer_launch_count(const moe_layer_t*);
 

@@ -272,20 +272,29 @@ int check_ready(moe_layer* L) {
     return MOE_OK;
 }
 
-// The grouped GEMM pair on `rows_cap` rows described by (expert_offset, tile_prefix).
-// CTA-pair tiles (256 rows, cta_group::2) need fewer cycles than single-CTA tiles but, measured over
-// seconds at the board's power limit, run at a lower SM clock and lose about 7 %; they are therefore
-// opt-in (MOE_B200_PAIR=1) and make sense for short bursts with at least ~2048 rows per expert.
+// m-tile height of the expert GEMMs: CTA pairs (256-row tiles, cta_group::2) or single CTAs (128-row
+// tiles) on the tensor-core path.  Measured on B200: with long K (Mixtral widths: d_model 4096, ffn
+// 14336) the single-CTA kernel wins by ~2.5 % in long, power-capped runs (the pair kernel is 2 %
+// faster per clock but settles at lower clocks); with short K (d 2048, hidden 1408, 66 experts) a
+// single CTA's four 48 KB stages cover too little load latency and the pair kernel, whose CTAs each
+// hold half of B and so have six stages, is 6.5 % faster for the whole layer.  Hence: pairs when both
+// GEMMs have short K and an expert has enough rows to fill 256-row tiles.  MOE_B200_PAIR = 0 / 1
+// forces the choice.
 int pick_tile_m(const moe_layer* L, int64_t rows, int n_experts) {
     if (L->cfg.compute_dtype != MOE_DTYPE_BF16) return F32_TILE_M;
     const char* ev = getenv("MOE_B200_PAIR");   // read per call: tests switch it at run time
     const int env_pair = ev ? atoi(ev) : -1;
-    (void)rows;
-    (void)n_experts;
-    const bool pair = env_pair > 0;
+    bool pair;
+    if (env_pair >= 0) {
+        pair = env_pair > 0;
+    } else {
+        const int64_t per_expert = n_experts > 0 ? rows / n_experts : 0;
+        pair = (int64_t)L->cfg.input_dim + L->cfg.hidden_dim <= 6144 && per_expert >= 2 * TC_PAIR_TILE_M;
+    }
     return pair ? TC_PAIR_TILE_M : TC_TILE_M;
 }
 
+// The grouped GEMM pair on `rows_cap` rows described by (expert_offset, tile_prefix).
 int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const int32_t* expert_offset,
                 const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base, int tile_m,
                 const int32_t* seg_start = nullptr, void* const* seg_dst = nullptr, int seg_per_expert = 0) {
@@ -1285,6 +1294,11 @@ int moe_layer_stage_ms(moe_layer_t* L, int calls_back, float ms[7]) {
 }
 
 int64_t moe_layer_launch_count(const moe_layer_t* L) { return L ? L->launches : 0; }
+
+int moe_layer_tile_rows(moe_layer_t* L, int64_t T) {
+    if (!L || T < 0) return fail(MOE_ERR_INVALID, "bad argument");
+    return pick_tile_m(L, T * L->k_tot, L->E);
+}
 
 int moe_layer_device_status(moe_layer_t* L, int32_t* status) {
     if (!L || !status) return fail(MOE_ERR_INVALID, "null argument");

@@ -568,6 +568,14 @@ class MoELayer:
         names = ["router", "scan_loss", "permute", "gemm1", "gemm2", "combine", "exchange"]
         return dict(zip(names, [float(v) for v in ms]))
 
+    def tile_rows(self, T: int) -> int:
+        """Rows per m-tile of the expert GEMMs for a batch of T tokens (256: CTA-pair kernel, 128:
+        single-CTA tensor-core kernel, 16: FP32 kernels)."""
+        n = int(_lib.lib.moe_layer_tile_rows(self._handle, int(T)))
+        if n < 0:
+            _lib.check(n)
+        return n
+
     def launch_count(self) -> int:
         return int(_lib.lib.moe_layer_launch_count(self._handle))
 
