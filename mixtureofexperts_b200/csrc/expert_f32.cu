@@ -142,8 +142,9 @@ __global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemm
 // One CTA owns (expert, 8*CW output columns); a warp owns CW columns; lanes split K in 16-byte
 // pieces, so every weight load instruction of a warp is a contiguous 512-byte read and a lane keeps
 // 2*CW (mode 1: 4*CW) of them in flight.  Four rows of the expert are held in registers per pass
-// (further rows re-read the CTA's weight slice, which is then L2-resident); partial dot products are
-// reduced with warp shuffles once per pass.  Bound: HBM, E*N*K*4 bytes of weights per GEMM.
+// (further rows of the expert are taken by the CTAs of the other blockIdx.z planes, which read the
+// same weight slice through L2 at the same time, or by further passes of this CTA); partial dot
+// products are reduced with warp shuffles once per pass.  Bound: HBM, E*N*K*4 bytes of weights per GEMM.
 constexpr int SK_ROWS = 4;
 constexpr int SK_THREADS = 256;
 
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(SK_THREADS) group_gemm_f32_skinny_kernel(const
     float* C = reinterpret_cast<float*>(p.C);
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
-    for (int r0 = row_begin; r0 < row_end; r0 += SK_ROWS) {
+    for (int r0 = row_begin + SK_ROWS * (int)blockIdx.z; r0 < row_end; r0 += SK_ROWS * (int)gridDim.z) {
         float acc[NB][CW][SK_ROWS];
 #pragma unroll
         for (int b = 0; b < NB; ++b)
@@ -241,17 +242,23 @@ __global__ void __launch_bounds__(SK_THREADS) group_gemm_f32_skinny_kernel(const
 }
 
 template <int MODE>
-int launch_skinny(const GroupGemmParams& p, int num_sms, cudaStream_t s) {
+int launch_skinny(const GroupGemmParams& p, int64_t rows, int num_sms, cudaStream_t s) {
+    // Row passes of an expert run side by side in the z planes of the grid instead of one after the
+    // other in one CTA: about twice the average rows per expert, at most 8 planes (a CTA whose
+    // plane has no rows left for its expert leaves at once).
+    const int64_t avg = p.E > 0 ? (rows + p.E - 1) / p.E : 1;
+    int planes = (int)((2 * avg + SK_ROWS - 1) / SK_ROWS);
+    planes = planes < 1 ? 1 : (planes > 8 ? 8 : planes);
     // fewer columns per warp when the problem would otherwise leave SMs without a CTA
     const long ctas4 = (long)((p.N + 31) / 32) * p.E;
     if (ctas4 >= 2L * num_sms) {
-        dim3 grid((p.N + 31) / 32, p.E);
+        dim3 grid((p.N + 31) / 32, p.E, planes);
         group_gemm_f32_skinny_kernel<MODE, 4><<<grid, SK_THREADS, 0, s>>>(p);
     } else if (ctas4 * 2 >= 2L * num_sms) {
-        dim3 grid((p.N + 15) / 16, p.E);
+        dim3 grid((p.N + 15) / 16, p.E, planes);
         group_gemm_f32_skinny_kernel<MODE, 2><<<grid, SK_THREADS, 0, s>>>(p);
     } else {
-        dim3 grid((p.N + 7) / 8, p.E);
+        dim3 grid((p.N + 7) / 8, p.E, planes);
         group_gemm_f32_skinny_kernel<MODE, 1><<<grid, SK_THREADS, 0, s>>>(p);
     }
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
@@ -267,7 +274,7 @@ int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, in
                          (mode != 1 || (reinterpret_cast<uintptr_t>(p.B1) & 15) == 0);
     if (aligned && rows <= 16L * p.E) {
         // on average at most 16 rows per expert: weight streaming beats tiling
-        return mode == 1 ? launch_skinny<1>(p, num_sms, s) : launch_skinny<2>(p, num_sms, s);
+        return mode == 1 ? launch_skinny<1>(p, rows, num_sms, s) : launch_skinny<2>(p, rows, num_sms, s);
     }
     dim3 grid(max_mtiles, (p.N + BN - 1) / BN);
     if (mode == 1) group_gemm_f32_kernel<1><<<grid, THREADS, 0, s>>>(p);
