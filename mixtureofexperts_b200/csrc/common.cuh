@@ -165,7 +165,7 @@ __device__ __forceinline__ T* group_gemm_out_row(const GroupGemmParams& p, int e
 
 // ---- launchers (each returns the number of kernels it launched, or <0 on a launch error) ---
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, int num_sms, cudaStream_t s);
-int router_tokens_per_cta(int64_t T, int num_sms);   // 64, 32 or 16
+int router_tokens_per_cta(int64_t T, int e_router, int num_sms);   // 64, 32 or 16
 int router_e_pad(int e_router);          // router rows padded to a multiple of 8 (bucketed)
 int router_d_pad(int D);                 // K rows of the K-major copy (multiple of 128)
 int launch_router_transpose(const float* w, float* wt, int E, int D, cudaStream_t s);

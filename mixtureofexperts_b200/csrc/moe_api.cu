@@ -377,7 +377,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     if ((rc = ensure_workspace(L, T > 0 ? T : 1))) return rc;
     if (!L->ep && L->plan_dirty && (rc = ensure_plan(L, L->xp, L->h, L->P_cap))) return rc;
 
-    const int tokens_per_cta = router_tokens_per_cta(T, L->num_sms);
+    const int tokens_per_cta = router_tokens_per_cta(T, L->E_router, L->num_sms);
     const int num_cta = (int)((T + tokens_per_cta - 1) / tokens_per_cta);
     if (L->prof_slots > 0) L->prof_cur = (int)(L->prof_calls++ % L->prof_slots);
     stage_mark(L, 0, s);

@@ -575,11 +575,22 @@ int launch_router_e(const RouterParams& p, int x_dtype, int num_cta, cudaStream_
 
 }  // namespace
 
-// Token tile of the router and permute kernels for a batch of T tokens: the largest of 64/32/16
-// that still gives every SM a CTA, so that small batches do not leave SMs idle.
-int router_tokens_per_cta(int64_t T, int num_sms) {
+// Token tile of the router and permute kernels for a batch of T tokens: the largest of 64/32/16 that
+// still gives enough CTAs.  A narrow router (at most 32 padded rows) is latency-bound and wants every
+// SM to have a CTA; a wide one is bound by FMA issue and loses more from re-reading the router
+// matrix for fewer tokens (66 rows, 32768 tokens: 0.53 ms with 64-token tiles, 0.73 ms with 32, 1.42
+// ms with 16) than from idle SMs, so it keeps large tiles until a quarter of the SMs would be idle.
+int router_tokens_per_cta(int64_t T, int e_router, int num_sms) {
+    static int forced = -1;     // MOE_B200_ROUTER_TILE = 16 / 32 / 64 forces the tile (experiments)
+    if (forced < 0) {
+        const char* e = getenv("MOE_B200_ROUTER_TILE");
+        const int v = e ? atoi(e) : 0;
+        forced = (v == 16 || v == 32 || v == 64) ? v : 0;
+    }
+    if (forced > 0) return forced;
+    const int64_t want = router_e_pad(e_router) <= 32 ? (int64_t)num_sms : (int64_t)num_sms * 3 / 4;
     for (int bt = ROUTER_TOKENS_PER_CTA; bt > 16; bt >>= 1)
-        if ((T + bt - 1) / bt >= (int64_t)num_sms) return bt;
+        if ((T + bt - 1) / bt >= want) return bt;
     return 16;
 }
 
