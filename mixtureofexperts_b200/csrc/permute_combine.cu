@@ -219,14 +219,24 @@ __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombinePara
     __shared__ float s_gate[MAX_KTOT];
     __shared__ int s_n;
     const int64_t t = blockIdx.x;
+    // the token's slots: one thread per slot fetches (expert, row, gate), so the loads overlap ...
+    __shared__ int s_id_in[MAX_KTOT], s_row_in[MAX_KTOT];
+    __shared__ float s_gate_in[MAX_KTOT];
+    if (threadIdx.x < p.k_tot) {
+        const int j = threadIdx.x;
+        s_id_in[j] = p.idx[t * p.k_tot + j];
+        s_row_in[j] = p.pair_pos[t * p.k_tot + j];
+        s_gate_in[j] = p.gate[t * p.k_tot + j];
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
-        // insertion sort of the token's slots by expert id (k_tot <= 16)
+        // ... then an insertion sort by expert id (k_tot <= 16)
         int ids[MAX_KTOT];
         int n = 0;
         for (int j = 0; j < p.k_tot; ++j) {
-            const int e = p.idx[t * p.k_tot + j];
-            const int r = p.pair_pos[t * p.k_tot + j];
-            const float g = p.gate[t * p.k_tot + j];
+            const int e = s_id_in[j];
+            const int r = s_row_in[j];
+            const float g = s_gate_in[j];
             if (r < 0) continue;
             int i = n++;
             while (i > 0 && ids[i - 1] > e) {
