@@ -14,14 +14,21 @@ benchmark configurations; weights N(0, 0.02^2), activations N(0, 1), seeded):
   c5  64 experts over N GPUs, same widths, top-2, BF16, 8192 tokens per GPU    (default at N>1)
   c4  64 routed + 2 shared experts, d 2048, hidden 1408, top-6, 32768 tokens, skewed routing
   c1  8 experts 512/2048/512, top-2, FP32, 32 tokens
+
+Keys of the line beyond the usual ones:
+  roofline        the dominant kernel (expert GEMM 1): algorithmic FLOPs / mean CUDA-event time of
+                  the timed steps, against the measured cuBLAS BF16 peaks (burst and sustained)
+  e2e             the same metric through moe_layer_forward_host with pinned host buffers
+  cpu_baseline    the CPU restatement of the reference path on the host cores, same token count
+  parity          outside the timed region: every rank compares its tokens' expert ids (all local
+                  tokens), a sample of outputs and the global loss with the CPU oracle
+  other_workloads c1 and c4 measured after the timed region (N=1 only)
 """
 from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -41,6 +48,8 @@ WORKLOADS = {
                desc="8 GatedExperts 512/2048/512 top-2 FP32, 32 tokens"),
 }
 SEED = 1234
+ALPHA, ZW = 0.01, 0.001
+CPU_BUDGET_S = 240.0        # the reference arm stops adding steps once it has used this much time
 
 
 def expert_flops(w, tokens):
@@ -56,6 +65,21 @@ def measured_peaks():
         return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
                     bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def recorded_dram_traffic(workload, kernel):
+    """DRAM bytes per launch of `kernel` on `workload`, from the record the ncu capture step leaves in
+    profiles/dram_traffic.txt (lines: workload kernel read_bytes write_bytes).  None if absent."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    try:
+        with open(path) as f:
+            for ln in f:
+                parts = ln.split()
+                if len(parts) >= 4 and not ln.startswith("#") and parts[0] == workload and parts[1] == kernel:
+                    return int(parts[2]) + int(parts[3]), f"ncu capture recorded in profiles/dram_traffic.txt: {ln.strip()}"
+    except OSError:
+        pass
+    return None, "no ncu capture recorded for this workload and kernel"
 
 
 class ClockSampler:
@@ -164,66 +188,320 @@ def build_layer(w, torch, device_index, ep=None):
     gate = m.SharedExpertGating(w["S"], m.TopKGating(w["k"]), w["E"]) if w["S"] else m.TopKGating(w["k"])
     cfg = m.create_moe_config(num_experts=w["E"], expert_type="gated", input_dim=w["D"], hidden_dim=w["H"],
                               output_dim=w["O"], activation=m.silu, gate_type=gate,
-                              balance_loss=m.SwitchTransformerLoss(0.01), z_loss_weight=0.001)
+                              balance_loss=m.SwitchTransformerLoss(ALPHA), z_loss_weight=ZW)
     router = make_router(w, torch, device)
     router.gate_type = gate
     return m.MoELayer(cfg, device=device_index, compute_dtype=w["dtype"], experts=make_expert_factory(w, torch, device),
                       router=router, expert_parallel=ep)
 
 
-def cpu_forward_rate(w, tokens, steps, warmup, threads_note=True):
-    """Times the CPU restatement of the reference path (the oracle) on `tokens` tokens of the
-    workload.  Returns (tokens/s, cores used, seconds per step)."""
+def workload_config(name, w, world):
+    """The `config` object of the JSON line: the same for the GPU arm and for the reference arm."""
+    if world == 1:
+        par = "single GPU"
+    else:
+        mode = os.environ.get("MOE_B200_EP_MODE", "peer")
+        data = ("token rows cross NVLink by peer stores inside the permute kernel and the GEMM-2 epilogue; NCCL carries "
+                "counts and the loss sums only") if mode != "nccl" else "token rows by grouped ncclSend/ncclRecv"
+        par = f"expert-parallel ep{world}: {w['E'] // world} experts per GPU, tokens data-parallel; {data}"
+    return {"workload": f"{name}: {w['desc']}", "tokens_per_gpu": w["T"], "experts": w["E"], "top_k": w["k"],
+            "shared_experts": w["S"], "d_model": w["D"], "ffn_hidden": w["H"], "parallelism": par, "training": True,
+            "l2": "inputs (activations + expert weights) are larger than L2; no flush needed"}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU leg: the restatement of the reference path (oracle/) timed on the host cores
+# --------------------------------------------------------------------------------------------------
+
+def cpu_forward_rate(w, world, steps, warmup, budget_s=CPU_BUDGET_S):
+    """Times the CPU restatement of the reference path on the workload's own token count.
+
+    world == 1: the whole layer (all experts, all T tokens).  world > 1: ONE rank's share of the
+    expert-parallel layer -- its E/world local experts on T tokens' worth of pairs (T*k rows, what a
+    rank receives on average) -- because all 64 experts in FP32 need 45 GB; the CPU doing the whole
+    job would run `world` such shares one after the other, so whole-job tokens/s = T / (time of one
+    share).  Weight values do not affect CPU time: one seeded N(0, std^2) draw per matrix shape is
+    rotated to give every expert its own arrays.  Returns (tokens/s, cores, s/step, steps timed, note)."""
     import numpy as np
 
     from oracle import moe_oracle as orc
 
     rng = np.random.Generator(np.random.PCG64(SEED))
-    E, D, H, O = w["E"], w["D"], w["H"], w["O"]
-    x = rng.standard_normal((tokens, D), dtype=np.float32)
+    E_all, D, H, O, T = w["E"], w["D"], w["H"], w["O"], w["T"]
+    E = E_all if world == 1 else E_all // world
+    S = w["S"] if world == 1 else 0
+    x = rng.standard_normal((T, D), dtype=np.float32)
     router = rng.standard_normal((E, D), dtype=np.float32) * np.float32(w["std"])
+    base = {"hd": rng.standard_normal((H, D), dtype=np.float32) * np.float32(w["std"]),
+            "oh": rng.standard_normal((O, H), dtype=np.float32) * np.float32(w["std"])}
     experts = []
-    for _ in range(E):
-        experts.append(orc.GatedExpertWeights(
-            w1=rng.standard_normal((H, D), dtype=np.float32) * np.float32(w["std"]),
-            w2=rng.standard_normal((O, H), dtype=np.float32) * np.float32(w["std"]),
-            w3=rng.standard_normal((H, D), dtype=np.float32) * np.float32(w["std"])))
-    gate = orc.SharedExpertGating(w["S"], orc.TopKGating(w["k"]), E) if w["S"] else orc.TopKGating(w["k"])
+    for e in range(E):
+        experts.append(orc.GatedExpertWeights(w1=np.roll(base["hd"], 7919 * (3 * e + 1)), w2=np.roll(base["oh"], 7919 * (3 * e + 2)),
+                                              w3=np.roll(base["hd"], 7919 * (3 * e + 3))))
+    gate = orc.SharedExpertGating(S, orc.TopKGating(w["k"]), E) if S else orc.TopKGating(w["k"])
     bias = None
     if w["bias_std"] > 0:
         bias = (rng.standard_normal(E) * w["bias_std"]).astype(np.float32)
-        bias[: w["S"]] = 0
+        bias[:S] = 0
     cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu", gate_type=gate,
-                        balance_alpha=0.01, z_loss_weight=0.001, router_bias=bias)
+                        balance_alpha=ALPHA, z_loss_weight=ZW, router_bias=bias)
     weights = orc.MoEWeights(router=router, experts=experts)
+    t_begin = time.perf_counter()
     for _ in range(warmup):
         orc.moe_layer_forward(cfg, weights, x, training=True)
-    t0 = time.perf_counter()
+    times = []
     for _ in range(steps):
+        t0 = time.perf_counter()
         orc.moe_layer_forward(cfg, weights, x, training=True)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    return tokens / dt, os.cpu_count() or 1, dt
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > budget_s:
+            break
+    dt = sum(times) / len(times)
+    if world == 1:
+        note = f"all {T} tokens of the same layer (all {E} experts, full widths), FP32 NumPy/OpenBLAS"
+    else:
+        note = (f"one rank's share of the {world}-GPU job: {E} local experts (full widths), {T} tokens top-{w['k']} = "
+                f"{T * w['k']} rows, FP32 NumPy/OpenBLAS; whole-job tokens/s = {T} / share time")
+    if len(times) < steps:
+        note += f"; stopped after {len(times)} of {steps} steps (time budget {budget_s:.0f} s)"
+    return T / dt, os.cpu_count() or 1, dt, len(times), note
 
 
 def run_reference_arm(args, w, name):
     """--impl reference: the reference's CPU path (its NumPy/OpenBLAS restatement; the Julia
-    original cannot run without a Julia runtime) on all host cores, a bounded sample per step."""
+    original cannot run without a Julia runtime) on all host cores, on the GPU arm's workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = min(w["T"], 1024 if w["dtype"] == "bf16" else w["T"])
-    rate, cores, dt = cpu_forward_rate(w, sample, args.steps, max(args.warmup, 1))
+    world = max(args.gpus, 1)
+    rate, cores, dt, done, note = cpu_forward_rate(w, world, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": rate, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{name}: {w['desc']}", "note": "CPU path, FP32 (OpenBLAS), host cores only"},
-        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"{sample} tokens per step of the same layer (all {w['E']} experts, full widths)"},
+        "config": workload_config(name, w, world),
+        "reference_note": "CPU path of the reference restated in NumPy (FP32, OpenBLAS on all host cores); no Julia runtime exists on the box",
+        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": note},
         "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+# parity block (outside every timed region): the oracle as the checker of what was just timed
+# --------------------------------------------------------------------------------------------------
+
+def parity_block(w, layer, x, torch, rank, world, dist, device, n_sample=96):
+    """Every rank checks its own tokens of the layer it just timed against the CPU oracle:
+    expert ids of ALL local tokens (exact, except float64-logit ties below 1e-6), gates, the
+    outputs of a sample of tokens (BF16: 2e-2, FP32: 1e-5, relative inf-norm) and the loss over all
+    ranks' tokens (1e-5 relative; oracle sums all-reduced in float64).  Experts are regenerated one
+    at a time from their seeds, so no rank ever holds more than one FP32 expert on the host.
+    Returns the dict printed as `parity`; `ok` is False on any violation."""
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import check_indices, rel_inf
+    from oracle import moe_oracle as orc
+
+    E, S, k, D, H, O, T = w["E"], w["S"], w["k"], w["D"], w["H"], w["O"], w["T"]
+    out, loss, routing = layer(x.t(), training=True, return_routing=True)
+    torch.cuda.synchronize()
+    dev_idx = routing["indices"].t().cpu().numpy()
+    dev_gates = routing["gates"].t().cpu().numpy()
+    dev_out = out.t()
+    router = make_router(w, torch, device)
+    bias = router.bias.cpu().numpy() if getattr(router, "bias", None) is not None else None
+    rw = router.weight.cpu().numpy()
+    xs = x.float().cpu().numpy()
+    gate = orc.SharedExpertGating(S, orc.TopKGating(k), E) if S else orc.TopKGating(k)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu", gate_type=gate,
+                        balance_alpha=ALPHA, z_loss_weight=ZW, router_bias=bias)
+    o_idx, o_gates, o_probs, o_logits = orc.router_forward(cfg, orc.MoEWeights(router=rw, experts=[]), xs)
+    logits64 = xs.astype(np.float64) @ rw.astype(np.float64).T
+    if bias is not None:
+        logits64 = logits64 + bias.astype(np.float64)
+    res = {"tokens": int(T), "ok": True}
+    try:
+        res["idx_excused"] = int(check_indices(dev_idx, o_idx, logits64, k, r0=S))
+    except AssertionError as exc:
+        res.update(ok=False, idx_error=str(exc)[:200])
+        res["idx_excused"] = -1
+    same = (dev_idx == o_idx).all(axis=1)
+    res["idx_mismatch_tokens"] = int((~same).sum())
+    res["gates_rel_inf"] = rel_inf(dev_gates[same], o_gates[same])
+    # global loss from the oracle's per-rank sums (Switch: f_i over all pairs, P_i mean prob; z: mean lse^2)
+    sums = np.concatenate([np.bincount(o_idx.ravel() - 1, minlength=E).astype(np.float64),
+                           o_probs.sum(axis=0, dtype=np.float64),
+                           [float((orc.logsumexp_dim1(o_logits).astype(np.float64) ** 2).sum()), float(T)]])
+    if world > 1:
+        ts = torch.from_numpy(sums).to(device)
+        dist.all_reduce(ts)
+        sums = ts.cpu().numpy()
+    Tg = sums[-1]
+    n_probs = o_probs.shape[1]
+    o_loss = ALPHA * n_probs * float(np.sum((sums[:E] / ((k + S) * Tg)) * (sums[E:E + n_probs] / Tg))) + ZW * sums[E + n_probs] / Tg
+    res["loss_rel"] = abs(float(loss.item()) - o_loss) / abs(o_loss)
+    # outputs: tokens whose oracle experts all lie in a small expert subset (spread over the ranks), so
+    # that only those experts have to be regenerated on the host
+    if 12.0 * E * H * D <= 8e9:
+        subset = list(range(E))                            # the whole layer in FP32 is a few GB: every expert
+    else:
+        subset = sorted({(rank * 5 + j * (E // 8 + 1)) % E for j in range(8)})
+    sub_mask = np.zeros(E + 1, dtype=bool)
+    sub_mask[np.asarray(subset) + 1] = True
+    cand = np.where(sub_mask[o_idx].all(axis=1) & same)[0]
+    if len(cand) > n_sample:
+        cand = cand[np.linspace(0, len(cand) - 1, n_sample).astype(np.int64)]
+    res["out_tokens"] = int(len(cand))
+    if len(cand):
+        fac = make_expert_factory(w, torch, device)
+        o_out = np.zeros((len(cand), O), dtype=np.float32)
+        xc = xs[cand]
+        for e in subset:                                   # ascending expert id, like the reference's expert loop
+            rows, slots = np.where(o_idx[cand] == e + 1)
+            if not len(rows):
+                continue
+            ex = fac(e)
+            ew = orc.GatedExpertWeights(w1=ex.w1.float().cpu().numpy(), w2=ex.w2.float().cpu().numpy(),
+                                        w3=ex.w3.float().cpu().numpy())
+            y = orc.gated_expert_forward(ew, xc[rows], orc.silu)
+            np.add.at(o_out, rows, o_gates[cand][rows, slots][:, None] * y)
+            del ex, ew
+        res["out_rel_inf"] = rel_inf(dev_out[torch.as_tensor(cand, device=device)].cpu().numpy(), o_out)
+    else:
+        res["out_rel_inf"] = None
+    tol_out = 2e-2 if w["dtype"] == "bf16" else 1e-5
+    if res["gates_rel_inf"] > 1e-5 or res["loss_rel"] > 1e-5 or not res["out_tokens"] or res["out_rel_inf"] > tol_out:
+        res["ok"] = False
+    res["tolerances"] = {"idx": "exact except float64-logit gaps < 1e-6", "gates": 1e-5, "loss_rel": 1e-5, "out_rel_inf": tol_out}
+    if world > 1:                                           # one verdict for the job: every rank must pass
+        agg = torch.tensor([0.0 if res["ok"] else 1.0, float(res["idx_mismatch_tokens"]), float(res["out_tokens"]),
+                            float(T)], device=device, dtype=torch.float64)
+        mx = torch.tensor([res["gates_rel_inf"], res["loss_rel"], res["out_rel_inf"] or 0.0], device=device, dtype=torch.float64)
+        dist.all_reduce(agg)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        res.update(ok=bool(agg[0].item() == 0), idx_mismatch_tokens=int(agg[1].item()),
+                   idx_excused=int(agg[1].item()) if res["idx_excused"] >= 0 else -1, out_tokens=int(agg[2].item()),
+                   tokens=int(agg[3].item()), gates_rel_inf=float(mx[0].item()), loss_rel=float(mx[1].item()),
+                   out_rel_inf=float(mx[2].item()), ranks=world)
+    return res
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU measurement of one workload
+# --------------------------------------------------------------------------------------------------
+
+def measure_device(layer, x, out, steps, warmup, torch, barrier, sampler=None):
+    """W untimed + K timed forwards with x resident in HBM; CUDA events on the launching stream."""
+    for _ in range(warmup):
+        layer(x.t(), training=True, out=out)
+    barrier()
+    layer.set_profiling(min(steps, 1024))
+    launches0 = layer.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_mark0 = sampler.mark() if sampler else None
+    ev0.record()
+    loss = None
+    for _ in range(steps):
+        _, loss = layer(x.t(), training=True, out=out)
+    ev1.record()
+    barrier()
+    t_mark1 = sampler.mark() if sampler else None
+    ms_total = ev0.elapsed_time(ev1)
+    launches = layer.launch_count() - launches0
+    n_prof = min(steps, 1024)
+    stages = {}
+    for back in range(n_prof):
+        for k_, v in layer.stage_ms(back).items():
+            stages[k_] = stages.get(k_, 0.0) + v / n_prof
+    layer.set_profiling(0)
+    return ms_total, launches, stages, loss, (t_mark0, t_mark1)
+
+
+def roofline_of(w, name, T, stages, ms_step, peaks, tile_rows, world, clocks, full_size):
+    f_g1 = 2.0 * w["H"] * 2 * w["D"] * T * (w["k"] + w["S"])
+    f_g2 = 2.0 * w["H"] * w["O"] * T * (w["k"] + w["S"])
+    mhz = (clocks or {}).get("sm_mhz")
+    if w["dtype"] == "bf16" and stages.get("gemm1", 0) > 0 and world == 1:
+        ach = f_g1 / (stages["gemm1"] * 1e-3) / 1e12
+        pair = tile_rows == 256
+        kernel = "group_gemm_tc2_kernel<1>" if pair else "group_gemm_tc_kernel<1>"
+        traffic, note = recorded_dram_traffic(name, kernel) if full_size else (None, "not the recorded workload size")
+        burst, sust = peaks["bf16_tflops"], peaks["bf16_tflops_sustained"]
+        return {"bound": "tensor", "kernel": kernel + (" (CTA pairs)" if pair else "") + ": x W1^T, x W3^T, act*up",
+                "achieved": ach, "peak": burst, "unit": "TFLOP/s", "frac": ach / burst,
+                "frac_burst": ach / burst, "frac_sustained": ach / sust, "peak_sustained": sust,
+                "peak_source": f"{peaks['source']} cuBLAS bf16 8192^3: burst {burst} (best of 10), sustained {sust} (4 s loop under the "
+                               "power cap); `frac` uses the burst figure, the timed region is a fraction of a second",
+                "gemm1_ms": stages["gemm1"], "gemm1_ms_x_sm_mhz": stages["gemm1"] * mhz if mhz else None,
+                "traffic": traffic, "traffic_unit": "bytes per launch", "traffic_note": note,
+                "algorithmic_bytes": 2.0 * (2 * w["E"] * w["H"] * w["D"] + T * (w["k"] + w["S"]) * (w["D"] + w["H"])),
+                "gemm2_achieved": f_g2 / (stages["gemm2"] * 1e-3) / 1e12 if stages.get("gemm2", 0) > 0 else None,
+                "layer_achieved": expert_flops(w, T) / (ms_step * 1e-3) / 1e12,
+                "layer_frac_burst": expert_flops(w, T) / (ms_step * 1e-3) / 1e12 / burst,
+                "layer_frac_sustained": expert_flops(w, T) / (ms_step * 1e-3) / 1e12 / sust}
+    if w["dtype"] == "bf16":
+        ach = expert_flops(w, T) / (ms_step * 1e-3) / 1e12
+        burst, sust = peaks["bf16_tflops"], peaks["bf16_tflops_sustained"]
+        return {"bound": "tensor", "kernel": "whole layer per GPU (expert GEMM FLOPs / step time)",
+                "achieved": ach, "peak": burst, "unit": "TFLOP/s", "frac": ach / burst, "frac_burst": ach / burst,
+                "frac_sustained": ach / sust, "peak_sustained": sust,
+                "peak_source": f"{peaks['source']} cuBLAS bf16: burst {burst}, sustained {sust}", "traffic": None}
+    nbytes = 4.0 * w["E"] * w["H"] * (2 * w["D"] + w["O"])
+    t_g = (stages.get("gemm1", 0) + stages.get("gemm2", 0)) * 1e-3
+    if t_g <= 0:
+        return None
+    ach = nbytes / t_g / 1e9
+    return {"bound": "hbm", "kernel": "FP32 expert GEMM pair (expert weights streamed once)",
+            "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+            "peak_source": f"{peaks['source']} STREAM-style copy", "traffic": None,
+            "note": "the 100 MB of weights fit in L2 (126 MB): without an L2 flush between steps this is an L2-resident figure"}
+
+
+def measure_other(name, torch, peaks, steps=10, warmup=3):
+    """One more workload on cuda:0 after the headline's timed region: ms/step, stage times, roofline."""
+    w = dict(WORKLOADS[name])
+    layer = build_layer(w, torch, 0)
+    T, D, O = w["T"], w["D"], w["O"]
+    xdt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    gx = torch.Generator(device="cuda:0").manual_seed(SEED + 7)
+    x = torch.randn((T, D), device="cuda:0", generator=gx, dtype=torch.float32).to(xdt)
+    out = torch.empty((T, O), device="cuda:0", dtype=torch.float32)
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda:0") if w["dtype"] == "f32" else None
+
+    def barrier():
+        torch.cuda.synchronize()
+
+    ms_total, launches, stages, loss, _ = measure_device(layer, x, out, steps, warmup, torch, barrier)
+    ms_step = ms_total / steps
+    res = {"workload": f"{name}: {w['desc']}", "ms_per_step": ms_step, "tokens_per_s": T / (ms_step * 1e-3),
+           "steps": steps, "warmup": warmup, "stage_ms": stages, "gpu_launches": launches,
+           "roofline": roofline_of(w, name, T, stages, ms_step, peaks, layer.tile_rows(T), 1, None, True),
+           "loss": float(loss.item()), "device_status": layer.device_status()}
+    if flush is not None:
+        # the FP32 workload's weights fit in L2: time it again with L2 flushed before every step
+        layer.set_profiling(steps)
+        for _ in range(steps):
+            flush.fill_(1)
+            layer(x.t(), training=True, out=out)
+        torch.cuda.synchronize()
+        cold = {}
+        for back in range(steps):
+            for k_, v in layer.stage_ms(back).items():
+                cold[k_] = cold.get(k_, 0.0) + v / steps
+        layer.set_profiling(0)
+        res["stage_ms_l2_flushed"] = cold
+        t_g = (cold.get("gemm1", 0) + cold.get("gemm2", 0)) * 1e-3
+        if t_g > 0:
+            nbytes = 4.0 * w["E"] * w["H"] * (2 * w["D"] + w["O"])
+            res["roofline_l2_flushed"] = {"bound": "hbm", "achieved": nbytes / t_g / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                          "frac": nbytes / t_g / 1e9 / peaks["hbm_gbs"],
+                                          "step_ms": sum(v for k_, v in cold.items() if k_ != "exchange")}
+    layer.close()
+    return res
 
 
 def main():
@@ -237,12 +515,15 @@ def main():
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="skip the c1/c4 block measured after the timed region")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3  # timing rule: at least 3 warm-up steps
 
     name = args.workload if args.workload != "auto" else ("c3" if args.gpus == 1 else "c5")
     w = dict(WORKLOADS[name])
+    full_size = args.tokens == 0 and args.experts == 0
     if args.tokens > 0:
         w["T"] = args.tokens
     if args.experts > 0:
@@ -283,30 +564,12 @@ def main():
     x = torch.randn((T, D), device=device, generator=gx, dtype=torch.float32).to(xdt)
     out = torch.empty((T, O), device=device, dtype=torch.float32)
 
-    def step():
-        return layer(x.t(), training=True, out=out)
-
     # ---- device-resident throughput ---------------------------------------------------------
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    layer.set_profiling(min(args.steps, 1024))
     sampler = ClockSampler(str(torch.cuda.get_device_properties(local_rank).uuid))
     if rank == 0:
         sampler.start()
-    launches0 = layer.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    t_mark0 = sampler.mark()
-    ev0.record()
-    for _ in range(args.steps):
-        _, loss = step()
-    ev1.record()
-    barrier()
-    t_mark1 = sampler.mark()
-    ms_total = ev0.elapsed_time(ev1)
-    clocks = sampler.stop(t_mark0, t_mark1) if rank == 0 else None
-    launches = layer.launch_count() - launches0
+    ms_total, launches, stages, loss, marks = measure_device(layer, x, out, args.steps, args.warmup, torch, barrier, sampler)
+    clocks = sampler.stop(*marks) if rank == 0 else None
     status = layer.device_status()
     if world > 1:
         t = torch.tensor([ms_total], device=device)
@@ -314,14 +577,6 @@ def main():
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
     value = T * world / (ms_step * 1e-3)
-
-    # per-stage device times of the timed steps (CUDA events on the launching stream)
-    n_prof = min(args.steps, 1024)
-    stages = {}
-    for back in range(n_prof):
-        for k_, v in layer.stage_ms(back).items():
-            stages[k_] = stages.get(k_, 0.0) + v / n_prof
-    layer.set_profiling(0)
     loss_value = float(loss.item())
     output_finite = bool(torch.isfinite(out).all().item())   # the timed steps produced real numbers
 
@@ -347,69 +602,48 @@ def main():
         e2e = {"value": T * world / dt, "unit": "tokens/s", "h2d_bytes_per_step": T * D * xh.element_size(),
                "d2h_bytes_per_step": T * O * 4 + 4, "ms_per_step": dt * 1e3,
                "timing": "host clock around synchronous moe_layer_forward_host calls (pinned buffers), max over ranks"}
+        del xh, oh
 
+    # ---- parity of what was just timed (outside the timed regions) --------------------------
+    parity = None
+    if not args.no_parity:
+        parity = parity_block(w, layer, x, torch, rank, world, dist, device)
+
+    tile_rows = layer.tile_rows(T)
+    layer.close()
+    del layer
+    fail = None
     if rank == 0:
         peaks = measured_peaks()
-        tokens_local_pairs = T  # per GPU
-        f_g1 = 2.0 * w["H"] * 2 * w["D"] * tokens_local_pairs * (w["k"] + w["S"])
-        f_g2 = 2.0 * w["H"] * w["O"] * tokens_local_pairs * (w["k"] + w["S"])
-        roof = None
-        # DRAM bytes of one group_gemm_tc_kernel<1> launch, from an ncu capture of this command at full
-        # size (dram__bytes_read.sum + dram__bytes_write.sum, 1 pass; profiles/c3_dram_bytes.md).
-        # Algorithmic bytes of the launch: weights 1.879 GB + rows 0.268 GB + h 0.940 GB = 3.087 GB.
-        traffic, traffic_note = None, "no ncu capture for this workload size"
-        if name == "c3" and args.tokens == 0 and args.experts == 0:
-            traffic = 2889976576 + 925794304
-            traffic_note = "ncu capture of this workload: 2.890 GB read + 0.926 GB written vs 3.087 GB algorithmic"
-        if w["dtype"] == "bf16" and stages.get("gemm1", 0) > 0 and world == 1:
-            ach = f_g1 / (stages["gemm1"] * 1e-3) / 1e12
-            peak = peaks["bf16_tflops_sustained"]
-            gemm_kernel = "group_gemm_tc2_kernel<1>, CTA pairs" if layer.tile_rows(T) == 256 else "group_gemm_tc_kernel<1>"
-            roof = {"bound": "tensor", "kernel": gemm_kernel + " (x W1^T, x W3^T, act*up)",
-                    "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                    "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (kernel timed inside a long step); burst {peaks['bf16_tflops']}",
-                    "traffic": traffic, "traffic_unit": "bytes per launch",
-                    "traffic_note": traffic_note,
-                    "gemm2_achieved": f_g2 / (stages["gemm2"] * 1e-3) / 1e12 if stages.get("gemm2", 0) > 0 else None,
-                    "layer_frac": expert_flops(w, T) / (ms_step * 1e-3) / 1e12 / peak}
-        elif w["dtype"] == "bf16" and world > 1:
-            ach = expert_flops(w, T) / (ms_step * 1e-3) / 1e12
-            peak = peaks["bf16_tflops_sustained"]
-            roof = {"bound": "tensor", "kernel": "whole layer per GPU (expert GEMM FLOPs / step time)",
-                    "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                    "peak_source": f"{peaks['source']} sustained cuBLAS bf16", "traffic": None}
-        elif w["dtype"] == "f32":
-            nbytes = 4.0 * w["E"] * w["H"] * (2 * w["D"] + w["O"])
-            t_g = (stages.get("gemm1", 0) + stages.get("gemm2", 0)) * 1e-3
-            if t_g > 0:
-                ach = nbytes / t_g / 1e9
-                roof = {"bound": "hbm", "kernel": "group_gemm_f32_kernel<1>+<2> (expert weights streamed once)",
-                        "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                        "peak_source": peaks["source"], "traffic": None}
+        roof = roofline_of(w, name, T, stages, ms_step, peaks, tile_rows, world, clocks, full_size)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            sample = min(T, 1024 if w["dtype"] == "bf16" else T)
-            rate, cores, dt = cpu_forward_rate(w, sample, 2, 1)
-            cpu = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port",
-                   "sample": f"{sample} tokens of the same layer (all {w['E']} experts, full widths), FP32 OpenBLAS, 2 timed passes"}
+            rate, cores, dt_cpu, done, note = cpu_forward_rate(w, 1, 2, 0, budget_s=60.0)
+            cpu = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "s_per_step": dt_cpu,
+                   "sample": note + f", {done} timed pass(es)"}
+        others = None
+        if world == 1 and not args.no_others and full_size:
+            torch.cuda.empty_cache()
+            others = {n: measure_other(n, torch, peaks) for n in ("c4", "c1") if n != name}
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": f"{name}: {w['desc']}", "tokens_per_gpu": T, "experts": w["E"],
-                       "top_k": w["k"], "shared_experts": w["S"], "d_model": D, "ffn_hidden": w["H"],
-                       "parallelism": "single GPU" if world == 1 else f"expert-parallel ep{world} (NCCL all-to-all)",
-                       "training": True, "l2": "inputs (activations + expert weights) are larger than L2; no flush needed"},
+            "config": workload_config(name, w, world),
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu,
-            "stage_ms": stages, "loss": loss_value, "output_finite": output_finite, "device_status": status,
+            "parity": parity, "stage_ms": stages, "loss": loss_value, "output_finite": output_finite,
+            "device_status": status, "other_workloads": others,
         }
         print(json.dumps(line), flush=True)
         if not output_finite or status != 0:
-            raise SystemExit("bench: the layer produced non-finite output or a device status")
-    layer.close()
+            fail = "bench: the layer produced non-finite output or a device status"
+        elif parity is not None and not parity["ok"]:
+            fail = f"bench: parity against the CPU oracle failed: {parity}"
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if fail:
+        raise SystemExit(fail)
 
 
 if __name__ == "__main__":

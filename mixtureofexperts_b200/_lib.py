@@ -29,6 +29,18 @@ EXPORTS = [
     "moe_route_static_error",
 ]
 
+# Return types that are not `int` (every other export returns a status code).  One table, applied
+# after the argument types, so that no later loop can overwrite a 64-bit or pointer return type.
+RESTYPES = {
+    "moe_layer_weights_image_bytes": C.c_int64,
+    "moe_layer_launch_count": C.c_int64,
+    "moe_ep_layout": C.c_int64,
+    "moe_route_static_scratch_bytes": C.c_int64,
+    "moe_route_static_error": C.c_char_p,
+    "moe_last_error": C.c_char_p,
+    "moe_version": C.c_char_p,
+}
+
 
 class MoEError(RuntimeError):
     """Raised for any non-zero status of the C ABI (the reference raises error()/ArgumentError)."""
@@ -70,7 +82,6 @@ def _load():
     lib.moe_layer_set_aux_free.argtypes = [vp, i32, C.c_float, C.c_float, i32, vp, i64]
     lib.moe_layer_aux_free_state.argtypes = [vp, vp, vp, vp]
     lib.moe_layer_weights_image_bytes.argtypes = [vp]
-    lib.moe_layer_weights_image_bytes.restype = i64
     lib.moe_layer_export_weights.argtypes = [vp, vp, i64]
     lib.moe_layer_import_weights.argtypes = [vp, vp, i64]
     lib.moe_layer_set_router.argtypes = [vp, vp, vp, i32, i32]
@@ -85,23 +96,15 @@ def _load():
     lib.moe_layer_stage_ms.argtypes = [vp, i32, C.POINTER(C.c_float)]
     lib.moe_layer_tile_rows.argtypes = [vp, i64]
     lib.moe_layer_launch_count.argtypes = [vp]
-    lib.moe_layer_launch_count.restype = C.c_int64
     lib.moe_layer_device_status.argtypes = [vp, C.POINTER(C.c_int32)]
     lib.moe_ep_unique_id.argtypes = [vp]
     lib.moe_ep_init.argtypes = [vp, vp, i32, i32]
     lib.moe_ep_layout.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
-    lib.moe_ep_layout.restype = C.c_int64
     lib.moe_layer_destroy.argtypes = [vp]
     lib.moe_route_static.argtypes = [i32, i32, i32, i32, i32, vp, i32, i64, i32, vp, vp, f32, f32, i32, vp, vp, vp, vp, vp]
-    lib.moe_route_static_scratch_bytes.restype = C.c_int64
-    lib.moe_route_static_error.restype = C.c_char_p
-    lib.moe_last_error.restype = C.c_char_p
-    lib.moe_version.restype = C.c_char_p
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name not in ("moe_last_error", "moe_version", "moe_layer_launch_count", "moe_route_static_error",
-                        "moe_route_static_scratch_bytes", "moe_ep_layout"):
-            fn.restype = C.c_int
+        fn.restype = RESTYPES.get(name, C.c_int)
     return lib
 
 

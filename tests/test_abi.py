@@ -30,6 +30,21 @@ def test_binding_lists_every_declared_symbol(lib_built):
     assert sorted(_lib.EXPORTS) == declared_symbols()
 
 
+def test_binding_return_types_follow_the_header(lib_built):
+    """Every export's ctypes restype must be the header's return type: an int64_t truncated to int
+    loses the size of weight images of 2 GiB and more; a char* read as int is garbage."""
+    from mixtureofexperts_b200 import _lib
+
+    text = open(os.path.join(ROOT, "include", "moe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    decl = dict((name, ret.strip()) for ret, name in re.findall(r"^\s*((?:const\s+)?[a-z0-9_]+\s*\*?)\s*(moe_[a-z0-9_]+)\s*\(", text, flags=re.M))
+    assert sorted(decl) == declared_symbols()
+    want = {"int": C.c_int, "int64_t": C.c_int64, "const char*": C.c_char_p, "const char *": C.c_char_p}
+    for name, ret in decl.items():
+        assert getattr(_lib.lib, name).restype is want[ret], (name, ret, getattr(_lib.lib, name).restype)
+    assert _lib.lib.moe_layer_weights_image_bytes.restype is C.c_int64
+
+
 def test_config_struct_matches_header(lib_built):
     from mixtureofexperts_b200 import _lib
 

@@ -12,7 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import bench  # noqa: E402
-from helpers import rel_inf  # noqa: E402
+from helpers import check_indices, rel_inf  # noqa: E402
 from oracle import moe_oracle as orc  # noqa: E402
 
 pytestmark = pytest.mark.gpu
@@ -32,7 +32,7 @@ def _oracle_weights(w, device):
     return orc.MoEWeights(router=r.weight.cpu().numpy(), experts=experts), bias
 
 
-@pytest.mark.parametrize("name,n_sample", [("c3", 24), ("c4", 12)])
+@pytest.mark.parametrize("name,n_sample", [("c3", 256), ("c4", 160)])
 def test_benchmark_workload_full_size(name, n_sample):
     w = dict(bench.WORKLOADS[name])
     device = "cuda:0"
@@ -68,10 +68,21 @@ def test_benchmark_workload_full_size(name, n_sample):
     gate = orc.SharedExpertGating(S, orc.TopKGating(k), E) if S else orc.TopKGating(k)
     cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=w["H"], output_dim=O, activation="silu", gate_type=gate,
                         z_loss_weight=0.0, router_bias=bias)
-    o_out, _, aux = orc.moe_layer_forward(cfg, weights, x[sample].float().cpu().numpy(), training=False)
+    xs = x[sample].float().cpu().numpy()
+    o_out, _, aux = orc.moe_layer_forward(cfg, weights, xs, training=False)
     got_idx = idx[sample].cpu().numpy()
+    # expert ids: bit-exact, except where the float64 logits of neighbouring ranks around the
+    # selected set differ by less than 1e-6 (the tie window of partialsortperm on FP32
+    # probabilities, src/gating/topk.jl:35); check_indices fails on any other difference
+    logits64 = xs.astype(np.float64) @ weights.router.astype(np.float64).T
+    if bias is not None:
+        logits64 = logits64 + bias.astype(np.float64)
+    excused = check_indices(got_idx, aux["indices"], logits64, k, r0=S)
     same = (got_idx == aux["indices"]).all(axis=1)
-    assert same.mean() >= 0.9, "more than a few sampled tokens route differently"   # ties aside
+    assert excused == int((~same).sum()) and excused <= max(1, n_sample // 50), excused
+    # outputs of the tokens whose ids agree (a tie-excused token ran through other experts)
     err = rel_inf(out.t()[sample][same].cpu().numpy(), o_out[same])
     assert err < 2e-2, err
+    g_err = rel_inf(gates[sample][same].cpu().numpy(), aux["gates"][same])
+    assert g_err < 1e-5, g_err
     layer.close()
