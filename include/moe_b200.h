@@ -24,6 +24,18 @@
  *     until the stream reaches the end of the call.
  *   - There is no CPU fallback: without a usable CUDA device every compute call fails
  *     with MOE_ERR_CUDA.
+ *
+ * Environment switches (experiments and comparisons; defaults are what the measurements use).
+ * The first three are read when a handle is created, the others once per process:
+ *   MOE_B200_PAIR=0|1          force the single-CTA (128-row tiles) or the CTA-pair (256-row tiles,
+ *                              cta_group::2) tensor-core GEMM kernels instead of the per-batch choice
+ *   MOE_B200_HOST_CHUNKS=n     moe_layer_forward_host cuts batches of 8192 tokens and more into n
+ *                              equal chunks (1 = no chunking) instead of its default 1/5/5/4/1 schedule
+ *   MOE_B200_HOST_TIMELINE=1   print every chunk's copy and compute times to stderr
+ *   MOE_B200_GROUP_M=n         m-tiles per group of the GEMM tile order (default 32)
+ *   MOE_B200_ROUTER_TILE=16|32|64   force the token tile of the router and permute kernels
+ *   MOE_B200_EP_MODE=nccl      expert parallelism moves token rows with ncclSend/ncclRecv instead of
+ *                              peer stores from the library's own kernels (read by moe_ep_init)
  */
 #ifndef MOE_B200_H
 #define MOE_B200_H
@@ -40,7 +52,8 @@ extern "C" {
 #define MOE_ERR_CUDA          -2   /* a CUDA runtime/driver call failed or no device */
 #define MOE_ERR_UNSUPPORTED   -3   /* valid request this build does not implement */
 #define MOE_ERR_STATE         -4   /* weights not set, EP not initialised, ... */
-#define MOE_ERR_TIMEOUT       -5   /* a bounded device-side wait gave up (status word set) */
+#define MOE_ERR_TIMEOUT       -5   /* a bounded wait gave up: a device-side wait (status word set) or, with
+                                      expert parallelism, a rank that did not join a collective in time */
 #define MOE_ERR_NCCL          -6   /* an NCCL call failed */
 
 /* ---- enums (int32 in moe_config_t) ------------------------------------------------- */
@@ -235,19 +248,44 @@ int64_t moe_layer_launch_count(const moe_layer_t*);
 /* Value of the device status word after the last synchronising call (0 = clean). */
 int moe_layer_device_status(moe_layer_t*, int32_t* status);
 
+/* Self-test of the bounded waits the tensor-core kernels are built on (no counterpart in the
+ * reference): launches one thread on `device` that waits on an mbarrier nobody ever arrives on,
+ * with a limit of `limit_us` microseconds (1..1000000), through the same wait routine the GEMM
+ * kernels use.  The wait must give up: *status_out receives the device status code it recorded
+ * (1 = "waited too long for a TMA stage") and *waited_us how long the thread waited.  Nothing
+ * faults or hangs; the context stays usable.  Synchronises the device. */
+int moe_selftest_bounded_wait(int device, int limit_us, int32_t* status_out, int32_t* waited_us);
+
 /* ---- expert parallelism (no counterpart in the reference: it has no communication layer) */
 
 /* Fill `id128` (128 bytes) with a fresh NCCL unique id; rank 0 calls it and ships the
  * bytes to the other ranks by any host channel. */
 int moe_ep_unique_id(void* id128);
 
-/* Joins the handle to an expert-parallel group of `world` ranks (one process per GPU).
+/* Joins the handle to an expert-parallel group of `world` ranks (one process per GPU, at most 32).
  * Experts are block-partitioned: rank r owns experts [r*E/world, (r+1)*E/world); only those
  * need moe_layer_set_expert.  Tokens stay data-parallel; the router is replicated.
  * After this, moe_layer_forward dispatches token rows with an all-to-all over NVLink,
  * runs the local experts, returns the rows with a second all-to-all and combines them;
- * the balance loss is reduced over all ranks' tokens. */
+ * the balance loss is reduced over all ranks' tokens.
+ *   - Every forward is a collective: all ranks call it the same number of times (a rank without
+ *     tokens calls it with T = 0).  moe_layer_forward then SYNCHRONISES WITH THE HOST once per call
+ *     (the routing counts of all ranks are read back to lay out the exchange), so it is not
+ *     asynchronous under expert parallelism.
+ *   - Per-expert pair counts travel as 32-bit integers and are summed in 64 bits: the loss is exact
+ *     as long as one rank's pairs per call stay below 2^31.
+ *   - Failure handling: the group is joined through a non-blocking NCCL communicator and every
+ *     wait on another rank -- on the host or in a kernel -- is bounded by the timeout below.  A rank
+ *     that does not arrive makes the call return MOE_ERR_TIMEOUT (or MOE_ERR_NCCL for an NCCL
+ *     error); the communicator is aborted, the GPU stays usable, and every later expert-parallel
+ *     call on the handle returns MOE_ERR_STATE.  A rank that cannot allocate its receive buffers
+ *     still takes part in the exchange of that fact, so all ranks return MOE_ERR_CUDA together. */
 int moe_ep_init(moe_layer_t*, const void* id128, int rank, int world);
+
+/* Deadline, in milliseconds, of every wait on another rank (default 30000; device-side waits use
+ * min(timeout, 10000)).  May be called before moe_ep_init (it then also bounds the rendezvous) or
+ * after it.  All ranks should use the same value. */
+int moe_ep_set_timeout_ms(moe_layer_t*, int timeout_ms);
 
 /* Host-only helper (no CUDA, no NCCL): the row layout one rank uses for the dispatch and the
  * combine, from the all-gathered pair counts counts[world][num_experts].  send_off[E+1]: first

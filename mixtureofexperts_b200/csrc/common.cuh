@@ -19,6 +19,7 @@ enum : int32_t {
     DEV_TIMEOUT_TMEM_FULL = 3,   // epilogue waited too long for an accumulator
     DEV_TIMEOUT_TMEM_EMPTY = 4,  // MMA warp waited too long for a drained accumulator
     DEV_BAD_INDEX = 5,           // an index check failed (recorded, access skipped)
+    DEV_TIMEOUT_PEER = 6,        // expert parallel: a peer's flag (records, barrier) did not arrive in time
 };
 
 constexpr int ROUTER_THREADS = 256;
@@ -88,9 +89,12 @@ struct ScanParams {
     float* u_loss;
     int64_t* u_tokens_per_expert;
     float* u_entropy;
-    // expert-parallel: when non-null the loss is finished later from all ranks' sums
+    // chunked host calls: when non-null the loss is finished later from the chunks' sums
     float* ep_sums;           // [E + E_probs + 3]: counts, prob sums, sum lse^2, T, entropy sum
     int sums_accumulate;      // 1: add into ep_sums / u_tokens_per_expert (chunks of one batch) instead of storing
+    // expert-parallel: this rank's record of the call for the exchange with the other ranks,
+    // [E + E_probs + 3] words = {int32 counts[E], float prob sums[E_probs], float lse^2 sum, int32 T, float entropy sum}
+    int32_t* ep_record;
 };
 
 struct PermuteParams {
@@ -200,6 +204,8 @@ int launch_group_gemm_tc(const TcGemmPlan*, int stage, int mode, const GroupGemm
                          int num_sms, cudaStream_t s);
 int launch_group_gemm_tc2(const TcGemmPlan*, int stage, int mode, const GroupGemmParams& p, int max_tiles,
                           int num_sms, cudaStream_t s);
+// one thread waits limit_us on an mbarrier nobody arrives on; 0 on success, the recorded status and waited time out
+int run_bounded_wait_selftest(int limit_us, int32_t* status_out, int32_t* waited_us);
 
 __host__ __device__ inline float bf16_bits_to_float(uint16_t b) {
     union { uint32_t u; float f; } v;

@@ -1,6 +1,7 @@
 // Expert-parallel exchange: all-to-all dispatch and combine of token rows between the ranks of
-// one node over NCCL (NVLink 5 / NVSwitch).  The reference has no communication layer at all;
-// the oracle for this path is the single-device layer on the concatenated batch.
+// one node over NVLink 5 / NVSwitch (peer stores from this library's own kernels by default, NCCL
+// send/recv as the comparison mode).  The reference has no communication layer at all; the oracle
+// for this path is the single-device layer on the concatenated batch.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -8,6 +9,14 @@
 namespace moe {
 
 struct EpState;
+
+// Control block every rank exports to its peers (32-bit words): three rows of arrival flags
+// (slot 0: rows dispatched, slot 1: expert outputs returned, slot 2: routing records posted), then
+// two record tables (parity of the call number) with one record per rank.
+constexpr int EP_MAX_WORLD = 32;
+constexpr int EP_MAX_REC_WORDS = 272;     // >= num_experts + router rows + 3
+constexpr int EP_CTL_FLAG_WORDS = 128;    // >= 3 * EP_MAX_WORLD
+constexpr int EP_CTL_WORDS = EP_CTL_FLAG_WORDS + 2 * EP_MAX_WORLD * EP_MAX_REC_WORDS;
 
 struct EpConfig {
     int rank, world;
@@ -17,13 +26,11 @@ struct EpConfig {
     int tile_m;    // m-tile height of the grouped GEMM that will run on the received rows
     int tile_m_alt;  // second tile height the caller may choose per call (0 = none)
     float alpha, z_weight;
+    int32_t* status;   // the handle's device status word (bounded waits report DEV_TIMEOUT_PEER here)
 };
 
 struct EpCall {
     int64_t T;                     // local tokens
-    int training;
-    float* u_loss;                 // device, nullable
-    float* u_entropy;              // device, nullable
     const void* xs;                // [pairs][D] rows grouped by global expert (send layout)
     void* y_back;                  // [pairs][O] expert outputs returned in the send layout
     const int32_t* expert_count;   // device [E], local counts per global expert
@@ -42,25 +49,34 @@ typedef int (*EpRunFn)(void* self, const void* a_in, void* h_buf, void* y_buf, c
 // m-tile prefix (tile_m rows per tile).  Returns the number of rows this rank receives.
 int64_t ep_plan_layout(const int32_t* cnt, int W, int E, int me, int tile_m, int64_t* send_off, int64_t* recv_off,
                        int32_t* local_off, int32_t* tile_prefix);
-// Loss from summed statistics {counts[E], prob sums[E_probs], lse^2, T, entropy}: the Switch loss
-// (+ z-loss) over all the tokens the sums cover.  Used for all ranks' tokens (expert parallel) and
-// for all chunks of a chunked host call.
-int launch_finish_loss(const float* sums, int E, int E_probs, int k_tot, float alpha, float z_weight, int training,
-                       float* u_loss, float* u_entropy, cudaStream_t s);
+// Loss of a batch that was processed in chunks on one GPU, from the chunks' summed statistics:
+// sums = {unused[E], prob sums[E_probs], lse^2 sum, unused, entropy sum} (FP32), the per-expert pair
+// counts and T as integers, so that counts beyond 2^24 stay exact.
+int launch_finish_loss(const float* sums, const int64_t* counts, int64_t T, int E, int E_probs, int k_tot, float alpha,
+                       float z_weight, int training, float* u_loss, float* u_entropy, cudaStream_t s);
 int ep_unique_id(void* id128, char* err, size_t errlen);
-int ep_create(EpState** out, const EpConfig& cfg, const void* id128, char* err, size_t errlen);
+// Joins the group through a NON-BLOCKING NCCL communicator; the rendezvous is polled against
+// timeout_ms (<= 0: the default of 30 s).  Every later wait on a collective uses the same deadline
+// and ends in ncclCommAbort + MOE_ERR_TIMEOUT; after that the state refuses every call.
+int ep_create(EpState** out, const EpConfig& cfg, const void* id128, int timeout_ms, char* err, size_t errlen);
 void ep_destroy(EpState*);
-float* ep_sums_buffer(EpState*);   // device [E + E_probs + 3]: counts, prob sums, lse^2, T, entropy
-int ep_exchange_and_run(EpState*, const EpCall&, EpRunFn run, void* self, int64_t* launches, char* err,
-                        size_t errlen);
+int ep_set_timeout_ms(EpState*, int ms);
+// device [E + E_probs + 3] words: this rank's record of the call = {int32 pair counts[E], float prob
+// sums[E_probs], float lse^2 sum, int32 T, float entropy sum}; the scan kernel writes it
+int32_t* ep_record_buffer(EpState*);
+// nccl mode: records, dispatch, local experts (callback), combine
+int ep_exchange_and_run(EpState*, const EpCall&, EpRunFn run, void* self, char* err, size_t errlen);
 float ep_last_exchange_ms(EpState*);
+// all ranks' largest local token count (collective, bounded)
+int ep_max_tokens(EpState*, int64_t T_local, cudaStream_t s, int64_t* T_max, char* err, size_t errlen);
 
 // ---- peer-memory mode (default): rows cross NVLink inside the permute and combine kernels ----
 // Every rank exports its receive buffers with CUDA IPC; the permute kernel stores each row
 // straight into the owner GPU's buffer, and the GEMM 2 epilogue stores every output row straight into
 // the buffer of the GPU that owns the token, tile by tile while the GEMM runs; the combine kernel then
-// reads local memory only.  NCCL only carries the small control collectives (counts, the loss sums that
-// double as a barrier, one more barrier).  MOE_B200_EP_MODE=nccl selects the send/recv path above.
+// reads local memory only.  Counts, statistics and the two barriers of a call travel through the
+// exported control block (flag kernels with bounded waits); NCCL only carries the IPC handles when
+// buffers grow.  MOE_B200_EP_MODE=nccl selects the send/recv path above.
 struct EpPlan {
     int64_t rows;                     // rows this rank received
     int64_t rows_cap;                 // capacity (rows) of the receive buffers
@@ -77,15 +93,17 @@ struct EpPlan {
 };
 bool ep_peer_mode(const EpState*);
 int ep_world(const EpState*);
-// all-gather of the counts, host sync, layout, (collective) buffer growth, pointer tables
-int ep_prepare(EpState*, const int32_t* d_expert_count, cudaStream_t s, EpPlan* plan, char* err, size_t errlen);
-// all-reduce of the loss sums; completes only when every rank has issued it, i.e. after every
-// rank's permute kernel: the barrier between dispatch and the expert GEMMs
-int ep_sums_barrier(EpState*, cudaStream_t s, char* err, size_t errlen);
-// barrier between the expert GEMMs and the combine kernels that read peers' outputs
-int ep_barrier(EpState*, cudaStream_t s, char* err, size_t errlen);
-int ep_finish_loss(EpState*, int training, float* u_loss, float* u_entropy, cudaStream_t s, int64_t* launches,
-                   char* err, size_t errlen);
+// exchange of the records, host sync, layout, (collective) buffer growth, pointer tables
+int ep_prepare(EpState*, int64_t T_local, cudaStream_t s, EpPlan* plan, char* err, size_t errlen);
+// flag barrier over all ranks (one small kernel, bounded wait).  slot 0: after the permute kernel,
+// "every rank's rows for my experts have landed"; slot 1: after GEMM 2, "the outputs of all my
+// pairs have landed"
+int ep_barrier(EpState*, int slot, cudaStream_t s, char* err, size_t errlen);
+// Switch loss (+ z-loss) and entropy over all ranks' tokens from the gathered records.  chunk_mode:
+// 0 = the call is a whole batch; 1 / 2 / 3 = first / middle / last chunk of a chunked host call
+// (running totals are kept between the chunks, the last one writes the result)
+int ep_finish_loss(EpState*, int training, int chunk_mode, float* u_loss, float* u_entropy, cudaStream_t s,
+                   int64_t* launches, char* err, size_t errlen);
 void ep_mark(EpState*, int i, cudaStream_t s);   // timing marks 0..3 around the two exchanges
 
 }  // namespace moe

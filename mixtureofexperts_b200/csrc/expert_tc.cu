@@ -251,6 +251,20 @@ group_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
 }
 
+// One thread waits, with a limit, on an mbarrier that nobody arrives on: the give-up path of
+// tc::mbar_wait, exercised without a GEMM around it.
+__global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns, int32_t* status, int32_t* waited_us) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const unsigned long long t0 = globaltimer_ns();
+    const bool ok = mbar_wait(&bar, 0, &abort_flag, status, DEV_TIMEOUT_TMA_FULL, limit_ns);
+    const unsigned long long dt = globaltimer_ns() - t0;
+    *waited_us = ok ? -1 : (int32_t)(dt / 1000ull);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -293,6 +307,21 @@ int group_m_setting() {
     // 32 m-tiles per group: measured best under sustained load (4: -11 %, 8: -4 %, 16: -1 %); a
     // group then covers a whole expert of the Mixtral-shaped workload, so its weights are read once
     return gm_env > 0 ? gm_env : 32;
+}
+
+int run_bounded_wait_selftest(int limit_us, int32_t* status_out, int32_t* waited_us) {
+    int32_t* d = nullptr;
+    if (cudaMalloc(&d, 2 * sizeof(int32_t)) != cudaSuccess) return -1;
+    cudaMemset(d, 0, 2 * sizeof(int32_t));
+    bounded_wait_selftest_kernel<<<1, 1>>>((unsigned long long)limit_us * 1000ull, d, d + 1);
+    int32_t h[2] = {0, 0};
+    const bool ok = cudaGetLastError() == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess &&
+                    cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess;
+    cudaFree(d);
+    if (!ok) return -1;
+    *status_out = h[0];
+    *waited_us = h[1];
+    return 0;
 }
 
 TcGemmPlan* tc_plan_create() { return new TcGemmPlan(); }

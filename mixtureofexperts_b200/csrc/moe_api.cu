@@ -4,6 +4,7 @@
 // that replaces (moe::MoELayer)(x; training) (src/core/moe_layer.jl:107-156) and
 // cuda_moe_forward! (src/cuda/layer.jl:3-32).  No CPU fallback exists in this file: every
 // compute entry point fails with MOE_ERR_CUDA when the device is unusable.
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -134,6 +135,12 @@ struct moe_layer {
     int64_t launches = 0;
 
     EpState* ep = nullptr;
+    int ep_timeout_ms = 0;          // moe_ep_set_timeout_ms before moe_ep_init; 0 = default
+
+    // experiment switches of the environment, read once when the handle is created
+    int force_pair = -1;            // MOE_B200_PAIR = 0 / 1: force single-CTA / CTA-pair GEMM kernels
+    int host_chunks = 0;            // MOE_B200_HOST_CHUNKS = n: n equal chunks per large host call
+    bool host_timeline = false;     // MOE_B200_HOST_TIMELINE = 1: print every chunk's copy/compute times
 };
 
 namespace {
@@ -282,8 +289,7 @@ int check_ready(moe_layer* L) {
 // forces the choice.
 int pick_tile_m(const moe_layer* L, int64_t rows, int n_experts) {
     if (L->cfg.compute_dtype != MOE_DTYPE_BF16) return F32_TILE_M;
-    const char* ev = getenv("MOE_B200_PAIR");   // read per call: tests switch it at run time
-    const int env_pair = ev ? atoi(ev) : -1;
+    const int env_pair = L->force_pair;
     bool pair;
     if (env_pair >= 0) {
         pair = env_pair > 0;
@@ -353,11 +359,21 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     return MOE_OK;
 }
 
-// partial_sums != null: this call covers one chunk of a larger batch; the scan kernel leaves its
-// statistics there and the caller finishes loss and entropy from the sum over chunks.
+// A call that covers one chunk of a larger host batch.  Without expert parallelism the scan kernel adds
+// its statistics into `sums` and the caller finishes loss and entropy from the total; with expert
+// parallelism the records of every chunk are exchanged anyway and the running totals live in the EP
+// state (ep_mode: 1 first, 2 middle, 3 last chunk).
+struct ChunkCtx {
+    float* sums = nullptr;
+    int want_entropy = 0;
+    int ep_mode = 0;
+};
+
 int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int training, float* out,
-                   const moe_forward_outputs_t* opt, cudaStream_t s, float* partial_sums = nullptr,
-                   int partial_want_entropy = 0) {
+                   const moe_forward_outputs_t* opt, cudaStream_t s, const ChunkCtx* chunk = nullptr) {
+    float* partial_sums = chunk ? chunk->sums : nullptr;
+    const int partial_want_entropy = chunk ? chunk->want_entropy : 0;
+    const bool chunked = chunk != nullptr;
     const moe_config_t& c = L->cfg;
     static const moe_forward_outputs_t none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     if (!opt) opt = &none;
@@ -449,11 +465,12 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     sp.expert_offset = L->expert_offset;
     sp.tile_prefix = L->tile_prefix;
     sp.loss_internal = L->loss_dev;
-    sp.u_loss = (L->ep || partial_sums) ? nullptr : opt->loss;
+    sp.u_loss = (L->ep || chunked) ? nullptr : opt->loss;
     sp.u_tokens_per_expert = opt->tokens_per_expert;
-    sp.u_entropy = (L->ep || partial_sums) ? nullptr : opt->routing_entropy;
-    sp.ep_sums = L->ep ? ep_sums_buffer(L->ep) : partial_sums;
-    sp.sums_accumulate = (!L->ep && partial_sums) ? 1 : 0;
+    sp.u_entropy = (L->ep || chunked) ? nullptr : opt->routing_entropy;
+    sp.ep_sums = L->ep ? nullptr : partial_sums;
+    sp.sums_accumulate = chunked ? 1 : 0;
+    sp.ep_record = L->ep ? ep_record_buffer(L->ep) : nullptr;
     n = launch_scan(sp, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "scan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
@@ -485,7 +502,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     EpPlan plan;
     const int ep_tile_m = L->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M;
     if (peer) {
-        if ((rc = ep_prepare(L->ep, L->expert_count, s, &plan, g_err, sizeof(g_err)))) return rc;
+        if ((rc = ep_prepare(L->ep, T, s, &plan, g_err, sizeof(g_err)))) return rc;
         pp.expert_dst = plan.d_expert_dst;
         ep_mark(L->ep, 0, s);
     }
@@ -500,9 +517,9 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
         if ((rc = run_experts(L, L->xp, L->h, L->y, L->expert_offset, L->tile_prefix, T * L->k_tot, L->E, s, 4, tile_m_local)))
             return rc;
     } else if (peer) {
-        // every rank's permute kernel has written its rows into the owners' buffers once the
-        // all-reduce of the loss sums completes
-        if ((rc = ep_sums_barrier(L->ep, s, g_err, sizeof(g_err)))) return rc;
+        // flag barrier: every rank's permute kernel has written its rows into the owners' buffers
+        if ((rc = ep_barrier(L->ep, 0, s, g_err, sizeof(g_err)))) return rc;
+        L->launches += 1;
         ep_mark(L->ep, 1, s);
         if ((rc = ensure_plan(L, plan.xr, plan.hr, plan.rows_cap))) return rc;
         const int n_local = L->e_hi - L->e_lo;
@@ -513,19 +530,16 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
             return rc;
         ep_mark(L->ep, 2, s);
         // every rank's GEMM 2 has stored its rows into the token owners' buffers before anybody combines
-        if ((rc = ep_barrier(L->ep, s, g_err, sizeof(g_err)))) return rc;
+        if ((rc = ep_barrier(L->ep, 1, s, g_err, sizeof(g_err)))) return rc;
+        L->launches += 1;
     } else {
         EpCall call;
         call.T = T;
-        call.training = training;
-        call.u_loss = opt->loss;
-        call.u_entropy = opt->routing_entropy;
         call.xs = L->xp;
         call.y_back = L->y;
         call.expert_count = L->expert_count;
         call.expert_offset = L->expert_offset;
         call.stream = s;
-        int64_t ep_launches = 0;
         rc = ep_exchange_and_run(
             L->ep, call,
             [](void* self, const void* a_in, void* h_buf, void* y_buf, const int32_t* eo, const int32_t* tp,
@@ -536,8 +550,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
                 return run_experts(M, a_in, h_buf, y_buf, eo, tp, rows, n_exp, st, 4,
                                    M->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M);
             },
-            L, &ep_launches, g_err, sizeof(g_err));
-        L->launches += ep_launches;
+            L, g_err, sizeof(g_err));
         if (rc) return rc;
     }
 
@@ -556,7 +569,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     stage_mark(L, 6, s);
     // compute_loss(::AuxiliaryFreeLoss) first updates the bias the next call selects with
     // (src/balancing/auxiliary_free.jl:73-83); partial (chunked) calls are updated by their caller
-    if (L->aux_free && training && !partial_sums) {
+    if (L->aux_free && training && !chunked) {
         ++L->aux_counter;
         if (L->aux_counter % L->aux_freq == 0) {
             n = launch_aux_free_update(L->expert_count, L->E_router, L->router_bias, L->bias_momentum, L->aux_lr,
@@ -565,9 +578,10 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
             L->launches += n;
         }
     }
-    if (peer) {
-        ep_mark(L->ep, 3, s);
-        if ((rc = ep_finish_loss(L->ep, training, opt->loss, opt->routing_entropy, s, &L->launches, g_err, sizeof(g_err))))
+    if (L->ep) {
+        if (peer) ep_mark(L->ep, 3, s);
+        if ((rc = ep_finish_loss(L->ep, training, chunk ? chunk->ep_mode : 0, opt->loss, opt->routing_entropy, s, &L->launches,
+                                 g_err, sizeof(g_err))))
             return rc;
     }
     return MOE_OK;
@@ -618,6 +632,9 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     L->E_probs = L->E_router;
     L->e_lo = 0;
     L->e_hi = L->E;
+    if (const char* ev = getenv("MOE_B200_PAIR")) L->force_pair = atoi(ev) > 0 ? 1 : 0;
+    if (const char* ev = getenv("MOE_B200_HOST_CHUNKS")) L->host_chunks = atoi(ev) > 0 ? atoi(ev) : 0;
+    if (const char* ev = getenv("MOE_B200_HOST_TIMELINE")) L->host_timeline = atoi(ev) > 0;
     auto cleanup = [&](int code) {
         moe_layer_destroy(L);
         return code;
@@ -1086,10 +1103,13 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     int nchunks = 1;
     int env_chunks = 0;   // MOE_B200_HOST_CHUNKS = n: n equal chunks (1 = off); unset: the default schedule
     // (not with the capacity constraint, whose capacity and first-come order span the whole batch)
-    if (!L->ep && L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T >= 8192 && !(L->cfg.drop_tokens && training) &&
+    // With expert parallelism every chunk is a collective, so all ranks must cut alike: they decide from
+    // the largest batch of any rank and every rank makes the same number of chunks (empty ones included).
+    int64_t T_rule = T;
+    if (L->ep && (rc = ep_max_tokens(L->ep, T, s, &T_rule, g_err, sizeof(g_err)))) return rc;
+    if (L->cfg.shared_mode != MOE_SHARED_LAYER_BLEND && T_rule >= 8192 && !(L->cfg.drop_tokens && training) &&
         !(L->noise && training) && !(L->aux_free && training)) {
-        const char* e = getenv("MOE_B200_HOST_CHUNKS");
-        env_chunks = e ? atoi(e) : 0;
+        env_chunks = L->host_chunks;
         nchunks = env_chunks > 0 ? env_chunks : 5;
         if (nchunks > moe_layer::MAX_CHUNKS) nchunks = moe_layer::MAX_CHUNKS;
     }
@@ -1098,8 +1118,7 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         if (!L->s_in) {
             CUDA_TRY(cudaStreamCreateWithFlags(&L->s_in, cudaStreamNonBlocking));
             CUDA_TRY(cudaStreamCreateWithFlags(&L->s_out, cudaStreamNonBlocking));
-            const char* tl = getenv("MOE_B200_HOST_TIMELINE");
-            L->timeline = tl && atoi(tl) > 0;
+            L->timeline = L->host_timeline;
             const unsigned ev_flags = L->timeline ? cudaEventDefault : cudaEventDisableTiming;
             for (auto& e : L->ev_in) CUDA_TRY(cudaEventCreateWithFlags(&e, ev_flags));
             for (auto& e : L->ev_done) CUDA_TRY(cudaEventCreateWithFlags(&e, ev_flags));
@@ -1117,18 +1136,22 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         bounds.push_back(0);
         if (env_chunks > 0) {
             const int64_t Tc = ((T + nchunks - 1) / nchunks + 63) / 64 * 64;
-            for (int64_t t = Tc; t < T; t += Tc) bounds.push_back(t);
+            for (int c = 1; c < nchunks; ++c) {
+                const int64_t t = std::min<int64_t>(T, c * Tc);
+                if (L->ep || (t > bounds.back() && t < T)) bounds.push_back(t);
+            }
         } else {
             static const int parts[] = {1, 5, 5, 4, 1};     // sixteenths of the batch
             nchunks = 5;
             int64_t acc16 = 0;
             for (int i = 0; i < 4; ++i) {
                 acc16 += parts[i];
-                const int64_t t = (T * acc16 / 16 + 63) / 64 * 64;
-                if (t > bounds.back() && t < T) bounds.push_back(t);
+                const int64_t t = std::min<int64_t>(T, (T * acc16 / 16 + 63) / 64 * 64);
+                if (L->ep || (t > bounds.back() && t < T)) bounds.push_back(t);
             }
         }
         bounds.push_back(T);
+        const int n_bounds = (int)bounds.size();
         const size_t xrow = (size_t)L->cfg.input_dim * dtype_size(x_dtype), orow = (size_t)L->cfg.output_dim * 4;
         CUDA_TRY(cudaMemsetAsync(L->chunk_acc, 0, sizeof(float) * nsum, s));
         CUDA_TRY(cudaMemsetAsync(L->chunk_tpe_acc, 0, sizeof(int64_t) * L->E, s));
@@ -1137,8 +1160,9 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
             const int64_t t0 = bounds[c];
             const int64_t n = bounds[c + 1] - t0;
             if (L->timeline) CUDA_TRY(cudaEventRecord(L->ev_in0[c], L->s_in));
-            CUDA_TRY(cudaMemcpyAsync((char*)L->hx + t0 * xrow, (const char*)x + t0 * xrow, n * xrow,
-                                     cudaMemcpyHostToDevice, L->s_in));
+            if (n > 0)
+                CUDA_TRY(cudaMemcpyAsync((char*)L->hx + t0 * xrow, (const char*)x + t0 * xrow, n * xrow,
+                                         cudaMemcpyHostToDevice, L->s_in));
             CUDA_TRY(cudaEventRecord(L->ev_in[c], L->s_in));
             CUDA_TRY(cudaStreamWaitEvent(s, L->ev_in[c], 0));
             moe_forward_outputs_t dc = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -1147,23 +1171,36 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
             if (d.probs) dc.probs = d.probs + t0 * ep;
             if (d.logits) dc.logits = d.logits + t0 * er;
             dc.tokens_per_expert = L->chunk_tpe_acc;       // the scan kernel adds every chunk's sums in place
+            dc.loss = d.loss;                              // written by the last chunk only (expert parallel)
+            dc.routing_entropy = d.routing_entropy;
+            ChunkCtx cc;
+            cc.sums = L->chunk_acc;
+            cc.want_entropy = d.routing_entropy != nullptr;
+            cc.ep_mode = c == 0 ? 1 : (c + 2 == n_bounds ? 3 : 2);
             if ((rc = forward_device(L, (char*)L->hx + t0 * xrow, x_dtype, n, training, L->hout + t0 * L->cfg.output_dim,
-                                     &dc, s, L->chunk_acc, d.routing_entropy != nullptr)))
+                                     &dc, s, &cc)))
                 return rc;
             CUDA_TRY(cudaEventRecord(L->ev_done[c], s));
             CUDA_TRY(cudaStreamWaitEvent(L->s_out, L->ev_done[c], 0));
-            CUDA_TRY(cudaMemcpyAsync((char*)out + t0 * orow, (char*)L->hout + t0 * orow, n * orow, cudaMemcpyDeviceToHost,
-                                     L->s_out));
+            if (n > 0)
+                CUDA_TRY(cudaMemcpyAsync((char*)out + t0 * orow, (char*)L->hout + t0 * orow, n * orow, cudaMemcpyDeviceToHost,
+                                         L->s_out));
+            if (n == 0) {
+                if (L->timeline) CUDA_TRY(cudaEventRecord(L->ev_out1[c], L->s_out));
+                continue;
+            }
             if (d.indices) CUDA_TRY(cudaMemcpyAsync(opt->indices + t0 * ku, dc.indices, (size_t)n * ku * 4, cudaMemcpyDeviceToHost, L->s_out));
             if (d.gates) CUDA_TRY(cudaMemcpyAsync(opt->gates + t0 * ku, dc.gates, (size_t)n * ku * 4, cudaMemcpyDeviceToHost, L->s_out));
             if (d.probs) CUDA_TRY(cudaMemcpyAsync(opt->probs + t0 * ep, dc.probs, (size_t)n * ep * 4, cudaMemcpyDeviceToHost, L->s_out));
             if (d.logits) CUDA_TRY(cudaMemcpyAsync(opt->logits + t0 * er, dc.logits, (size_t)n * er * 4, cudaMemcpyDeviceToHost, L->s_out));
             if (L->timeline) CUDA_TRY(cudaEventRecord(L->ev_out1[c], L->s_out));
         }
-        if (launch_finish_loss(L->chunk_acc, L->E, L->E_probs, L->k_tot, L->cfg.balance_alpha, L->cfg.z_loss_weight,
-                               training, d.loss, d.routing_entropy, s) < 0)
-            return fail(MOE_ERR_CUDA, "loss launch failed");
-        L->launches += 1;
+        if (!L->ep) {
+            if (launch_finish_loss(L->chunk_acc, L->chunk_tpe_acc, T, L->E, L->E_probs, L->k_tot, L->cfg.balance_alpha,
+                                   L->cfg.z_loss_weight, training, d.loss, d.routing_entropy, s) < 0)
+                return fail(MOE_ERR_CUDA, "loss launch failed");
+            L->launches += 1;
+        }
         if (d.loss) CUDA_TRY(cudaMemcpyAsync(opt->loss, d.loss, 4, cudaMemcpyDeviceToHost, s));
         if (d.tokens_per_expert)
             CUDA_TRY(cudaMemcpyAsync(opt->tokens_per_expert, L->chunk_tpe_acc, (size_t)L->E * 8, cudaMemcpyDeviceToHost, s));
@@ -1307,6 +1344,15 @@ int moe_layer_device_status(moe_layer_t* L, int32_t* status) {
     return MOE_OK;
 }
 
+int moe_selftest_bounded_wait(int device, int limit_us, int32_t* status_out, int32_t* waited_us) {
+    if (!status_out || !waited_us) return fail(MOE_ERR_INVALID, "null argument");
+    if (limit_us < 1 || limit_us > 1000000) return fail(MOE_ERR_INVALID, "limit_us must be in 1..1000000");
+    CUDA_TRY(cudaSetDevice(device));
+    if (run_bounded_wait_selftest(limit_us, status_out, waited_us) != 0)
+        return fail(MOE_ERR_CUDA, "bounded-wait self-test failed to run: %s", cudaGetErrorString(cudaGetLastError()));
+    return MOE_OK;
+}
+
 int moe_ep_unique_id(void* id128) { return ep_unique_id(id128, g_err, sizeof(g_err)); }
 
 int64_t moe_ep_layout(const int32_t* counts, int world, int num_experts, int rank, int tile_m, int64_t* send_off,
@@ -1316,6 +1362,14 @@ int64_t moe_ep_layout(const int32_t* counts, int world, int num_experts, int ran
     if (world < 1 || rank < 0 || rank >= world || num_experts < 1 || num_experts % world || tile_m < 1)
         return fail(MOE_ERR_INVALID, "bad world/rank/num_experts/tile_m");
     return ep_plan_layout(counts, world, num_experts, rank, tile_m, send_off, recv_off, local_off, tile_prefix);
+}
+
+int moe_ep_set_timeout_ms(moe_layer_t* L, int timeout_ms) {
+    if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    if (timeout_ms < 1) return fail(MOE_ERR_INVALID, "timeout_ms must be positive");
+    L->ep_timeout_ms = timeout_ms;
+    if (L->ep) return ep_set_timeout_ms(L->ep, timeout_ms);
+    return MOE_OK;
 }
 
 int moe_ep_init(moe_layer_t* L, const void* id128, int rank, int world) {
@@ -1341,7 +1395,8 @@ int moe_ep_init(moe_layer_t* L, const void* id128, int rank, int world) {
     ec.tile_m_alt = L->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_PAIR_TILE_M : 0;
     ec.alpha = L->cfg.balance_alpha;
     ec.z_weight = L->cfg.z_loss_weight;
-    const int rc = ep_create(&L->ep, ec, id128, g_err, sizeof(g_err));
+    ec.status = L->status;
+    const int rc = ep_create(&L->ep, ec, id128, L->ep_timeout_ms, g_err, sizeof(g_err));
     if (rc) return rc;
     const int per = L->E / world;
     L->e_lo = rank * per;

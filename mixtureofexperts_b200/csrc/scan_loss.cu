@@ -99,6 +99,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_loss_kernel(const ScanParam
         }
     }
 
+    if (p.ep_record) {
+        for (int e = threadIdx.x; e < p.E; e += SCAN_THREADS) p.ep_record[e] = s_count[e];
+        for (int e = threadIdx.x; e <= p.E_probs; e += SCAN_THREADS) p.ep_record[p.E + e] = __float_as_int(s_psum[e]);
+        if (threadIdx.x == 0) {
+            p.ep_record[p.E + p.E_probs + 1] = (int32_t)p.T;
+            p.ep_record[p.E + p.E_probs + 2] = __float_as_int((float)s_ent);
+        }
+    }
+
     // (iii) loss = alpha * N * sum_i f_i P_i  (+ z_weight * mean lse^2), one warp
     if (warp == 0) {
         float acc = 0.f;

@@ -56,3 +56,30 @@ def exchange_layout(counts, rank: int, tile_m: int):
     if rows < 0:
         _lib.check(int(rows))
     return send_off, recv_off, local_off, tile_prefix, int(rows)
+
+
+def all_gather_counts(dist, counts, rank: int, timeout_s: float = 30.0):
+    """All-gather of the per-expert pair counts over the default torch.distributed group for callers
+    that run the exchange themselves (the library's own forward exchanges them on the device).
+    Bounded like the library's collectives: a rank that never posts its counts ends the wait with
+    MoEError(ERR_TIMEOUT) after ``timeout_s`` instead of hanging, and a gathered table whose own
+    row differs from what this rank posted, or that holds a negative count, raises
+    MoEError(ERR_NCCL).  Returns ``counts[world][E]`` (int32)."""
+    import datetime
+
+    import torch
+
+    mine = torch.from_numpy(np.ascontiguousarray(counts, dtype=np.int32))
+    world = dist.get_world_size()
+    gathered = [torch.zeros_like(mine) for _ in range(world)]
+    try:
+        work = dist.all_gather(gathered, mine, async_op=True)
+        done = work.wait(timeout=datetime.timedelta(seconds=timeout_s))
+    except Exception as exc:  # noqa: BLE001  (gloo reports a missing peer as a RuntimeError)
+        raise _lib.MoEError(_lib.ERR_TIMEOUT, f"a rank did not post its routing counts within {timeout_s} s: {exc}") from None
+    if done is False:
+        raise _lib.MoEError(_lib.ERR_TIMEOUT, f"a rank did not post its routing counts within {timeout_s} s")
+    cnt = np.stack([g.numpy() for g in gathered]).astype(np.int32)
+    if not np.array_equal(cnt[rank], mine.numpy()) or (cnt < 0).any():
+        raise _lib.MoEError(_lib.ERR_NCCL, "the gathered routing counts do not match this rank's own (corrupted exchange)")
+    return cnt

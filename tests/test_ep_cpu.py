@@ -54,9 +54,7 @@ def _rank_main(rank, world, port, E, k, T, D, H, O, tile_m, q):
         per = len(mine)
 
         counts = np.bincount(idx.ravel() - 1, minlength=E).astype(np.int32)
-        gathered = [torch.zeros(E, dtype=torch.int32) for _ in range(world)]
-        dist.all_gather(gathered, torch.from_numpy(counts))
-        cnt = np.stack([g.numpy() for g in gathered])
+        cnt = parallel.all_gather_counts(dist, counts, rank, timeout_s=60.0)
         send_off, recv_off, local_off, tile_prefix, rows = parallel.exchange_layout(cnt, rank, tile_m)
         assert rows == cnt[:, mine.start:mine.stop].sum()
         assert tile_prefix[-1] == sum((cnt[:, e].sum() + tile_m - 1) // tile_m for e in mine)
@@ -147,3 +145,113 @@ def test_layout_of_a_hand_checked_case(lib_built):
     assert tp.tolist() == [0, 1, 3]
     with pytest.raises(Exception):
         parallel.exchange_layout(np.zeros((3, 4), dtype=np.int32), 0, 2)  # 4 experts over 3 ranks
+
+
+def test_layout_rejects_count_vectors_that_no_router_produced(lib_built):
+    """moe_ep_layout is what every rank runs on the gathered counts: a negative count, or more rows
+    than an int32 row index can address, must be refused (the forward then fails on every rank
+    alike, because all ranks look at the same table)."""
+    from mixtureofexperts_b200 import _lib, parallel
+
+    bad = np.array([[3, 0, 2, 1], [1, -4, 0, 2]], dtype=np.int32)
+    with pytest.raises(_lib.MoEError) as ei:
+        parallel.exchange_layout(bad, 0, 2)
+    assert ei.value.code == _lib.ERR_INVALID
+    huge = np.full((2, 4), 2**30, dtype=np.int32)
+    with pytest.raises(_lib.MoEError) as ei:
+        parallel.exchange_layout(huge, 1, 128)
+    assert ei.value.code == _lib.ERR_UNSUPPORTED
+
+
+def _absent_rank_main(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    import time
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        from mixtureofexperts_b200 import _lib, parallel
+
+        counts = np.arange(8, dtype=np.int32) + rank
+        cnt = parallel.all_gather_counts(dist, counts, rank, timeout_s=30.0)       # everybody posts: fine
+        assert cnt.shape == (world, 8) and np.array_equal(cnt[rank], counts)
+        if rank == 0:
+            t0 = time.perf_counter()
+            try:
+                parallel.all_gather_counts(dist, counts, rank, timeout_s=1.5)       # rank 1 stays away
+                q.put((rank, "no error", 0.0))
+            except _lib.MoEError as exc:
+                q.put((rank, exc.code, time.perf_counter() - t0))
+        else:
+            time.sleep(4.0)                                                          # never posts its counts
+            q.put((rank, "absent", 0.0))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001  (the group is broken on purpose)
+            pass
+
+
+def test_a_rank_that_never_posts_its_counts_costs_a_timeout_not_a_hang(lib_built):
+    from mixtureofexperts_b200 import _lib
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 500) + 11
+    procs = [ctx.Process(target=_absent_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode is not None, "a rank is still waiting"
+    results = dict((r[0], r[1:]) for r in (q.get(timeout=5) for _ in range(2)))
+    code, waited = results[0]
+    assert code == _lib.ERR_TIMEOUT and waited < 30.0
+    assert results[1][0] == "absent"
+
+
+def _disagree_main(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mixtureofexperts_b200 import _lib, parallel
+
+        counts = np.array([2, 1, 0, 3], dtype=np.int32)
+        # rank 1's transport hands back a table whose own row is not what it posted
+        class Tampering:
+            def get_world_size(self):
+                return dist.get_world_size()
+
+            def all_gather(self, out, t, async_op=False):
+                w = dist.all_gather(out, t, async_op=async_op)
+                if rank == 1:
+                    if w is not None:
+                        w.wait()
+                    out[1][0] += 5
+                return w
+
+        try:
+            parallel.all_gather_counts(Tampering(), counts, rank, timeout_s=30.0)
+            q.put((rank, "ok"))
+        except _lib.MoEError as exc:
+            q.put((rank, exc.code))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_count_vectors_that_disagree_with_what_was_posted_are_refused(lib_built):
+    from mixtureofexperts_b200 import _lib
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 500) + 17
+    procs = [ctx.Process(target=_disagree_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    results = dict(q.get(timeout=5) for _ in range(2))
+    assert results[0] == "ok" and results[1] == _lib.ERR_NCCL
