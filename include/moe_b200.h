@@ -34,6 +34,8 @@
  *   MOE_B200_HOST_TIMELINE=1   print every chunk's copy and compute times to stderr
  *   MOE_B200_GROUP_M=n         m-tiles per group of the GEMM tile order (default 32)
  *   MOE_B200_ROUTER_TILE=16|32|64   force the token tile of the router and permute kernels
+ *   MOE_B200_ROUTER_TC=0       keep the FP32-FMA router kernel for wide routers too (comparison; read at
+ *                              handle creation)
  *   MOE_B200_EP_MODE=nccl      expert parallelism moves token rows with ncclSend/ncclRecv instead of
  *                              peer stores from the library's own kernels (read by moe_ep_init)
  */
@@ -244,6 +246,13 @@ int moe_layer_tile_rows(moe_layer_t*, int64_t T);
 
 /* Number of kernel launches of this library issued through the handle since creation. */
 int64_t moe_layer_launch_count(const moe_layer_t*);
+
+/* Routers with 33..80 rows fed BF16 activations run their gate GEMM on the tensor cores (an exact
+ * three-way BF16 split of the FP32 router matrix, FP32 accumulation) and re-evaluate with FP32 FMAs
+ * every token whose top-(k+1) ranking has two neighbours closer than 1e-4 * max(1, |logit|).  *tokens
+ * receives how many tokens were re-evaluated through this handle since creation (0 for layers
+ * that never take that path).  A diagnostic without counterpart in the reference; synchronises. */
+int moe_layer_router_rechecks(moe_layer_t*, int64_t* tokens);
 
 /* Value of the device status word after the last synchronising call (0 = clean). */
 int moe_layer_device_status(moe_layer_t*, int32_t* status);

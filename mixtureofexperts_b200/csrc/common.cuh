@@ -68,6 +68,10 @@ struct RouterParams {
     float* u_gate;
     float* u_probs;
     float* u_logits;
+    // tensor-core router (router_tc.cu): scratch for the logits [T][E_PAD] and a counter of the tokens
+    // whose logits were re-evaluated with FP32 FMAs; null = not available to this call
+    float* tc_logits = nullptr;
+    int32_t* tc_recheck_count = nullptr;
 };
 
 struct ScanParams {
@@ -190,6 +194,18 @@ int launch_loss_only(float alpha, float z_weight, int n_probs, int k, int index_
                      cudaStream_t s);
 int launch_transpose_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int rows_out,
                              int cols_out, int src_is_transposed, cudaStream_t s);
+
+// tensor-core router for wide gates and BF16 activations (router_tc.cu)
+struct RouterTcPlan;
+RouterTcPlan* router_tc_plan_create();
+void router_tc_plan_destroy(RouterTcPlan*);
+int router_tc_e_pad(int e_router);       // padded router width of the tensor-core path, 0 = not offered for this width
+// splits w (FP32 [E_router][D]) into w3 (BF16 [3*e_pad][D]) and encodes its tensor map; 1 = ready, 0 = not offered, <0 error
+int router_tc_plan_set(RouterTcPlan*, const float* w, void* w3, int e_router, int D, cudaStream_t s);
+bool router_tc_usable(const RouterTcPlan*, const RouterParams& p, int x_dtype);
+int launch_router_tc(const RouterTcPlan*, const RouterParams& p, int num_cta, int num_sms, int32_t* status, cudaStream_t s);
+// K-major BF16 matrix [rows][K] as a 2-D tensor map with boxes of 64 x box_rows and 128-byte swizzle
+bool tc_encode_bf16_2d(void* map, const void* base, uint64_t K, uint64_t rows, uint32_t box_rows);
 
 // tcgen05 path (expert_tc.cu)
 struct TcGemmPlan;  // tensor maps + geometry, owned by the handle

@@ -73,6 +73,12 @@ struct moe_layer {
     float* router_wt_noise = nullptr;  // [D_pad][e_pad(2 E_router)]: router columns, then noise-network columns
     float* router_bias = nullptr;
     bool has_bias = false, router_set = false;
+    // tensor-core router (wide gates, BF16 activations): split router matrix, its plan, scratch
+    RouterTcPlan* rplan = nullptr;
+    void* router_w3 = nullptr;      // BF16 [3*e_pad][D]: hi, mid, lo parts of router_w
+    float* tc_logits = nullptr;     // workspace [T_cap][e_pad]
+    int32_t* tc_recheck = nullptr;  // tokens re-evaluated with FP32 FMAs since creation
+    bool router_tc_enabled = true;  // MOE_B200_ROUTER_TC=0 keeps the FP32-FMA router (comparison)
     // AuxiliaryFreeLoss.update_bias! on the device (moe_layer_set_aux_free)
     bool aux_free = false;
     float aux_lr = 0.f, aux_momentum = 0.f;
@@ -215,6 +221,7 @@ void free_workspace(moe_layer* L) {
     dev_free(L->xp);
     dev_free(L->h);
     dev_free(L->y);
+    dev_free(L->tc_logits);
     L->T_cap = 0;
     L->P_cap = 0;
 }
@@ -235,6 +242,7 @@ int ensure_workspace(moe_layer* L, int64_t T) {
     if ((rc = dev_alloc(&L->cta_counts, (size_t)num_cta * L->E))) return rc;
     if ((rc = dev_alloc(&L->cta_psum, (size_t)num_cta * (L->E_probs + 1)))) return rc;
     if ((rc = dev_alloc(&L->cta_entropy, (size_t)num_cta))) return rc;
+    if (L->rplan && (rc = dev_alloc(&L->tc_logits, (size_t)T * router_tc_e_pad(L->E_router)))) return rc;
     const bool peer = L->ep && ep_peer_mode(L->ep);
     if (!peer) {
         // (in peer mode rows go straight into the owners' receive buffers and come back from them)
@@ -432,9 +440,14 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     r.u_gate = opt->gates;
     r.u_probs = opt->probs;
     r.u_logits = opt->logits;
+    r.tc_logits = L->tc_logits;
+    r.tc_recheck_count = L->tc_recheck;
     int n = 0;
     if (num_cta > 0) {
-        n = launch_router(r, x_dtype, num_cta, L->num_sms, s);
+        if (L->router_tc_enabled && router_tc_usable(L->rplan, r, x_dtype))
+            n = launch_router_tc(L->rplan, r, num_cta, L->num_sms, L->status, s);
+        else
+            n = launch_router(r, x_dtype, num_cta, L->num_sms, s);
         if (n < 0) return fail(MOE_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         L->launches += n;
     }
@@ -635,6 +648,7 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     if (const char* ev = getenv("MOE_B200_PAIR")) L->force_pair = atoi(ev) > 0 ? 1 : 0;
     if (const char* ev = getenv("MOE_B200_HOST_CHUNKS")) L->host_chunks = atoi(ev) > 0 ? atoi(ev) : 0;
     if (const char* ev = getenv("MOE_B200_HOST_TIMELINE")) L->host_timeline = atoi(ev) > 0;
+    if (const char* ev = getenv("MOE_B200_ROUTER_TC")) L->router_tc_enabled = atoi(ev) != 0;
     auto cleanup = [&](int code) {
         moe_layer_destroy(L);
         return code;
@@ -647,6 +661,13 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     if ((rc = dev_alloc(&L->tile_prefix, (size_t)L->E + 1))) return cleanup(rc);
     if ((rc = dev_alloc(&L->loss_dev, 1))) return cleanup(rc);
     if ((rc = dev_alloc(&L->status, 1))) return cleanup(rc);
+    if (router_tc_e_pad(L->E_router) && cfg->input_dim % 8 == 0) {
+        L->rplan = router_tc_plan_create();
+        if (cudaMalloc(&L->router_w3, (size_t)3 * router_tc_e_pad(L->E_router) * cfg->input_dim * 2) != cudaSuccess)
+            return cleanup(fail(MOE_ERR_CUDA, "cudaMalloc failed"));
+        if ((rc = dev_alloc(&L->tc_recheck, 1))) return cleanup(rc);
+        if (cudaMemset(L->tc_recheck, 0, sizeof(int32_t)) != cudaSuccess) return cleanup(fail(MOE_ERR_CUDA, "cudaMemset failed"));
+    }
     if (cudaMemset(L->status, 0, sizeof(int32_t)) != cudaSuccess) return cleanup(fail(MOE_ERR_CUDA, "cudaMemset failed"));
     if (cudaStreamCreateWithFlags(&L->stream, cudaStreamNonBlocking) != cudaSuccess)
         return cleanup(fail(MOE_ERR_CUDA, "cudaStreamCreate failed"));
@@ -668,6 +689,9 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->router_w);
     dev_free(L->router_bias);
     dev_free(L->router_wt);
+    dev_free(L->router_w3);
+    dev_free(L->tc_recheck);
+    if (L->rplan) router_tc_plan_destroy(L->rplan);
     dev_free(L->bias_momentum);
     dev_free(L->router_nw);
     dev_free(L->router_wt_noise);
@@ -797,6 +821,11 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     const int n2 = launch_router_transpose(L->router_w, L->router_wt, L->E_router, L->cfg.input_dim, L->stream);
     if (n2 < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n2;
+    if (L->rplan) {
+        const int n4 = router_tc_plan_set(L->rplan, L->router_w, L->router_w3, L->E_router, L->cfg.input_dim, L->stream);
+        if (n4 < 0) return fail(MOE_ERR_CUDA, "router split failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n4;
+    }
     if (L->router_nw) {
         const int n3 = launch_router_transpose_noise(L->router_w, L->router_nw, L->router_wt_noise, L->E_router,
                                                      L->cfg.input_dim, L->stream);
@@ -956,6 +985,11 @@ int moe_layer_import_weights(moe_layer_t* L, const void* src, int64_t bytes) {
     int n = launch_router_transpose(L->router_w, L->router_wt, L->E_router, L->cfg.input_dim, L->stream);
     if (n < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     L->launches += n;
+    if (L->rplan) {
+        n = router_tc_plan_set(L->rplan, L->router_w, L->router_w3, L->E_router, L->cfg.input_dim, L->stream);
+        if (n < 0) return fail(MOE_ERR_CUDA, "router split failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n;
+    }
     if (L->router_nw) {
         n = launch_router_transpose_noise(L->router_w, L->router_nw, L->router_wt_noise, L->E_router, L->cfg.input_dim, L->stream);
         if (n < 0) return fail(MOE_ERR_CUDA, "router transpose launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -1111,6 +1145,17 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         !(L->noise && training) && !(L->aux_free && training)) {
         env_chunks = L->host_chunks;
         nchunks = env_chunks > 0 ? env_chunks : 5;
+        if (env_chunks <= 0) {
+            // A chunk must still give every expert enough rows that its weights are not streamed for
+            // nothing (every chunk reads all weights again): at least 512 rows per expert and chunk.
+            const int world = L->ep ? ep_world(L->ep) : 1;
+            const int64_t rows_per_expert = T_rule * world * L->k_tot / L->E;
+            const int64_t fit = rows_per_expert / 512;
+            if (fit < 5) {
+                nchunks = fit < 1 ? 1 : (int)fit;
+                env_chunks = nchunks;        // equal chunks
+            }
+        }
         if (nchunks > moe_layer::MAX_CHUNKS) nchunks = moe_layer::MAX_CHUNKS;
     }
     if (nchunks > 1) {
@@ -1331,6 +1376,18 @@ int moe_layer_stage_ms(moe_layer_t* L, int calls_back, float ms[7]) {
 }
 
 int64_t moe_layer_launch_count(const moe_layer_t* L) { return L ? L->launches : 0; }
+
+int moe_layer_router_rechecks(moe_layer_t* L, int64_t* tokens) {
+    if (!L || !tokens) return fail(MOE_ERR_INVALID, "null argument");
+    *tokens = 0;
+    if (!L->tc_recheck) return MOE_OK;
+    CUDA_TRY(cudaSetDevice(L->device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    int32_t v = 0;
+    CUDA_TRY(cudaMemcpy(&v, L->tc_recheck, sizeof(v), cudaMemcpyDeviceToHost));
+    *tokens = v;
+    return MOE_OK;
+}
 
 int moe_layer_tile_rows(moe_layer_t* L, int64_t T) {
     if (!L || T < 0) return fail(MOE_ERR_INVALID, "bad argument");

@@ -8,6 +8,7 @@
 //
 // Bound: HBM (reads x once: T*D*sizeof(x); everything else is O(T*E)).
 #include "common.cuh"
+#include "router_gate.cuh"
 
 #include <cfloat>
 #include <cstdlib>
@@ -17,238 +18,7 @@ namespace moe {
 
 namespace {
 
-struct GateCtx {
-    int E_router;     // columns of the incoming logits
-    int r0;           // first routed column (S in GATING mode, else 0)
-    int S, k, k_tot, E, E_probs;
-    int shared_mode, bias_gates_only, index_base, want_entropy;
-    int idx_base;     // base added to the ids stored through `idx` (0 inside the layer)
-    const float* noise;   // [T][E_router] standard-normal draws or null; scaled by noise_scale
-    float noise_scale;
-    int noise_net;        // draws are multiplied by softplus(noise-network logit) (src/core/router.jl:34-37)
-    const float* bias;
-    int32_t* idx;
-    float* gate;
-    int32_t* u_idx;
-    float* u_gate;
-    float* u_probs;
-    float* u_logits;
-};
-
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ double warp_sum_d(double v) {
-#pragma unroll
-    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-// One token, one warp.  lg[j] is the raw logit of router column lane + 32*j.
-// Accumulators (per warp, lane-owned columns): s_psum[e] += prob, returns lse^2 and entropy.
-template <int NJ>
-__device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ],
-                                           const float (&nl)[NJ], int lane, int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc) {
-    // Training-time router noise (src/core/router.jl:32-41): logits + noise_scale * randn (times
-    // softplus(noise_weight x) when the router has a noise network, nl[] = those logits) feed the
-    // gate and are the logits the router returns; the z-loss is computed by a second, noise-free
-    // router pass in the reference (src/core/moe_layer.jl:117-121), hence from the clean logits.
-    float lsel[NJ], lprob[NJ], lclean[NJ];
-    bool valid[NJ];
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const int e = lane + 32 * j;
-        const bool in = e < c.E_router;
-        const float b = (in && c.bias) ? c.bias[e] : 0.f;
-        float nz = 0.f;
-        if (in && c.noise) {
-            float draw = c.noise[t * c.E_router + e];
-            // NNlib.softplus(x) = log1p(exp(-|x|)) + relu(x)
-            if (c.noise_net) draw *= log1pf(expf(-fabsf(nl[j]))) + fmaxf(nl[j], 0.f);
-            nz = c.noise_scale * draw;
-        }
-        const float noisy = lg_in[j] + nz;
-        lsel[j] = noisy + b;
-        lprob[j] = c.bias_gates_only ? noisy : lsel[j];
-        lclean[j] = c.bias_gates_only ? lg_in[j] : lg_in[j] + b;
-        valid[j] = in && e >= c.r0;
-        if (in && c.u_logits) c.u_logits[t * c.E_router + e] = lprob[j];
-    }
-    // logsumexp over every router column (src/balancing/losses.jl:103-114)
-    {
-        float m = -FLT_MAX;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j < c.E_router) m = fmaxf(m, lclean[j]);
-        m = warp_max(m);
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j < c.E_router) s += expf(lclean[j] - m);
-        s = warp_sum(s);
-        const float lse = m + logf(s);
-        lse2_acc += lse * lse;
-    }
-    // softmax over the routed columns (NNlib.softmax: subtract max, exp, divide by the sum)
-    float pr[NJ], psel[NJ];
-    {
-        float m = -FLT_MAX;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (valid[j]) m = fmaxf(m, lprob[j]);
-        m = warp_max(m);
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            pr[j] = valid[j] ? expf(lprob[j] - m) : 0.f;
-            s += pr[j];
-        }
-        s = warp_sum(s);
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) pr[j] = pr[j] / s;
-    }
-    if (c.bias && c.bias_gates_only) {
-        float m = -FLT_MAX;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (valid[j]) m = fmaxf(m, lsel[j]);
-        m = warp_max(m);
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            psel[j] = valid[j] ? expf(lsel[j] - m) : 0.f;
-            s += psel[j];
-        }
-        s = warp_sum(s);
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) psel[j] = psel[j] / s;
-    } else {
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) psel[j] = pr[j];
-    }
-    // top-k of the probabilities: k passes of arg-max; among equal values the lowest column
-    // wins (Base.partialsortperm rev=true is stable; src/cuda/kernels.jl:24 uses strict '>').
-    bool taken[NJ];
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) taken[j] = false;
-    float my_v = 0.f;
-    int my_i = 0;
-    for (int s = 0; s < c.k; ++s) {
-        float best = -2.f;
-        int bi = INT_MAX;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            // a NaN probability ranks below every number but stays selectable
-            const float v = (psel[j] == psel[j]) ? psel[j] : -1.f;
-            if (valid[j] && !taken[j] && v > best) {
-                best = v;
-                bi = lane + 32 * j;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) {
-                best = ob;
-                bi = oi;
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j == bi) taken[j] = true;
-        if (lane == s) {
-            my_v = best < 0.f ? nanf("") : best;
-            my_i = bi;
-        }
-    }
-    // gates = selected / sum(selected), summed in slot order like the reference
-    float gsum = 0.f;
-    for (int s = 0; s < c.k; ++s) gsum += __shfl_sync(0xffffffffu, my_v, s);
-    const float g = my_v / gsum;
-
-    const int n_shared_slots = (c.shared_mode == MOE_SHARED_NONE) ? 0 : c.S;
-    if (lane < c.k && my_i != INT_MAX) {
-        const int layer_id = my_i + (c.shared_mode == MOE_SHARED_LAYER_BLEND ? c.S : 0);
-        float gi = g;
-        if (c.shared_mode == MOE_SHARED_GATING) gi = (float)((double)g * (1.0 - (double)c.S / (double)c.k_tot));
-        if (c.shared_mode == MOE_SHARED_LAYER_BLEND) gi = 0.5f * g;
-        const int slot = n_shared_slots + lane;
-        if (c.idx) c.idx[t * c.k_tot + slot] = layer_id + c.idx_base;
-        if (c.gate) c.gate[t * c.k_tot + slot] = gi;
-        atomicAdd(&s_cnt[layer_id], 1);
-        if (c.shared_mode == MOE_SHARED_LAYER_BLEND) {
-            if (c.u_idx) c.u_idx[t * c.k + lane] = layer_id + c.index_base;
-            if (c.u_gate) c.u_gate[t * c.k + lane] = g;
-        } else {
-            if (c.u_idx) c.u_idx[t * c.k_tot + slot] = layer_id + c.index_base;
-            if (c.u_gate) c.u_gate[t * c.k_tot + slot] = gi;
-        }
-    }
-    if (lane < n_shared_slots) {
-        const float gs = (c.shared_mode == MOE_SHARED_GATING) ? 1.0f / (float)c.k_tot : 0.5f / (float)c.S;
-        if (c.idx) c.idx[t * c.k_tot + lane] = lane + c.idx_base;
-        if (c.gate) c.gate[t * c.k_tot + lane] = gs;
-        atomicAdd(&s_cnt[lane], 1);
-        if (c.shared_mode == MOE_SHARED_GATING) {
-            if (c.u_idx) c.u_idx[t * c.k_tot + lane] = lane + c.index_base;
-            if (c.u_gate) c.u_gate[t * c.k_tot + lane] = gs;
-        }
-    }
-    // probabilities as the reference returns them, their per-expert sums, and the entropy
-    double ent = 0.0;
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const int e = lane + 32 * j;
-        if (e < c.E_probs) {
-            float pv;
-            if (c.shared_mode == MOE_SHARED_GATING) {
-                pv = (e < c.S) ? 1.0f / (float)c.E
-                               : (float)((double)pr[j] * (1.0 - (double)c.S / (double)c.E));
-            } else {
-                pv = pr[j];
-            }
-            if (c.u_probs) c.u_probs[t * c.E_probs + e] = pv;
-            s_psum[e] += pv;
-            if (c.want_entropy) ent -= (double)pv * log((double)pv + 1e-8);
-        }
-    }
-    if (c.want_entropy) ent_acc += warp_sum_d(ent);
-}
-
-__device__ __forceinline__ GateCtx make_ctx(const RouterParams& p) {
-    GateCtx c;
-    c.E_router = p.E_router;
-    c.r0 = (p.shared_mode == MOE_SHARED_GATING) ? p.S : 0;
-    c.S = p.S;
-    c.k = p.k;
-    c.k_tot = p.k_tot;
-    c.E = p.E;
-    c.E_probs = p.E_probs;
-    c.shared_mode = p.shared_mode;
-    c.bias_gates_only = p.bias_gates_only;
-    c.index_base = p.index_base;
-    c.want_entropy = p.want_entropy;
-    c.idx_base = 0;
-    c.noise = p.noise;
-    c.noise_scale = p.noise_scale;
-    c.noise_net = p.noise_off > 0;
-    c.bias = p.bias;
-    c.idx = p.idx;
-    c.gate = p.gate;
-    c.u_idx = p.u_idx;
-    c.u_gate = p.u_gate;
-    c.u_probs = p.u_probs;
-    c.u_logits = p.u_logits;
-    return c;
-}
+using namespace gating;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),

@@ -576,6 +576,12 @@ class MoELayer:
             _lib.check(n)
         return n
 
+    def router_rechecks(self) -> int:
+        """Tokens whose logits the tensor-core router re-evaluated with FP32 FMAs since creation."""
+        n = C.c_int64()
+        _lib.check(_lib.lib.moe_layer_router_rechecks(self._handle, C.byref(n)))
+        return int(n.value)
+
     def launch_count(self) -> int:
         return int(_lib.lib.moe_layer_launch_count(self._handle))
 

@@ -539,6 +539,54 @@ def test_exact_ties_go_to_the_lowest_index():
     assert di.cpu().numpy().T.tolist() == [[2, 3], [1, 2]]
 
 
+# ---- wide routers on the tensor cores (33..80 router rows, BF16 activations) ---------------------
+
+@pytest.mark.parametrize("T,E,k,D,gate,S", [
+    (1000, 66, 6, 2048, "shared", 2),     # the DeepSeek-style router: 64 routed + 2 shared rows, top-6
+    (300, 64, 2, 4096, "topk", 0),        # the expert-parallel layer's router width and depth
+    (129, 33, 3, 136, "topk", 0),         # narrowest width of the path, D not a multiple of the K block
+    (1, 80, 8, 256, "topk", 0),           # widest width, a single token
+    (2500, 48, 1, 512, "switch", 0),      # many tiles per CTA
+])
+def test_tensor_core_router_against_oracle(T, E, k, D, gate, S):
+    """Indices by the tie rule, logits/gates/probs/loss at the FP32 tolerance: the split gate GEMM on the
+    tensor cores plus the exact re-evaluation of close rankings must be indistinguishable from FP32."""
+    run_case(T, D, 64, 64, E, gate, k, S, seed=T + E, compute="bf16", std=0.05)
+
+
+def test_tensor_core_router_logit_error_and_rechecks(monkeypatch):
+    """The tensor-core logits against float64, beside the FP32-FMA router kernel on the same inputs; and
+    duplicated router rows (exact ties in every token) must be decided like the reference: lowest id."""
+    import mixtureofexperts_b200 as m
+
+    T, D, H, O, E, k = 4096, 4096, 64, 64, 64, 2
+    x, w = orc.make_layer_inputs(11, T, D, H, O, E, init="normal", std=0.02, bf16=True)
+    w.router[40] = w.router[7]                     # experts 8 and 41 always tie
+    lg64 = logits64(x, w)
+    cfg = orc.MoEConfig(num_experts=E, input_dim=D, hidden_dim=H, output_dim=O, activation="silu",
+                        gate_type=orc.TopKGating(k), balance_alpha=0.01, z_loss_weight=0.001)
+    o_idx, o_gates, o_probs, _ = orc.router_forward(cfg, w, x)
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    errs = {}
+    for tc in ("1", "0"):
+        monkeypatch.setenv("MOE_B200_ROUTER_TC", tc)
+        layer = make_device_layer(w, D=D, H=H, O=O, gate=m.TopKGating(k), compute_dtype="bf16")
+        _, _, routing = layer(xt.t(), training=True, return_routing=True)
+        torch.cuda.synchronize()
+        idx = routing["indices"].cpu().numpy().T
+        check_indices(idx, o_idx, lg64, k)
+        tied = (o_idx == 8).any(axis=1) | (o_idx == 41).any(axis=1)
+        assert np.array_equal(idx[tied], o_idx[tied])          # 8 before 41, never 41 without 8
+        assert rel_inf(routing["gates"].cpu().numpy().T, o_gates) < F32_TOL
+        assert rel_inf(routing["probs"].cpu().numpy().T, o_probs) < F32_TOL
+        errs[tc] = float(np.abs(routing["logits"].cpu().numpy().T.astype(np.float64) - lg64).max())
+        rechecks = layer.router_rechecks()
+        assert (rechecks >= int(tied.sum())) if tc == "1" else rechecks == 0
+        layer.close()
+    print(f"max |logit - float64|: tensor-core router {errs['1']:.3e}, FP32-FMA router {errs['0']:.3e}")
+    assert errs["1"] < 5e-6 and errs["0"] < 5e-6          # |logits| are ~1.3 here: a few 1e-6 relative for both
+
+
 # ---- StandardExpert: w2(act.(w1 x .+ b1)) .+ b2 -------------------------------------------------
 
 @pytest.mark.parametrize("T,E,k,D,H,O,activation", [
