@@ -467,6 +467,10 @@ def measure_other(name, torch, peaks, steps=10, warmup=3):
     layer = build_layer(w, torch, 0)
     T, D, O = w["T"], w["D"], w["O"]
     xdt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    if w["dtype"] == "f32":
+        # a step of this workload is ~0.1 ms: a few warm-up steps do not bring the SM clock up from
+        # idle, so warm up for a few tenths of a second and time more steps
+        steps, warmup = max(steps, 200), max(warmup, 3000)
     gx = torch.Generator(device="cuda:0").manual_seed(SEED + 7)
     x = torch.randn((T, D), device="cuda:0", generator=gx, dtype=torch.float32).to(xdt)
     out = torch.empty((T, O), device="cuda:0", dtype=torch.float32)

@@ -249,7 +249,7 @@ int64_t moe_layer_launch_count(const moe_layer_t*);
 
 /* Routers with 33..80 rows fed BF16 activations run their gate GEMM on the tensor cores (an exact
  * three-way BF16 split of the FP32 router matrix, FP32 accumulation) and re-evaluate with FP32 FMAs
- * every token whose top-(k+1) ranking has two neighbours closer than 1e-4 * max(1, |logit|).  *tokens
+ * every token whose top-(k+1) ranking has two neighbours closer than 3e-5 * max(1, |logit|).  *tokens
  * receives how many tokens were re-evaluated through this handle since creation (0 for layers
  * that never take that path).  A diagnostic without counterpart in the reference; synchronises. */
 int moe_layer_router_rechecks(moe_layer_t*, int64_t* tokens);

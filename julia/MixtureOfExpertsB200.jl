@@ -1,16 +1,18 @@
 # MixtureOfExpertsB200.jl - Julia host side of libmoe_b200.so.
 #
 # Keeps the names of MixtureOfExperts.jl for the MoE-layer forward path (create_moe_config,
-# MoELayer, TopKGating, SwitchGating, SharedExpertGating, GatedExpert, SwitchTransformerLoss,
-# cuda_moe_forward!) and calls the CUDA kernels through the C ABI of include/moe_b200.h with
-# ccall.  It replaces src/cuda of the reference; the CPU types of the reference keep working
+# MoELayer, TopKGating, SwitchGating, SharedExpertGating, GatedExpert, StandardExpert,
+# SwitchTransformerLoss, cuda_moe_forward!, create_cuda_moe, to_cuda, to_cpu, and the computing
+# part of the Llama2 glue, moe_ffn_forward!) and calls the CUDA kernels through the C ABI of
+# include/moe_b200.h with ccall.  It replaces src/cuda of the reference; the CPU types of the reference keep working
 # next to it.  NOTE: written against the header, not executed - no Julia runtime was available
 # where this library was developed.
 module MixtureOfExpertsB200
 
 export MoEConfig, create_moe_config, MoELayer, create_moe_layer, TopKGating, SwitchGating,
-       SharedExpertGating, GatedExpert, SwitchTransformerLoss, GatingMechanism, LoadBalancingLoss,
-       cuda_moe_forward!, reset_stats!, load_balance_score, silu
+       SharedExpertGating, GatedExpert, StandardExpert, SwitchTransformerLoss, GatingMechanism, LoadBalancingLoss,
+       cuda_moe_forward!, create_cuda_moe, to_cuda, to_cpu, reset_stats!, load_balance_score, silu,
+       set_router_noise!, enable_aux_free!, aux_free_state, moe_ffn_forward!, moe_ffn_forward_batch!, release_device_layers!
 
 const LIB = get(ENV, "MOE_B200_LIB", joinpath(@__DIR__, "..", "mixtureofexperts_b200", "lib", "libmoe_b200.so"))
 
@@ -231,6 +233,106 @@ function load_balance_score(counts::AbstractVector)   # src/core/utils.jl:40-52
     total == 0 && return 1.0f0
     ideal = total / n
     1.0f0 - sqrt(sum((counts .- ideal) .^ 2) / n) / ideal
+end
+
+# ---- the remaining names of src/cuda (src/cuda/utils.jl:4-15) ------------------------------------
+"create_cuda_moe(; kwargs...): the reference built a CudaMoELayer from CudaMoEConfig keywords; here it is the same MoELayer."
+create_cuda_moe(; device::Int = 0, compute_dtype::Symbol = :f32, kwargs...) =
+    MoELayer(create_moe_config(; kwargs...); device = device, compute_dtype = compute_dtype)
+"to_cuda(x) / to_cpu(x): the layer takes host arrays (moe(x)) or device pointers (cuda_moe_forward!) directly, so these are the identity."
+to_cuda(x::AbstractArray) = x
+to_cpu(x::AbstractArray) = Array(x)
+
+# ---- training-time branches that live in the handle ---------------------------------------------
+"Router noise (src/core/router.jl:32-41): `draws` is a DEVICE pointer to (E_router x T) standard-normal Float32 draws for the next training forward; C_NULL clears it."
+set_router_noise!(moe::MoELayer, draws::Ptr{Cvoid}, noise_scale::Real) =
+    check(ccall((:moe_layer_set_router_noise, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Cfloat), moe.handle, draws, Float32(noise_scale)))
+
+"AuxiliaryFreeLoss.update_bias! on the device (src/balancing/auxiliary_free.jl:36-71): `bias` goes in as the router's logit bias (bias_gates_only must be 1 in the config the handle was created with)."
+function enable_aux_free!(moe::MoELayer, bias::Vector{Float32}, bias_momentum::Vector{Float32}; learning_rate::Real = 0.01,
+                          momentum::Real = 0.9, update_freq::Int = 1, update_counter::Int = 0)
+    check(ccall((:moe_layer_set_router, LIB), Cint, (Ptr{Cvoid}, Ptr{Float32}, Ptr{Float32}, Cint, Cint),
+                moe.handle, moe.router_weight, bias, LAYOUT_OUT_CONTIG, 0))
+    check(ccall((:moe_layer_set_aux_free, LIB), Cint, (Ptr{Cvoid}, Cint, Cfloat, Cfloat, Cint, Ptr{Float32}, Int64),
+                moe.handle, 1, Float32(learning_rate), Float32(momentum), update_freq, bias_momentum, update_counter))
+end
+function aux_free_state(moe::MoELayer)
+    n = size(moe.router_weight, 1)
+    bias, mom, cnt = zeros(Float32, n), zeros(Float32, n), Ref{Int64}(0)
+    check(ccall((:moe_layer_aux_free_state, LIB), Cint, (Ptr{Cvoid}, Ptr{Float32}, Ptr{Float32}, Ref{Int64}),
+                moe.handle, bias, mom, cnt))
+    return bias, mom, cnt[]
+end
+
+# ---- Llama2 glue ------------------------------------------------------------------------------------
+# convert_to_moe and sample_moe of the reference (src/llama2/conversion.jl:43-107,
+# src/llama2/generation.jl:38-128) build and walk plain Julia structs; they stay as they are.  The
+# only code of that path that computes is moe_ffn_forward! (src/llama2/inference.jl:58-121); the two
+# functions below replace its routing + expert loop by one library call on the structs convert_to_moe
+# made (duck-typed: `layer.moe_experts[e].w1/.w2/.w3`, `layer.moe_router_weight`, `layer.moe_config`;
+# `state.xb`, `state.xb2`, `state.selected_experts`, `state.expert_gates`, `state.expert_load_counts`).
+# Llama2.jl stores W as (in x out) column-major and applies W'x, i.e. the IN index is contiguous.
+
+const DEVICE_LAYERS = IdDict{Any, Ptr{Cvoid}}()      # converted layer => handle (made on first use)
+
+function device_layer(layer; device::Int = 0, compute_dtype::Symbol = :f32)
+    get!(DEVICE_LAYERS, layer) do
+        cfg = layer.moe_config
+        dim, hidden = size(layer.moe_experts[1].w1)                      # w1 is (dim x hidden_dim)
+        kind, k, _ = gate_kind(cfg.gate_type)
+        c = CMoeConfig(length(layer.moe_experts), 0, k, dim, hidden, dim, kind, ACT_SILU,
+                       compute_dtype == :bf16 ? DTYPE_BF16 : DTYPE_F32, SHARED_NONE, 0.01f0, 0.0f0, 1, 0, 1.25f0, 0, 0)
+        h = Ref{Ptr{Cvoid}}(C_NULL)
+        check(ccall((:moe_layer_create, LIB), Cint, (Ref{CMoeConfig}, Cint, Ref{Ptr{Cvoid}}), c, device, h))
+        for (i, e) in enumerate(layer.moe_experts)
+            check(ccall((:moe_layer_set_expert, LIB), Cint,
+                        (Ptr{Cvoid}, Cint, Ptr{Float32}, Ptr{Float32}, Ptr{Float32}, Cint, Cint, Cint),
+                        h[], i - 1, e.w1, e.w2, e.w3, DTYPE_F32, LAYOUT_IN_CONTIG, 0))
+        end
+        check(ccall((:moe_layer_set_router, LIB), Cint, (Ptr{Cvoid}, Ptr{Float32}, Ptr{Float32}, Cint, Cint),
+                    h[], layer.moe_router_weight, C_NULL, LAYOUT_IN_CONTIG, 0))
+        h[]
+    end
+end
+
+"Free the device handles made by device_layer (call when a converted model is dropped)."
+function release_device_layers!()
+    for h in values(DEVICE_LAYERS)
+        ccall((:moe_layer_destroy, LIB), Cint, (Ptr{Cvoid},), h)
+    end
+    empty!(DEVICE_LAYERS)
+end
+
+"""
+moe_ffn_forward!(state, layer, config; rmsnorm! = nothing): the body of the reference's function
+for one token.  `rmsnorm!` is Llama2.rmsnorm! (pass it to have `state.xb` computed here like the
+reference does; leave it out if `state.xb` already holds the normalised activations).
+"""
+function moe_ffn_forward!(state, layer, config; rmsnorm! = nothing)
+    rmsnorm! === nothing || rmsnorm!(state.xb, state.x, layer.llama_layer.rms_ffn_weight)
+    h = device_layer(layer)
+    k = length(state.selected_experts)
+    idx = zeros(Int32, k)
+    GC.@preserve idx begin
+        o = CForwardOutputs(C_NULL, pointer(idx), pointer(state.expert_gates), C_NULL, C_NULL, C_NULL, C_NULL)
+        check(ccall((:moe_layer_forward_host, LIB), Cint,
+                    (Ptr{Cvoid}, Ptr{Cvoid}, Cint, Int64, Cint, Ptr{Float32}, Ref{CForwardOutputs}),
+                    h, state.xb, DTYPE_F32, 1, 0, state.xb2, o))
+    end
+    for j in 1:k
+        state.selected_experts[j] = idx[j]
+        idx[j] > 0 && (state.expert_load_counts[idx[j]] += 1)
+    end
+    return nothing
+end
+
+"Prefill: the MoE FFN of one layer for all prompt positions at once; X and OUT are (dim x n) Float32 matrices."
+function moe_ffn_forward_batch!(OUT::Matrix{Float32}, X::Matrix{Float32}, layer)
+    o = CForwardOutputs(C_NULL, C_NULL, C_NULL, C_NULL, C_NULL, C_NULL, C_NULL)
+    check(ccall((:moe_layer_forward_host, LIB), Cint,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Cint, Int64, Cint, Ptr{Float32}, Ref{CForwardOutputs}),
+                device_layer(layer), X, DTYPE_F32, size(X, 2), 0, OUT, o))
+    return OUT
 end
 
 end # module

@@ -202,10 +202,13 @@ void router_tc_plan_destroy(RouterTcPlan*);
 int router_tc_e_pad(int e_router);       // padded router width of the tensor-core path, 0 = not offered for this width
 // splits w (FP32 [E_router][D]) into w3 (BF16 [3*e_pad][D]) and encodes its tensor map; 1 = ready, 0 = not offered, <0 error
 int router_tc_plan_set(RouterTcPlan*, const float* w, void* w3, int e_router, int D, cudaStream_t s);
-bool router_tc_usable(const RouterTcPlan*, const RouterParams& p, int x_dtype);
+// may this call take the tensor-core router?  (BF16 activations, 16-byte aligned, no noise network armed)
+bool router_tc_usable(const RouterTcPlan*, const void* x, int x_dtype, bool noise_network_armed, int e_router, int D);
 int launch_router_tc(const RouterTcPlan*, const RouterParams& p, int num_cta, int num_sms, int32_t* status, cudaStream_t s);
 // K-major BF16 matrix [rows][K] as a 2-D tensor map with boxes of 64 x box_rows and 128-byte swizzle
 bool tc_encode_bf16_2d(void* map, const void* base, uint64_t K, uint64_t rows, uint32_t box_rows);
+// row-major FP32 matrix [rows][K] as a 2-D tensor map with plain boxes of box_k x box_rows (each <= 256)
+bool tc_encode_f32_2d(void* map, const void* base, uint64_t K, uint64_t rows, uint32_t box_k, uint32_t box_rows);
 
 // tcgen05 path (expert_tc.cu)
 struct TcGemmPlan;  // tensor maps + geometry, owned by the handle

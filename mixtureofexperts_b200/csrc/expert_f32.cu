@@ -7,7 +7,7 @@
 // Rows of the permuted buffer are grouped by expert; an m-tile (F32_TILE_M rows) never spans
 // two experts.  Weights are [E][N][K], K contiguous.  At the small per-expert row counts this
 // path serves, the kernel is bound by streaming the expert weights from HBM once.
-#include "activation.cuh"
+#include "tc_common.cuh"
 
 namespace moe {
 namespace {
@@ -139,14 +139,37 @@ __global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemm
 }
 
 // ---- few rows per expert (decode, tiny batches): stream the weights once ------------------------
-// One CTA owns (expert, 8*CW output columns); a warp owns CW columns; lanes split K in 16-byte
-// pieces, so every weight load instruction of a warp is a contiguous 512-byte read and a lane keeps
-// 2*CW (mode 1: 4*CW) of them in flight.  Four rows of the expert are held in registers per pass
-// (further rows of the expert are taken by the CTAs of the other blockIdx.z planes, which read the
-// same weight slice through L2 at the same time, or by further passes of this CTA); partial dot
-// products are reduced with warp shuffles once per pass.  Bound: HBM, E*N*K*4 bytes of weights per GEMM.
-constexpr int SK_ROWS = 4;
-constexpr int SK_THREADS = 256;
+// Bound: HBM, E*N*K*4 bytes of weights per GEMM.  A persistent CTA per SM walks work items (expert,
+// block of 16 output columns, pass of up to 16 of the expert's rows); a producer thread streams each
+// item as K tiles of 256 floats through a 4-stage shared-memory ring with TMA tensor loads (one
+// 16 x 256 box per weight matrix and one for the activation rows per stage, completion on an
+// mbarrier; 1-D bulk copies, one per row piece, were tried first and were bound by the ~50 ns the
+// TMA unit spends per copy), so ~190 KB per SM are in flight whatever the consumers do.
+// Eight consumer warps own two columns each (sixteen warps with one column each were no faster);
+// lanes split a K tile in 16-byte pieces (conflict-free shared-memory reads), keep (matrices x 2
+// columns x 16 rows) accumulators in registers over the whole K loop, rows taken in groups of four,
+// and finish with one multi-value butterfly (31 shuffles for 32 sums, fixed order) that leaves lane
+// l with the sum for (column l / 16, row l % 16).  Every wait is bounded like in
+// the tensor-core kernels.
+constexpr int ST_COLS = 16;          // output columns per work item
+constexpr int ST_ROWS = 16;          // rows of an expert per pass
+constexpr int ST_KT = 256;           // floats of K per ring stage
+constexpr int ST_STAGES = 4;
+constexpr int ST_CONSUMER_WARPS = 8;
+constexpr int ST_THREADS = (ST_CONSUMER_WARPS + 1) * 32;
+
+template <int NB>
+struct __align__(128) StreamStage {
+    float w[NB][ST_COLS][ST_KT];
+    float x[ST_ROWS][ST_KT];
+};
+template <int NB>
+struct __align__(128) StreamStorage {
+    StreamStage<NB> st[ST_STAGES];
+    uint64_t full_bar[ST_STAGES];
+    uint64_t empty_bar[ST_STAGES];
+    volatile int abort_flag;
+};
 
 __device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc) {
     acc = fmaf(a.x, b.x, acc);
@@ -156,111 +179,199 @@ __device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc)
     return acc;
 }
 
-template <int MODE, int CW>
-__global__ void __launch_bounds__(SK_THREADS) group_gemm_f32_skinny_kernel(const GroupGemmParams p) {
-    constexpr int NB = (MODE == 1) ? 2 : 1;
-    const int e = blockIdx.y;
-    const int row_begin = p.expert_offset[e], row_end = p.expert_offset[e + 1];
-    if (row_begin >= row_end) return;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_base = (blockIdx.x * (SK_THREADS / 32) + warp) * CW;
-    if (n_base >= p.N) return;
-    const float* A = reinterpret_cast<const float*>(p.A);
-    const float* Bm[2] = {reinterpret_cast<const float*>(p.B0) + (size_t)e * p.N * p.K,
-                          MODE == 1 ? reinterpret_cast<const float*>(p.B1) + (size_t)e * p.N * p.K : nullptr};
-    float* C = reinterpret_cast<float*>(p.C);
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-
-    for (int r0 = row_begin + SK_ROWS * (int)blockIdx.z; r0 < row_end; r0 += SK_ROWS * (int)gridDim.z) {
-        float acc[NB][CW][SK_ROWS];
+// 32 sums over the warp's lanes in 31 shuffles: after the call a[0] of lane l is the total of a[l].
+__device__ __forceinline__ void warp_reduce32(float (&a)[32], int lane) {
+    int n = 32;
 #pragma unroll
-        for (int b = 0; b < NB; ++b)
+    for (int o = 16; o; o >>= 1) {
+        n >>= 1;
+        const bool up = (lane & o) != 0;
 #pragma unroll
-            for (int c = 0; c < CW; ++c)
-#pragma unroll
-                for (int r = 0; r < SK_ROWS; ++r) acc[b][c][r] = 0.f;
-        for (int kc = 0; kc < p.K; kc += 256) {
-            const int k0 = kc + lane * 4, k1 = kc + 128 + lane * 4;   // K % 4 == 0: a piece is all in or all out
-            float4 xa[SK_ROWS], xb[SK_ROWS];
-#pragma unroll
-            for (int r = 0; r < SK_ROWS; ++r) {
-                const bool ok = r0 + r < row_end;
-                const float* row = A + (size_t)(r0 + r) * p.K;
-                xa[r] = (ok && k0 < p.K) ? *reinterpret_cast<const float4*>(row + k0) : zero4;
-                xb[r] = (ok && k1 < p.K) ? *reinterpret_cast<const float4*>(row + k1) : zero4;
+        for (int i = 0; i < 16; ++i) {
+            if (i < n) {
+                const float send = up ? a[i] : a[i + n];
+                const float keep = up ? a[i + n] : a[i];
+                a[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
             }
-            float4 wa[NB][CW], wb[NB][CW];
-#pragma unroll
-            for (int b = 0; b < NB; ++b)
-#pragma unroll
-                for (int c = 0; c < CW; ++c) {
-                    const int n = n_base + c;
-                    const float* wrow = Bm[b] + (size_t)n * p.K;
-                    wa[b][c] = (n < p.N && k0 < p.K) ? __ldg(reinterpret_cast<const float4*>(wrow + k0)) : zero4;
-                    wb[b][c] = (n < p.N && k1 < p.K) ? __ldg(reinterpret_cast<const float4*>(wrow + k1)) : zero4;
-                }
-#pragma unroll
-            for (int b = 0; b < NB; ++b)
-#pragma unroll
-                for (int c = 0; c < CW; ++c)
-#pragma unroll
-                    for (int r = 0; r < SK_ROWS; ++r)
-                        acc[b][c][r] = dot4(wb[b][c], xb[r], dot4(wa[b][c], xa[r], acc[b][c][r]));
         }
-#pragma unroll
-        for (int b = 0; b < NB; ++b)
-#pragma unroll
-            for (int c = 0; c < CW; ++c)
-#pragma unroll
-                for (int r = 0; r < SK_ROWS; ++r) {
-                    float v = acc[b][c][r];
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                    acc[b][c][r] = v;
-                }
-        // lane (c*SK_ROWS + r) writes element (row r, column c)
-#pragma unroll
-        for (int c = 0; c < CW; ++c)
-#pragma unroll
-            for (int r = 0; r < SK_ROWS; ++r) {
-                if (lane == c * SK_ROWS + r) {
-                    const int row = r0 + r, n = n_base + c;
-                    if (row < row_end && n < p.N) {
-                        float v;
-                        if (MODE == 1) {
-                            v = apply_act(p.activation, acc[0][c][r]) * acc[NB - 1][c][r];
-                        } else {
-                            v = acc[0][c][r];
-                            if (p.bias) v += p.bias[(size_t)e * p.N + n];
-                            if (p.epilogue_act >= 0) v = apply_act(p.epilogue_act, v);
-                        }
-                        group_gemm_out_row<float>(p, e, row)[n] = v;
-                    }
-                }
-            }
     }
 }
 
 template <int MODE>
-int launch_skinny(const GroupGemmParams& p, int64_t rows, int num_sms, cudaStream_t s) {
-    // Row passes of an expert run side by side in the z planes of the grid instead of one after the
-    // other in one CTA: about twice the average rows per expert, at most 8 planes (a CTA whose
-    // plane has no rows left for its expert leaves at once).
-    const int64_t avg = p.E > 0 ? (rows + p.E - 1) / p.E : 1;
-    int planes = (int)((2 * avg + SK_ROWS - 1) / SK_ROWS);
-    planes = planes < 1 ? 1 : (planes > 8 ? 8 : planes);
-    // fewer columns per warp when the problem would otherwise leave SMs without a CTA
-    const long ctas4 = (long)((p.N + 31) / 32) * p.E;
-    if (ctas4 >= 2L * num_sms) {
-        dim3 grid((p.N + 31) / 32, p.E, planes);
-        group_gemm_f32_skinny_kernel<MODE, 4><<<grid, SK_THREADS, 0, s>>>(p);
-    } else if (ctas4 * 2 >= 2L * num_sms) {
-        dim3 grid((p.N + 15) / 16, p.E, planes);
-        group_gemm_f32_skinny_kernel<MODE, 2><<<grid, SK_THREADS, 0, s>>>(p);
-    } else {
-        dim3 grid((p.N + 7) / 8, p.E, planes);
-        group_gemm_f32_skinny_kernel<MODE, 1><<<grid, SK_THREADS, 0, s>>>(p);
+__global__ void __launch_bounds__(ST_THREADS, 1)
+group_gemm_f32_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                             const __grid_constant__ CUtensorMap map_b1, const GroupGemmParams p) {
+    constexpr int NB = (MODE == 1) ? 2 : 1;
+    using Storage = StreamStorage<NB>;
+    extern __shared__ uint8_t smem_raw[];
+    Storage* ss = reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ncb = (p.N + ST_COLS - 1) / ST_COLS;
+    const int num_items = p.E * ncb;
+    const int nkt = (p.K + ST_KT - 1) / ST_KT;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < ST_STAGES; ++s) {
+            tc::mbar_init(&ss->full_bar[s], 1);
+            tc::mbar_init(&ss->empty_bar[s], ST_CONSUMER_WARPS);
+        }
+        ss->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    __syncthreads();
+
+    int stage = 0;
+    uint32_t phase = 0;
+    if (warp == ST_CONSUMER_WARPS) {
+        // ------------------------------ producer ----------------------------------------------
+        uint32_t armed = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+            const int e = item / ncb, n0 = (item % ncb) * ST_COLS;
+            const int row_begin = p.expert_offset[e], row_end = p.expert_offset[e + 1];
+            for (int r0 = row_begin; ok && r0 < row_end; r0 += ST_ROWS) {
+                for (int kt = 0; kt < nkt; ++kt) {
+                    int go = 1;
+                    if (lane == 0)
+                        go = tc::mbar_wait(&ss->empty_bar[stage], phase ^ 1u, &ss->abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY);
+                    go = __shfl_sync(0xffffffffu, go, 0);
+                    if (!go) {
+                        ok = false;
+                        break;
+                    }
+                    if (lane == 0) {
+                        // boxes are always transferred whole (rows and columns past the tensor arrive as zeros)
+                        StreamStage<NB>& st = ss->st[stage];
+                        tc::mbar_expect_tx(&ss->full_bar[stage], (uint32_t)sizeof(StreamStage<NB>));
+                        tc::tma_load_2d(&st.w[0][0][0], &map_b0, kt * ST_KT, e * p.N + n0, &ss->full_bar[stage]);
+                        if (NB == 2) tc::tma_load_2d(&st.w[NB - 1][0][0], &map_b1, kt * ST_KT, e * p.N + n0, &ss->full_bar[stage]);
+                        tc::tma_load_2d(&st.x[0][0], &map_a, kt * ST_KT, r0, &ss->full_bar[stage]);
+                    }
+                    armed |= 1u << stage;
+                    if (++stage == ST_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        if ((!ok || ss->abort_flag) && lane == 0) {
+            // leaving early: give the copies already issued a bounded time to land
+            for (int s = 0; s < ST_STAGES; ++s) {
+                if (!(armed & (1u << s))) continue;
+                const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+                const unsigned long long t0 = tc::globaltimer_ns();
+                while (!tc::mbar_try_wait(&ss->full_bar[s], par) && tc::globaltimer_ns() - t0 < tc::DRAIN_LIMIT_NS) {
+                }
+            }
+        }
+        return;
+    }
+
+    // ------------------------------ consumers (warps 0..7): columns 2w, 2w+1 of the item -----------
+    const int c_lo = warp * 2;
+    bool alive = true;
+    for (int item = blockIdx.x; alive && item < num_items; item += gridDim.x) {
+        const int e = item / ncb, n0 = (item % ncb) * ST_COLS;
+        const int row_begin = p.expert_offset[e], row_end = p.expert_offset[e + 1];
+        for (int r0 = row_begin; alive && r0 < row_end; r0 += ST_ROWS) {
+            const int rc = min(ST_ROWS, row_end - r0);
+            float acc[NB][32];                       // [matrix][column (0/1) * 16 + row]
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[b][i] = 0.f;
+            for (int kt = 0; kt < nkt; ++kt) {
+                int ready = 1;
+                if (lane == 0) ready = tc::mbar_wait(&ss->full_bar[stage], phase, &ss->abort_flag, p.status, DEV_TIMEOUT_TMA_FULL);
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (!ready) {
+                    alive = false;
+                    break;
+                }
+                while (!tc::mbar_try_wait(&ss->full_bar[stage], phase)) {
+                }  // already complete: gives every lane its own acquire
+                const StreamStage<NB>& st = ss->st[stage];
+                const int klen = min(ST_KT, p.K - kt * ST_KT);
+#pragma unroll
+                for (int piece = 0; piece < ST_KT / 128; ++piece) {
+                    const int k = piece * 128 + lane * 4;
+                    if (k < klen) {
+                        float4 w[NB][2];
+#pragma unroll
+                        for (int b = 0; b < NB; ++b) {
+                            w[b][0] = *reinterpret_cast<const float4*>(&st.w[b][c_lo][k]);
+                            w[b][1] = *reinterpret_cast<const float4*>(&st.w[b][c_lo + 1][k]);
+                        }
+                        // rows in groups of four (a group past the pass's rows is skipped as a whole; rows past
+                        // rc inside a group hold other experts' rows and their sums are never stored)
+#pragma unroll
+                        for (int g = 0; g < ST_ROWS / 4; ++g) {
+                            if (g * 4 < rc) {
+                                float4 xv[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) xv[q] = *reinterpret_cast<const float4*>(&st.x[g * 4 + q][k]);
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const int r = g * 4 + q;
+#pragma unroll
+                                    for (int b = 0; b < NB; ++b) {
+                                        acc[b][r] = dot4(w[b][0], xv[q], acc[b][r]);
+                                        acc[b][16 + r] = dot4(w[b][1], xv[q], acc[b][16 + r]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&ss->empty_bar[stage]);
+                if (++stage == ST_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (!alive) break;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) warp_reduce32(acc[b], lane);
+            // lane l now holds (column c_lo + l / 16, row r0 + l % 16)
+            const int n = n0 + c_lo + (lane >> 4), row = r0 + (lane & 15);
+            if (n < p.N && (lane & 15) < rc) {
+                float v;
+                if (MODE == 1) {
+                    v = apply_act(p.activation, acc[0][0]) * acc[NB - 1][0];
+                } else {
+                    v = acc[0][0];
+                    if (p.bias) v += p.bias[(size_t)e * p.N + n];
+                    if (p.epilogue_act >= 0) v = apply_act(p.epilogue_act, v);
+                }
+                group_gemm_out_row<float>(p, e, row)[n] = v;
+            }
+        }
+    }
+}
+
+template <int MODE>
+int launch_stream(const GroupGemmParams& p, int64_t rows, int num_sms, cudaStream_t s) {
+    constexpr int NB = (MODE == 1) ? 2 : 1;
+    auto kern = group_gemm_f32_stream_kernel<MODE>;
+    const size_t smem = sizeof(StreamStorage<NB>) + 128;
+    static bool attr_done[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
+        attr_done[dev] = true;
+    }
+    CUtensorMap ma, mb0, mb1;
+    if (!tc_encode_f32_2d(&ma, p.A, (uint64_t)p.K, (uint64_t)rows, ST_KT, ST_ROWS) ||
+        !tc_encode_f32_2d(&mb0, p.B0, (uint64_t)p.K, (uint64_t)p.E * p.N, ST_KT, ST_COLS) ||
+        !tc_encode_f32_2d(&mb1, NB == 2 ? p.B1 : p.B0, (uint64_t)p.K, (uint64_t)p.E * p.N, ST_KT, ST_COLS))
+        return -1;
+    const long items = (long)p.E * ((p.N + ST_COLS - 1) / ST_COLS);
+    const int grid = (int)(items < num_sms ? items : num_sms);
+    kern<<<grid, ST_THREADS, smem, s>>>(ma, mb0, mb1, p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
@@ -274,7 +385,7 @@ int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, in
                          (mode != 1 || (reinterpret_cast<uintptr_t>(p.B1) & 15) == 0);
     if (aligned && rows <= 16L * p.E) {
         // on average at most 16 rows per expert: weight streaming beats tiling
-        return mode == 1 ? launch_skinny<1>(p, rows, num_sms, s) : launch_skinny<2>(p, rows, num_sms, s);
+        return mode == 1 ? launch_stream<1>(p, rows, num_sms, s) : launch_stream<2>(p, rows, num_sms, s);
     }
     dim3 grid(max_mtiles, (p.N + BN - 1) / BN);
     if (mode == 1) group_gemm_f32_kernel<1><<<grid, THREADS, 0, s>>>(p);

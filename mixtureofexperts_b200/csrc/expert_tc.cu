@@ -309,6 +309,19 @@ bool tc_encode_bf16_2d(void* map, const void* base, uint64_t K, uint64_t rows, u
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// row-major FP32 matrix [rows][K] as a 2-D tensor map with plain (unswizzled) boxes of box_k x box_rows
+bool tc_encode_f32_2d(void* map, const void* base, uint64_t K, uint64_t rows, uint32_t box_k, uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn || box_rows == 0 || box_rows > 256 || box_k == 0 || box_k > 256) return false;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K * 4};
+    cuuint32_t box[2] = {box_k, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(reinterpret_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides,
+              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int group_m_setting() {
     static int gm_env = -1;
     if (gm_env < 0) {

@@ -401,7 +401,12 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     if ((rc = ensure_workspace(L, T > 0 ? T : 1))) return rc;
     if (!L->ep && L->plan_dirty && (rc = ensure_plan(L, L->xp, L->h, L->P_cap))) return rc;
 
-    const int tokens_per_cta = router_tokens_per_cta(T, L->E_router, L->num_sms);
+    // the tensor-core router's gating kernel is latency-bound per token like a narrow router's: it takes the
+    // narrow rule (enough CTAs for every SM) whatever the router width
+    const bool noise_net_armed = training && L->noise_scale > 0.f && L->noise && L->router_nw;
+    const bool use_tc_router = L->router_tc_enabled && L->tc_logits != nullptr &&
+                               router_tc_usable(L->rplan, x, x_dtype, noise_net_armed, L->E_router, c.input_dim);
+    const int tokens_per_cta = router_tokens_per_cta(T, use_tc_router ? 8 : L->E_router, L->num_sms);
     const int num_cta = (int)((T + tokens_per_cta - 1) / tokens_per_cta);
     if (L->prof_slots > 0) L->prof_cur = (int)(L->prof_calls++ % L->prof_slots);
     stage_mark(L, 0, s);
@@ -442,17 +447,6 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     r.u_logits = opt->logits;
     r.tc_logits = L->tc_logits;
     r.tc_recheck_count = L->tc_recheck;
-    int n = 0;
-    if (num_cta > 0) {
-        if (L->router_tc_enabled && router_tc_usable(L->rplan, r, x_dtype))
-            n = launch_router_tc(L->rplan, r, num_cta, L->num_sms, L->status, s);
-        else
-            n = launch_router(r, x_dtype, num_cta, L->num_sms, s);
-        if (n < 0) return fail(MOE_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
-        L->launches += n;
-    }
-    stage_mark(L, 1, s);
-
     ScanParams sp{};
     sp.T = T;
     sp.E = L->E;
@@ -484,10 +478,6 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     sp.ep_sums = L->ep ? nullptr : partial_sums;
     sp.sums_accumulate = chunked ? 1 : 0;
     sp.ep_record = L->ep ? ep_record_buffer(L->ep) : nullptr;
-    n = launch_scan(sp, s);
-    if (n < 0) return fail(MOE_ERR_CUDA, "scan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
-    L->launches += n;
-    stage_mark(L, 2, s);
 
     PermuteParams pp{};
     pp.x = x;
@@ -511,6 +501,21 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     pp.gate_rw = L->gate;
     pp.u_idx = opt->indices;
     pp.u_gate = opt->gates;
+
+    int n = 0;
+    if (num_cta > 0) {
+        if (use_tc_router)
+            n = launch_router_tc(L->rplan, r, num_cta, L->num_sms, L->status, s);
+        else
+            n = launch_router(r, x_dtype, num_cta, L->num_sms, s);
+        if (n < 0) return fail(MOE_ERR_CUDA, "router launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        L->launches += n;
+    }
+    stage_mark(L, 1, s);
+    n = launch_scan(sp, s);
+    if (n < 0) return fail(MOE_ERR_CUDA, "scan launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    L->launches += n;
+    stage_mark(L, 2, s);
     const bool peer = L->ep && ep_peer_mode(L->ep);
     EpPlan plan;
     const int ep_tile_m = L->cfg.compute_dtype == MOE_DTYPE_BF16 ? TC_TILE_M : F32_TILE_M;

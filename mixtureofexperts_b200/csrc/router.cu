@@ -237,7 +237,7 @@ router_kernel(const RouterParams p) {
             lg[j] = s;
             nl[j] = sn;
         }
-        gate_token<NJ>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
+        gate_token<NJ, false>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
     }
     if (lane == 0) {
         s_lse2[warp] = lse2;
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) gates_only_kernel(GateCtx c, c
     }
     float lse2 = 0.f;
     double ent = 0.0;
-    gate_token<NJ>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
+    gate_token<NJ, false>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
 }
 
 template <int E_PAD, int BK, int KS, typename XT, int NI>

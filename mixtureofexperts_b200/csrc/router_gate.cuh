@@ -48,9 +48,16 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 
 // One token, one warp.  lg[j] is the raw logit of router column lane + 32*j.
 // Accumulators (per warp, lane-owned columns): s_psum[e] += prob, returns lse^2 and entropy.
-template <int NJ>
-__device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ],
-                                           const float (&nl)[NJ], int lane, int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc) {
+//
+// PROBE = true (tensor-core router): the logits carry a rounding error of about 1.5e-6 times their
+// scale, so the ranking is looked at before anything is written: one extra arg-max pass finds the
+// (k+1)-th probability, and if two neighbours of the top k+1 are closer than probe_rel * max(1,
+// largest |logit|) -- relative differences of probabilities are differences of logits -- the function
+// returns false WITHOUT side effects and the caller gates the token again from exact logits.
+template <int NJ, bool PROBE>
+__device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ], const float (&nl)[NJ], int lane,
+                                           int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc, float probe_rel = 0.f) {
+    constexpr unsigned FULL = 0xffffffffu;
     // Training-time router noise (src/core/router.jl:32-41): logits + noise_scale * randn (times
     // softplus(noise_weight x) when the router has a noise network, nl[] = those logits) feed the
     // gate and are the logits the router returns; the z-loss is computed by a second, noise-free
@@ -74,22 +81,6 @@ __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const fl
         lprob[j] = c.bias_gates_only ? noisy : lsel[j];
         lclean[j] = c.bias_gates_only ? lg_in[j] : lg_in[j] + b;
         valid[j] = in && e >= c.r0;
-        if (in && c.u_logits) c.u_logits[t * c.E_router + e] = lprob[j];
-    }
-    // logsumexp over every router column (src/balancing/losses.jl:103-114)
-    {
-        float m = -FLT_MAX;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j < c.E_router) m = fmaxf(m, lclean[j]);
-        m = warp_max(m);
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j < c.E_router) s += expf(lclean[j] - m);
-        s = warp_sum(s);
-        const float lse = m + logf(s);
-        lse2_acc += lse * lse;
     }
     // softmax over the routed columns (NNlib.softmax: subtract max, exp, divide by the sum)
     float pr[NJ], psel[NJ];
@@ -130,43 +121,67 @@ __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const fl
     }
     // top-k of the probabilities: k passes of arg-max; among equal values the lowest column
     // wins (Base.partialsortperm rev=true is stable; src/cuda/kernels.jl:24 uses strict '>').
-    bool taken[NJ];
+    // A probability is >= 0, so its bit pattern orders like a signed integer; a NaN probability is
+    // keyed as -1.0f: it ranks below every number but stays selectable.  Two warp reductions per
+    // pass: the largest key, then the lowest column that holds it.
+    int key[NJ];
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) taken[j] = false;
+    for (int j = 0; j < NJ; ++j) {
+        const float v = (psel[j] == psel[j]) ? psel[j] : -1.f;
+        key[j] = valid[j] ? __float_as_int(v) : INT_MIN;
+    }
     float my_v = 0.f;
     int my_i = 0;
-    for (int s = 0; s < c.k; ++s) {
-        float best = -2.f;
-        int bi = INT_MAX;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            // a NaN probability ranks below every number but stays selectable
-            const float v = (psel[j] == psel[j]) ? psel[j] : -1.f;
-            if (valid[j] && !taken[j] && v > best) {
-                best = v;
-                bi = lane + 32 * j;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) {
-                best = ob;
-                bi = oi;
-            }
-        }
+    float prev = 0.f;
+    bool close = false;
+    const int passes = PROBE ? min(c.k + 1, c.E_router - c.r0) : c.k;
+    for (int s = 0; s < passes; ++s) {
+        int bk = INT_MIN, bj = 0;
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j == bi) taken[j] = true;
+            if (key[j] > bk) {
+                bk = key[j];
+                bj = j;
+            }
+        const int m = __reduce_max_sync(FULL, bk);
+        int bi = __reduce_min_sync(FULL, (bk == m && m != INT_MIN) ? lane + 32 * bj : INT_MAX);
+        const float best = m == INT_MIN ? -2.f : __int_as_float(m);
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+            if (lane + 32 * j == bi) key[j] = INT_MIN;
+        if (PROBE) {
+            if (s > 0 && !(prev - best >= probe_rel * prev)) close = true;
+            prev = best;
+            if (s == c.k) break;          // the (k+1)-th value was only needed for the comparison
+        }
         if (lane == s) {
             my_v = best < 0.f ? nanf("") : best;
             my_i = bi;
         }
     }
+    if (PROBE && close) return false;
+
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+        if (lane + 32 * j < c.E_router && c.u_logits) c.u_logits[t * c.E_router + lane + 32 * j] = lprob[j];
+    // logsumexp over every router column (src/balancing/losses.jl:103-114)
+    {
+        float m = -FLT_MAX;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+            if (lane + 32 * j < c.E_router) m = fmaxf(m, lclean[j]);
+        m = warp_max(m);
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+            if (lane + 32 * j < c.E_router) s += expf(lclean[j] - m);
+        s = warp_sum(s);
+        const float lse = m + logf(s);
+        lse2_acc += lse * lse;
+    }
     // gates = selected / sum(selected), summed in slot order like the reference
     float gsum = 0.f;
-    for (int s = 0; s < c.k; ++s) gsum += __shfl_sync(0xffffffffu, my_v, s);
+    for (int s = 0; s < c.k; ++s) gsum += __shfl_sync(FULL, my_v, s);
     const float g = my_v / gsum;
 
     const int n_shared_slots = (c.shared_mode == MOE_SHARED_NONE) ? 0 : c.S;
@@ -198,7 +213,10 @@ __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const fl
         }
     }
     // probabilities as the reference returns them, their per-expert sums, and the entropy
-    double ent = 0.0;
+    // -sum p log(p + 1e-8) (src/core/moe_layer.jl:262: Float64 there because of the literal; FP32 here
+    // agrees with it to ~1e-7 relative, the per-token sums are then accumulated in double)
+    float ent = 0.f;
+    const float shared_scale = (float)(1.0 - (double)c.S / (double)c.E);
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int e = lane + 32 * j;
@@ -212,10 +230,12 @@ __device__ __forceinline__ void gate_token(const GateCtx& c, int64_t t, const fl
             }
             if (c.u_probs) c.u_probs[t * c.E_probs + e] = pv;
             s_psum[e] += pv;
-            if (c.want_entropy) ent -= (double)pv * log((double)pv + 1e-8);
+            if (c.want_entropy) ent -= pv * logf(pv + 1e-8f);
         }
     }
-    if (c.want_entropy) ent_acc += warp_sum_d(ent);
+    (void)shared_scale;
+    if (c.want_entropy) ent_acc += (double)warp_sum(ent);
+    return true;
 }
 
 __device__ __forceinline__ GateCtx make_ctx(const RouterParams& p) {

@@ -23,7 +23,7 @@
 //       after the others, its logits are recomputed with FP32 FMAs (the eight warps of the CTA share
 //       the router rows, lanes split K, fixed-order shuffle sum) before gate_token() runs.  The
 //       tensor-core logits are within ~1.5e-6 of that scale of the float64 values (measured in the
-//       tests: the same as the FP32-FMA kernel), far below RECHECK_REL = 1e-4, so a token that is not
+//       tests: the same as the FP32-FMA kernel), far below RECHECK_REL = 3e-5, so a token that is not
 //       re-evaluated has the same ranking under exact arithmetic, and ties within 1e-6 are always
 //       decided on FP32-FMA values.
 #include <cuda.h>
@@ -47,7 +47,7 @@ constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = 512;          // two accumulators of up to 256 columns
 constexpr int NUM_THREADS = 192;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr float RECHECK_REL = 1e-4f;     // re-evaluate when two ranked logits are closer than this times max(1, |logit|)
+constexpr float RECHECK_REL = 3e-5f;     // re-evaluate when two ranked logits are closer than this times max(1, |logit|)
 
 template <int E_PAD>
 struct __align__(1024) RouterTcStorage {
@@ -260,73 +260,42 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     }
 }
 
-// Could the rounding of the tensor-core logits have changed the ranking of this token's top k+1
-// selection logits?  True if two neighbours of that ranking are closer than RECHECK_REL * max(1, largest
-// |logit| of the token): the tensor-core logits are within ~1.5e-6 of that scale of the exact ones.
-template <int NJ>
-__device__ __forceinline__ bool ranking_is_close(const GateCtx& c, const float (&lg)[NJ], int lane) {
-    float v[NJ];
-    bool avail[NJ];
-    float mag = 0.f;
+// NE logits of token t with FP32 FMAs by one warp: lanes split K in 16-byte pieces (8 products per
+// piece into one accumulator per logit, at most D/32 products per lane), then fixed-order shuffle sums.
+// The NE router rows are read side by side so that their loads are in flight together.
+template <int NE>
+__device__ __forceinline__ void exact_logits(const __nv_bfloat16* __restrict__ x, const float* const (&w)[NE], int D, int lane,
+                                             float (&out)[NE]) {
+    float s[NE];
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const int e = lane + 32 * j;
-        avail[j] = e < c.E_router && e >= c.r0;
-        v[j] = lg[j] + ((avail[j] && c.bias) ? c.bias[e] : 0.f);
-        if (v[j] != v[j]) v[j] = -FLT_MAX;            // NaN: ranked last, like in gate_token
-        if (avail[j] && v[j] > -FLT_MAX) mag = fmaxf(mag, fabsf(lg[j]));
-    }
-    mag = warp_max(mag);
-    const float gap = RECHECK_REL * fmaxf(1.f, mag);
-    const int passes = min(c.k + 1, c.E_router - c.r0);
-    float prev = 0.f;
-    bool close = false;
-    for (int s = 0; s < passes; ++s) {
-        float best = -INFINITY;                       // lanes with nothing left never win
-        int bi = INT_MAX;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (avail[j] && (bi == INT_MAX || v[j] > best)) {
-                best = v[j];
-                bi = lane + 32 * j;
-            }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) {
-                best = ob;
-                bi = oi;
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < NJ; ++j)
-            if (lane + 32 * j == bi) avail[j] = false;
-        if (s > 0 && !(prev - best >= gap)) close = true;
-        prev = best;
-    }
-    return close;
-}
-
-// One logit of token t with FP32 FMAs by one warp: lanes split K in 16-byte pieces (8 products per
-// piece into one accumulator, at most D/32 products per lane), then a fixed-order shuffle sum.
-__device__ __forceinline__ float exact_logit(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, int D, int lane) {
-    float s = 0.f;
-#pragma unroll 4
+    for (int i = 0; i < NE; ++i) s[i] = 0.f;
+#pragma unroll 2
     for (int k0 = lane * 8; k0 < D; k0 += 256) {
         const uint4 xv = *reinterpret_cast<const uint4*>(x + k0);
-        const float4 w0 = *reinterpret_cast<const float4*>(w + k0);
-        const float4 w1 = *reinterpret_cast<const float4*>(w + k0 + 4);
-        s = fmaf(__uint_as_float(xv.x << 16), w0.x, s);
-        s = fmaf(__uint_as_float(xv.x & 0xffff0000u), w0.y, s);
-        s = fmaf(__uint_as_float(xv.y << 16), w0.z, s);
-        s = fmaf(__uint_as_float(xv.y & 0xffff0000u), w0.w, s);
-        s = fmaf(__uint_as_float(xv.z << 16), w1.x, s);
-        s = fmaf(__uint_as_float(xv.z & 0xffff0000u), w1.y, s);
-        s = fmaf(__uint_as_float(xv.w << 16), w1.z, s);
-        s = fmaf(__uint_as_float(xv.w & 0xffff0000u), w1.w, s);
+        float4 w0[NE], w1[NE];
+#pragma unroll
+        for (int i = 0; i < NE; ++i) {
+            w0[i] = *reinterpret_cast<const float4*>(w[i] + k0);
+            w1[i] = *reinterpret_cast<const float4*>(w[i] + k0 + 4);
+        }
+        const float x0 = __uint_as_float(xv.x << 16), x1 = __uint_as_float(xv.x & 0xffff0000u),
+                    x2 = __uint_as_float(xv.y << 16), x3 = __uint_as_float(xv.y & 0xffff0000u),
+                    x4 = __uint_as_float(xv.z << 16), x5 = __uint_as_float(xv.z & 0xffff0000u),
+                    x6 = __uint_as_float(xv.w << 16), x7 = __uint_as_float(xv.w & 0xffff0000u);
+#pragma unroll
+        for (int i = 0; i < NE; ++i) {
+            s[i] = fmaf(x0, w0[i].x, s[i]);
+            s[i] = fmaf(x1, w0[i].y, s[i]);
+            s[i] = fmaf(x2, w0[i].z, s[i]);
+            s[i] = fmaf(x3, w0[i].w, s[i]);
+            s[i] = fmaf(x4, w1[i].x, s[i]);
+            s[i] = fmaf(x5, w1[i].y, s[i]);
+            s[i] = fmaf(x6, w1[i].z, s[i]);
+            s[i] = fmaf(x7, w1[i].w, s[i]);
+        }
     }
-    return warp_sum(s);
+#pragma unroll
+    for (int i = 0; i < NE; ++i) out[i] = warp_sum(s[i]);
 }
 
 constexpr int GATE_THREADS = 256;
@@ -364,11 +333,15 @@ __global__ void __launch_bounds__(GATE_THREADS) router_gate_kernel(const RouterP
             lg[j] = e < p.E_router ? logits[(size_t)t * ld + e] : 0.f;
             nl[j] = 0.f;
         }
-        if (ranking_is_close<NJ>(c, lg, lane)) {
+        // probe threshold: RECHECK_REL times max(1, largest |logit| of the token)
+        float mag = 0.f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+            if (lane + 32 * j < p.E_router && fabsf(lg[j]) <= FLT_MAX) mag = fmaxf(mag, fabsf(lg[j]));
+        mag = __int_as_float(__reduce_max_sync(0xffffffffu, __float_as_int(mag)));   // non-negative floats order like ints
+        if (!gate_token<NJ, true>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent, RECHECK_REL * fmaxf(1.f, mag))) {
             if (lane == 0) atomicOr(&s_defer, 1ull << tok);
-            continue;
         }
-        gate_token<NJ>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
     }
     __syncthreads();
     unsigned long long defer = s_defer;
@@ -378,9 +351,16 @@ __global__ void __launch_bounds__(GATE_THREADS) router_gate_kernel(const RouterP
         defer &= defer - 1ull;
         const int64_t t = tok0 + tok;
         const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x) + (size_t)t * p.D;
-        for (int e = warp; e < p.E_router; e += GATE_WARPS) {
-            const float v = exact_logit(x, p.w + (size_t)e * p.D, p.D, lane);
-            if (lane == 0) s_exact[e] = v;
+        // warp w owns router rows w, w + 8, w + 16, ...; four rows at a time
+        for (int e0 = warp; e0 < p.E_router; e0 += 4 * GATE_WARPS) {
+            const float* rows[4];
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) rows[i] = p.w + (size_t)min(e0 + i * GATE_WARPS, p.E_router - 1) * p.D;
+            exact_logits<4>(x, rows, p.D, lane, v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (lane == 0 && e0 + i * GATE_WARPS < p.E_router) s_exact[e0 + i * GATE_WARPS] = v[i];
         }
         __syncthreads();
         if (warp == 0) {
@@ -391,7 +371,7 @@ __global__ void __launch_bounds__(GATE_THREADS) router_gate_kernel(const RouterP
                 lg[j] = e < p.E_router ? s_exact[e] : 0.f;
                 nl[j] = 0.f;
             }
-            gate_token<NJ>(c, t, lg, nl, lane, s_cnt, s_psum[0], lse2, ent);
+            gate_token<NJ, false>(c, t, lg, nl, lane, s_cnt, s_psum[0], lse2, ent);
         }
         __syncthreads();
     }
@@ -468,9 +448,9 @@ int router_tc_plan_set(RouterTcPlan* plan, const float* w, void* w3, int e_route
     return 1;
 }
 
-bool router_tc_usable(const RouterTcPlan* plan, const RouterParams& p, int x_dtype) {
-    return plan && plan->valid && p.tc_logits && x_dtype == MOE_DTYPE_BF16 && p.noise_off == 0 && p.D % 8 == 0 &&
-           (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 && router_tc_e_pad(p.E_router) == plan->e_pad;
+bool router_tc_usable(const RouterTcPlan* plan, const void* x, int x_dtype, bool noise_network_armed, int e_router, int D) {
+    return plan && plan->valid && x_dtype == MOE_DTYPE_BF16 && !noise_network_armed && D % 8 == 0 &&
+           (reinterpret_cast<uintptr_t>(x) & 15) == 0 && router_tc_e_pad(e_router) == plan->e_pad;
 }
 
 int launch_router_tc(const RouterTcPlan* plan, const RouterParams& p, int num_cta, int num_sms, int32_t* status, cudaStream_t s) {
