@@ -34,6 +34,8 @@
  *   MOE_B200_HOST_TIMELINE=1   print every chunk's copy and compute times to stderr
  *   MOE_B200_GROUP_M=n         m-tiles per group of the GEMM tile order (default 32)
  *   MOE_B200_ROUTER_TILE=16|32|64   force the token tile of the router and permute kernels
+ *   MOE_B200_INPLACE_SHARED=0  shared experts' rows are copied by the permute like everybody's instead of being
+ *                              read from the activations in place (comparison; read at handle creation)
  *   MOE_B200_ROUTER_TC=0       keep the FP32-FMA router kernel for wide routers too (comparison; read at
  *                              handle creation)
  *   MOE_B200_EP_MODE=nccl      expert parallelism moves token rows with ncclSend/ncclRecv instead of

@@ -122,6 +122,9 @@ struct PermuteParams {
     float* gate_rw;
     int32_t* u_idx;
     float* u_gate;
+    // shared experts read the activations in place (experts below this id see every token, in token
+    // order, so their block of xp would be a copy of x): their rows are numbered but not copied
+    int inplace_experts = 0;
     // expert-parallel peer mode (else null): expert_dst[e] is where this rank's rows for expert e
     // start, possibly in another GPU's memory; row (pos - expert_offset[e]) of that segment is written
     void* const* expert_dst;
@@ -158,6 +161,9 @@ struct GroupGemmParams {
     const int32_t* seg_start;
     void* const* seg_dst;
     int seg_per_expert;
+    // GEMM 1 of the tensor-core path: experts below this id take their A rows from the activations x
+    // themselves (row r of the expert = token r) through a second tensor map, instead of from A
+    int inplace_experts = 0;
 };
 
 // Where row `row` of expert `e` of a grouped GEMM's output goes.
@@ -203,7 +209,7 @@ int router_tc_e_pad(int e_router);       // padded router width of the tensor-co
 // splits w (FP32 [E_router][D]) into w3 (BF16 [3*e_pad][D]) and encodes its tensor map; 1 = ready, 0 = not offered, <0 error
 int router_tc_plan_set(RouterTcPlan*, const float* w, void* w3, int e_router, int D, cudaStream_t s);
 // may this call take the tensor-core router?  (BF16 activations, 16-byte aligned, no noise network armed)
-bool router_tc_usable(const RouterTcPlan*, const void* x, int x_dtype, bool noise_network_armed, int e_router, int D);
+bool router_tc_usable(const RouterTcPlan*, const void* x, int x_dtype, bool noise_network_armed, int e_router, int D, int64_t T);
 int launch_router_tc(const RouterTcPlan*, const RouterParams& p, int num_cta, int num_sms, int32_t* status, cudaStream_t s);
 // K-major BF16 matrix [rows][K] as a 2-D tensor map with boxes of 64 x box_rows and 128-byte swizzle
 bool tc_encode_bf16_2d(void* map, const void* base, uint64_t K, uint64_t rows, uint32_t box_rows);
@@ -217,6 +223,8 @@ void tc_plan_destroy(TcGemmPlan*);
 // (re)encodes the tensor maps; returns 0 or a negative MOE_ERR_* (message via out_msg)
 int tc_plan_encode(TcGemmPlan*, const void* xp, const void* h, int64_t P_cap, int D, int H, int O, int E,
                    const void* w1, const void* w3, const void* w2, const char** out_msg);
+// tensor map of this call's activations x [T][D] (BF16) for experts that read them in place; false if x does not qualify
+bool tc_plan_set_x(TcGemmPlan*, const void* x, int64_t T, int D);
 // stage 1: A = permuted rows, B = w1 (and w3 in mode 1); stage 2: A = hidden activations, B = w2.
 // mode 1: gated pair with act(gate)*up epilogue; mode 2: single matrix (+ bias, + activation).
 int launch_group_gemm_tc(const TcGemmPlan*, int stage, int mode, const GroupGemmParams& p, int max_tiles,

@@ -61,7 +61,8 @@ struct __align__(1024) SharedStorage {
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 group_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
-                     const __grid_constant__ CUtensorMap map_b1, const GroupGemmParams p, const int gm) {
+                     const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_x,
+                     const GroupGemmParams p, const int gm) {
     extern __shared__ uint8_t smem_raw[];
     SharedStorage* ss = reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                          ~(uintptr_t)1023);
@@ -103,13 +104,17 @@ group_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 const TileCoord t = decode_tile(L, n_tiles, gm, p.tile_prefix, p.expert_offset, p.E, BM);
                 const int brow0 = (MODE == 1) ? t.n_idx * 128 : t.n_idx * 256;
                 const int brow1 = (MODE == 1) ? t.n_idx * 128 : t.n_idx * 256 + 128;
+                // an expert that sees every token in token order reads the activations themselves
+                const bool inplace = t.e < p.inplace_experts;
+                const CUtensorMap* ma = inplace ? &map_x : &map_a;
+                const int arow = inplace ? t.row0 - p.expert_offset[t.e] : t.row0;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1u, &ss->abort_flag, p.status, DEV_TIMEOUT_SMEM_EMPTY)) {
                         ok = false;
                         break;
                     }
                     mbar_expect_tx(&ss->full_bar[stage], STAGE_TX_BYTES);
-                    tma_load_2d(ss->a[stage], &map_a, kb * BK, t.row0, &ss->full_bar[stage]);
+                    tma_load_2d(ss->a[stage], ma, kb * BK, arow, &ss->full_bar[stage]);
                     tma_load_3d(ss->b[stage], &map_b0, kb * BK, brow0, t.e, &ss->full_bar[stage]);
                     tma_load_3d(ss->b[stage] + B_HALF_BYTES, &map_b1, kb * BK, brow1, t.e, &ss->full_bar[stage]);
                     armed |= 1u << stage;
@@ -376,6 +381,11 @@ int tc_plan_encode(TcGemmPlan* plan, const void* xp, const void* h, int64_t P_ca
     return MOE_OK;
 }
 
+bool tc_plan_set_x(TcGemmPlan* plan, const void* x, int64_t T, int D) {
+    if (!plan || D % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || T < 1) return false;
+    return encode_map(&plan->map_x, x, (uint64_t)D, (uint64_t)T, 1, false);
+}
+
 int launch_group_gemm_tc(const TcGemmPlan* plan_c, int stage, int mode, const GroupGemmParams& p, int max_tiles,
                          int num_sms, cudaStream_t s) {
     TcGemmPlan* plan = const_cast<TcGemmPlan*>(plan_c);
@@ -393,11 +403,11 @@ int launch_group_gemm_tc(const TcGemmPlan* plan_c, int stage, int mode, const Gr
     const int gm = group_m_setting();
     const int grid = max_tiles < num_sms ? max_tiles : num_sms;
     if (mode == 1)
-        group_gemm_tc_kernel<1><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w3, p, gm);
+        group_gemm_tc_kernel<1><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w3, plan->map_x, p, gm);
     else if (stage == 1)
-        group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w1, p, gm);
+        group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w1, plan->map_x, p, gm);
     else
-        group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_h, plan->map_w2, plan->map_w2, p, gm);
+        group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_h, plan->map_w2, plan->map_w2, plan->map_h, p, gm);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 

@@ -126,7 +126,8 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
-                      const __grid_constant__ CUtensorMap map_b1, const GroupGemmParams p, const int gm) {
+                      const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_x,
+                      const GroupGemmParams p, const int gm) {
     extern __shared__ uint8_t smem_raw[];
     PairStorage* ss = reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -166,7 +167,10 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             uint32_t phase = 0;
             for (int L = tile0; L < total_tiles; L += tile_step) {
                 const TileCoord t = decode_tile(L, n_tiles, gm, p.tile_prefix, p.expert_offset, p.E, BM_PAIR);
-                const int arow = t.row0 + (int)rank * BM_CTA;
+                // an expert that sees every token in token order reads the activations themselves
+                const bool inplace = t.e < p.inplace_experts;
+                const CUtensorMap* ma = inplace ? &map_x : &map_a;
+                const int arow = t.row0 + (int)rank * BM_CTA - (inplace ? p.expert_offset[t.e] : 0);
                 // this CTA's half of the weight tile
                 const CUtensorMap* mb = (MODE == 1 && rank == 1) ? &map_b1 : &map_b0;
                 const int brow = (MODE == 1) ? t.n_idx * 128 : t.n_idx * 256 + (int)rank * 128;
@@ -178,7 +182,7 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     }
                     const uint32_t full_leader = map_to_cta(smem_u32(&ss->full_bar[stage]), 0);
                     if (leader) mbar_expect_tx(&ss->full_bar[stage], PAIR_TX_BYTES);
-                    tma2_load_2d(ss->a[stage], &map_a, kb * BK, arow, full_leader);
+                    tma2_load_2d(ss->a[stage], ma, kb * BK, arow, full_leader);
                     tma2_load_3d(ss->b[stage], mb, kb * BK, brow, t.e, full_leader);
                     if (++stage == STAGES) {
                         stage = 0;
@@ -349,11 +353,11 @@ int launch_group_gemm_tc2(const TcGemmPlan* plan_c, int stage, int mode, const G
     const int gm = group_m_setting();
     cudaError_t e;
     if (mode == 1)
-        e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<1>, plan->map_xp, plan->map_w1, plan->map_w3, p, gm);
+        e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<1>, plan->map_xp, plan->map_w1, plan->map_w3, plan->map_x, p, gm);
     else if (stage == 1)
-        e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<2>, plan->map_xp, plan->map_w1, plan->map_w1, p, gm);
+        e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<2>, plan->map_xp, plan->map_w1, plan->map_w1, plan->map_x, p, gm);
     else
-        e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<2>, plan->map_h, plan->map_w2, plan->map_w2, p, gm);
+        e = cudaLaunchKernelEx(&cfg, group_gemm_tc2_kernel<2>, plan->map_h, plan->map_w2, plan->map_w2, plan->map_h, p, gm);
     return e == cudaSuccess ? 1 : -1;
 }
 

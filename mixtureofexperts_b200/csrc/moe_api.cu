@@ -79,6 +79,7 @@ struct moe_layer {
     float* tc_logits = nullptr;     // workspace [T_cap][e_pad]
     int32_t* tc_recheck = nullptr;  // tokens re-evaluated with FP32 FMAs since creation
     bool router_tc_enabled = true;  // MOE_B200_ROUTER_TC=0 keeps the FP32-FMA router (comparison)
+    bool inplace_shared = true;     // MOE_B200_INPLACE_SHARED=0: shared experts' rows are copied by the permute too
     // AuxiliaryFreeLoss.update_bias! on the device (moe_layer_set_aux_free)
     bool aux_free = false;
     float aux_lr = 0.f, aux_momentum = 0.f;
@@ -311,7 +312,8 @@ int pick_tile_m(const moe_layer* L, int64_t rows, int n_experts) {
 // The grouped GEMM pair on `rows_cap` rows described by (expert_offset, tile_prefix).
 int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const int32_t* expert_offset,
                 const int32_t* tile_prefix, int64_t rows, int n_experts, cudaStream_t s, int ev_base, int tile_m,
-                const int32_t* seg_start = nullptr, void* const* seg_dst = nullptr, int seg_per_expert = 0) {
+                const int32_t* seg_start = nullptr, void* const* seg_dst = nullptr, int seg_per_expert = 0,
+                int inplace_experts = 0) {
     const moe_config_t& c = L->cfg;
     GroupGemmParams g{};
     g.E = n_experts;
@@ -340,6 +342,7 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.K = c.input_dim;
     g.bias = standard ? L->b1 : nullptr;
     g.epilogue_act = standard ? c.activation : -1;
+    g.inplace_experts = tc ? inplace_experts : 0;
     if (pair) n = launch_group_gemm_tc2(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
     else if (tc) n = launch_group_gemm_tc(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
     else n = launch_group_gemm_f32(g, mode1, max_mtiles, rows, L->num_sms, s);
@@ -352,6 +355,7 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.B1 = nullptr;
     g.bias = standard ? L->b2 : nullptr;
     g.epilogue_act = -1;
+    g.inplace_experts = 0;
     g.C = y_buf;
     g.N = c.output_dim;
     g.K = c.hidden_dim;
@@ -405,7 +409,7 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     // narrow rule (enough CTAs for every SM) whatever the router width
     const bool noise_net_armed = training && L->noise_scale > 0.f && L->noise && L->router_nw;
     const bool use_tc_router = L->router_tc_enabled && L->tc_logits != nullptr &&
-                               router_tc_usable(L->rplan, x, x_dtype, noise_net_armed, L->E_router, c.input_dim);
+                               router_tc_usable(L->rplan, x, x_dtype, noise_net_armed, L->E_router, c.input_dim, T);
     const int tokens_per_cta = router_tokens_per_cta(T, use_tc_router ? 8 : L->E_router, L->num_sms);
     const int num_cta = (int)((T + tokens_per_cta - 1) / tokens_per_cta);
     if (L->prof_slots > 0) L->prof_cur = (int)(L->prof_calls++ % L->prof_slots);
@@ -501,6 +505,13 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     pp.gate_rw = L->gate;
     pp.u_idx = opt->indices;
     pp.u_gate = opt->gates;
+    // Shared experts (ids 0..S-1 of SharedExpertGating / num_shared_experts) see every token in token
+    // order: on the tensor-core path GEMM 1 reads x itself for them and the permute copies nothing.
+    int inplace_experts = 0;
+    if (L->S > 0 && L->inplace_shared && !L->ep && capacity < 0 && c.compute_dtype == MOE_DTYPE_BF16 && x_dtype == MOE_DTYPE_BF16 && L->plan &&
+        tc_plan_set_x(L->plan, x, T, c.input_dim))
+        inplace_experts = L->S;
+    pp.inplace_experts = inplace_experts;
 
     int n = 0;
     if (num_cta > 0) {
@@ -532,7 +543,8 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     stage_mark(L, 3, s);
 
     if (!L->ep) {
-        if ((rc = run_experts(L, L->xp, L->h, L->y, L->expert_offset, L->tile_prefix, T * L->k_tot, L->E, s, 4, tile_m_local)))
+        if ((rc = run_experts(L, L->xp, L->h, L->y, L->expert_offset, L->tile_prefix, T * L->k_tot, L->E, s, 4, tile_m_local,
+                              nullptr, nullptr, 0, inplace_experts)))
             return rc;
     } else if (peer) {
         // flag barrier: every rank's permute kernel has written its rows into the owners' buffers
@@ -654,6 +666,7 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     if (const char* ev = getenv("MOE_B200_HOST_CHUNKS")) L->host_chunks = atoi(ev) > 0 ? atoi(ev) : 0;
     if (const char* ev = getenv("MOE_B200_HOST_TIMELINE")) L->host_timeline = atoi(ev) > 0;
     if (const char* ev = getenv("MOE_B200_ROUTER_TC")) L->router_tc_enabled = atoi(ev) != 0;
+    if (const char* ev = getenv("MOE_B200_INPLACE_SHARED")) L->inplace_shared = atoi(ev) != 0;
     auto cleanup = [&](int code) {
         moe_layer_destroy(L);
         return code;

@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
         int nd = 0;
         for (int j = 0; j < p.k_tot; ++j) {
             const int pos = s_pos[tl * p.k_tot + j];
-            if (pos < 0) continue;
+            if (pos < 0 || s_exp[tl * p.k_tot + j] < p.inplace_experts) continue;
             if (p.expert_dst) {
                 const int e = s_exp[tl * p.k_tot + j];
                 dst[nd++] = reinterpret_cast<PT*>(p.expert_dst[e]) + (size_t)(pos - p.expert_offset[e]) * p.D;

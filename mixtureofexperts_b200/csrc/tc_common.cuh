@@ -208,6 +208,7 @@ __device__ __forceinline__ void store_row32(__nv_bfloat16* dst_row, int col0, in
 // Tensor maps of one layer's grouped GEMM pair (rows in boxes of 64 x 128, weights 64 x 128 x 1).
 struct TcGemmPlan {
     CUtensorMap map_xp, map_h, map_w1, map_w3, map_w2;
+    CUtensorMap map_x;      // this call's activations, for experts that read them in place (tc_plan_set_x)
     bool valid = false;
     bool attr_set = false;
     bool attr2_set = false;
