@@ -75,6 +75,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
     return r;
 }
+// Raise the abort flag of the other CTA of the pair too, so that it leaves its loops at its next
+// check instead of when its own waits run out.
+__device__ __forceinline__ void raise_peer_abort(volatile int* my_flag, uint32_t my_rank) {
+    const uint32_t peer = map_to_cta(smem_u32(const_cast<int*>(my_flag)), my_rank ^ 1u);
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer), "r"(1u) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -165,6 +171,7 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
+            uint32_t armed = 0;   // bit s: this CTA has issued copies into stage s that nobody consumed yet
             for (int L = tile0; L < total_tiles; L += tile_step) {
                 const TileCoord t = decode_tile(L, n_tiles, gm, p.tile_prefix, p.expert_offset, p.E, BM_PAIR);
                 // an expert that sees every token in token order reads the activations themselves
@@ -184,12 +191,32 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (leader) mbar_expect_tx(&ss->full_bar[stage], PAIR_TX_BYTES);
                     tma2_load_2d(ss->a[stage], ma, kb * BK, arow, full_leader);
                     tma2_load_3d(ss->b[stage], mb, kb * BK, brow, t.e, full_leader);
+                    armed |= 1u << stage;
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
+            }
+            if (ss->abort_flag) {
+                // Leaving early: tell the other CTA, then give the copies already issued a bounded time to
+                // land so that none is still writing this CTA's shared memory when it exits.  The leader can
+                // watch its full barriers (both CTAs' copies complete there); the peer has no barrier of its
+                // own for them and simply waits out the limit.
+                raise_peer_abort(&ss->abort_flag, rank);
+                const unsigned long long t0 = globaltimer_ns();
+                if (leader) {
+                    for (int s2 = 0; s2 < STAGES; ++s2) {
+                        if (!(armed & (1u << s2))) continue;
+                        const uint32_t par = (s2 < stage) ? phase : (phase ^ 1u);
+                        while (!mbar_try_wait(&ss->full_bar[s2], par) && globaltimer_ns() - t0 < DRAIN_LIMIT_NS) {
+                        }
+                    }
+                } else if (armed) {
+                    while (globaltimer_ns() - t0 < DRAIN_LIMIT_NS) {
+                    }
+                }
             }
         }
     } else if (warp == 1) {
@@ -229,6 +256,7 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     aphase ^= 1u;
                 }
             }
+            if (ss->abort_flag) raise_peer_abort(&ss->abort_flag, rank);
         }
     } else {
         // ------------------------------ epilogue (warps 2..5 of each CTA) ----------------------
@@ -295,6 +323,7 @@ group_gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 aphase ^= 1u;
             }
         }
+        if (lane == 0 && ss->abort_flag) raise_peer_abort(&ss->abort_flag, rank);
     }
 
     // ------------------------------ teardown --------------------------------------------------
