@@ -547,11 +547,18 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
     torch.cuda.set_device(local_rank)
     device = f"cuda:{local_rank}"
+    from mixtureofexperts_b200 import parallel
+
+    # one process per GPU: run on the CPUs next to this GPU so the pinned buffers of the end-to-end leg
+    # are allocated in the memory closest to it (MOE_B200_NUMA_BIND=0 leaves the affinity alone)
+    numa = {"node": -1, "why": "MOE_B200_NUMA_BIND=0"}
+    if os.environ.get("MOE_B200_NUMA_BIND", "1") != "0":
+        props = torch.cuda.get_device_properties(local_rank)
+        numa = parallel.bind_to_gpu_numa_node(f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0")
     ep = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(device))
-        from mixtureofexperts_b200 import parallel
 
         uid = parallel.broadcast_unique_id(dist, rank, device)
         ep = (rank, world, uid)
@@ -605,7 +612,8 @@ def main():
             dt = float(t.item())
         e2e = {"value": T * world / dt, "unit": "tokens/s", "h2d_bytes_per_step": T * D * xh.element_size(),
                "d2h_bytes_per_step": T * O * 4 + 4, "ms_per_step": dt * 1e3,
-               "timing": "host clock around synchronous moe_layer_forward_host calls (pinned buffers), max over ranks"}
+               "timing": "host clock around synchronous moe_layer_forward_host calls (pinned buffers), max over ranks",
+               "numa_rank0": numa}
         del xh, oh
 
     # ---- parity of what was just timed (outside the timed regions) --------------------------

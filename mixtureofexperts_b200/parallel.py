@@ -18,6 +18,48 @@ def expert_partition(num_experts: int, world: int, rank: int) -> range:
     return range(rank * per, (rank + 1) * per)
 
 
+def _parse_cpulist(text: str) -> set:
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_to_gpu_numa_node(pci_bus_id: str, sysfs: str = "/sys") -> dict:
+    """Pin the calling process to the CPUs of the NUMA node its GPU hangs off, so that the pinned
+    host buffers it allocates next are first-touched in the memory closest to that GPU's PCIe
+    root.  With one process per GPU and all GPUs copying at once, buffers on the far socket halve
+    the host-copy rate.  ``pci_bus_id`` is "domain:bus:device.function" as CUDA reports it.
+
+    Returns {"node": n, "cpus": count} on success; {"node": -1, "why": ...} and no change when the
+    node is unknown (virtualised PCI topology), the CPU list is empty, or the process may not use
+    those CPUs (a cgroup cpuset)."""
+    import os
+
+    dev = pci_bus_id.lower()
+    if dev.count(":") == 1:
+        dev = "0000:" + dev
+    if len(dev.split(":")[0]) > 4:      # CUDA prints an 8-digit domain, sysfs a 4-digit one
+        dev = dev.split(":")[0][-4:] + dev[dev.index(":"):]
+    try:
+        with open(f"{sysfs}/bus/pci/devices/{dev}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"node": -1, "why": "sysfs reports no NUMA node for the GPU"}
+        with open(f"{sysfs}/devices/system/node/node{node}/cpulist") as f:
+            cpus = _parse_cpulist(f.read())
+    except (OSError, ValueError) as exc:
+        return {"node": -1, "why": f"{type(exc).__name__}: {exc}"}
+    allowed = cpus & os.sched_getaffinity(0)
+    if not allowed:
+        return {"node": -1, "why": "none of the node's CPUs are in this process's affinity mask"}
+    os.sched_setaffinity(0, allowed)
+    return {"node": node, "cpus": len(allowed)}
+
+
 def new_unique_id() -> bytes:
     buf = C.create_string_buffer(128)
     _lib.check(_lib.lib.moe_ep_unique_id(buf))

@@ -255,3 +255,35 @@ def test_count_vectors_that_disagree_with_what_was_posted_are_refused(lib_built)
         assert p.exitcode == 0
     results = dict(q.get(timeout=5) for _ in range(2))
     assert results[0] == "ok" and results[1] == _lib.ERR_NCCL
+
+
+def test_numa_binding_reads_sysfs_and_leaves_unknown_topologies_alone(tmp_path):
+    """bind_to_gpu_numa_node: the node's CPU list (restricted to what the process may use) becomes
+    the affinity mask; an unknown node, a missing device or a foreign CPU list changes nothing."""
+    import os
+
+    from mixtureofexperts_b200 import parallel
+
+    before = os.sched_getaffinity(0)
+    try:
+        dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+        dev.mkdir(parents=True)
+        node = tmp_path / "devices/system/node/node1"
+        node.mkdir(parents=True)
+        mine = sorted(before)
+        keep = mine[: max(1, len(mine) // 2)]
+        (dev / "numa_node").write_text("1\n")
+        (node / "cpulist").write_text(",".join(str(c) for c in keep) + ",100000-100003\n")
+        got = parallel.bind_to_gpu_numa_node("00000000:1B:00.0", sysfs=str(tmp_path))
+        assert got == {"node": 1, "cpus": len(keep)}
+        assert os.sched_getaffinity(0) == set(keep)
+        os.sched_setaffinity(0, before)
+        (dev / "numa_node").write_text("-1\n")
+        assert parallel.bind_to_gpu_numa_node("0000:1b:00.0", sysfs=str(tmp_path))["node"] == -1
+        assert parallel.bind_to_gpu_numa_node("0000:99:00.0", sysfs=str(tmp_path))["node"] == -1
+        (dev / "numa_node").write_text("1\n")
+        (node / "cpulist").write_text("100000-100003\n")
+        assert parallel.bind_to_gpu_numa_node("1b:00.0", sysfs=str(tmp_path))["node"] == -1
+        assert os.sched_getaffinity(0) == before
+    finally:
+        os.sched_setaffinity(0, before)
