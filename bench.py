@@ -22,7 +22,8 @@ Keys of the line beyond the usual ones:
   cpu_baseline    the CPU restatement of the reference path on the host cores, same token count
   parity          outside the timed region: every rank compares its tokens' expert ids (all local
                   tokens), a sample of outputs and the global loss with the CPU oracle
-  other_workloads c1 and c4 measured after the timed region (N=1 only)
+  other_workloads c1 and c4 measured after the timed region, and the per-position / per-prompt host
+                  calls of the Llama2 MoE FFN (c2) (N=1 only)
 """
 from __future__ import annotations
 
@@ -46,6 +47,8 @@ WORKLOADS = {
                desc="DeepSeek-style layer: 64 routed + 2 shared GatedExperts d=2048 hidden=1408 top-6 BF16, 32768 tokens, skewed"),
     "c1": dict(E=8, S=0, k=2, D=512, H=2048, O=512, T=32, dtype="f32", std=0.05, bias_std=0.0,
                desc="8 GatedExperts 512/2048/512 top-2 FP32, 32 tokens"),
+    "c2": dict(E=8, S=0, k=2, D=512, H=1376, O=512, T=64, dtype="f32", std=0.02, bias_std=0.0,
+               desc="MoE FFN of a converted Llama2 layer (dim 512, hidden 1376, 8 experts, top-2, FP32), 64 positions"),
 }
 SEED = 1234
 ALPHA, ZW = 0.01, 0.001
@@ -393,12 +396,20 @@ def parity_block(w, layer, x, torch, rank, world, dist, device, n_sample=96):
 # GPU measurement of one workload
 # --------------------------------------------------------------------------------------------------
 
-def measure_device(layer, x, out, steps, warmup, torch, barrier, sampler=None):
-    """W untimed + K timed forwards with x resident in HBM; CUDA events on the launching stream."""
+def measure_device(layer, x, out, steps, warmup, torch, barrier, sampler=None, stages_apart=False):
+    """W untimed + K timed forwards with x resident in HBM; CUDA events on the launching stream.
+    The per-stage events are recorded inside the timed steps, except with ``stages_apart`` (steps of a
+    tenth of a millisecond, where seven event records per step would be a large part of what is timed
+    and would keep the library from replaying its graph): then the K steps are timed bare, each step
+    being the one C call moe_layer_forward with its arguments bound beforehand (MoELayer.bind_forward:
+    the argument checks and allocations of the Python mirror's __call__ take longer than such a step),
+    and the stage times come from K more steps after them."""
+    step = (lambda: layer(x.t(), training=True, out=out)) if not stages_apart else layer.bind_forward(x.t(), out, training=True)
     for _ in range(warmup):
-        layer(x.t(), training=True, out=out)
+        step()
     barrier()
-    layer.set_profiling(min(steps, 1024))
+    if not stages_apart:
+        layer.set_profiling(min(steps, 1024))
     launches0 = layer.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -406,13 +417,18 @@ def measure_device(layer, x, out, steps, warmup, torch, barrier, sampler=None):
     ev0.record()
     loss = None
     for _ in range(steps):
-        _, loss = layer(x.t(), training=True, out=out)
+        _, loss = step()
     ev1.record()
     barrier()
     t_mark1 = sampler.mark() if sampler else None
     ms_total = ev0.elapsed_time(ev1)
     launches = layer.launch_count() - launches0
     n_prof = min(steps, 1024)
+    if stages_apart:
+        layer.set_profiling(n_prof)
+        for _ in range(n_prof):
+            layer(x.t(), training=True, out=out)
+        barrier()
     stages = {}
     for back in range(n_prof):
         for k_, v in layer.stage_ms(back).items():
@@ -479,12 +495,18 @@ def measure_other(name, torch, peaks, steps=10, warmup=3):
     def barrier():
         torch.cuda.synchronize()
 
-    ms_total, launches, stages, loss, _ = measure_device(layer, x, out, steps, warmup, torch, barrier)
+    replays0 = layer.graph_replays()
+    ms_total, launches, stages, loss, _ = measure_device(layer, x, out, steps, warmup, torch, barrier,
+                                                         stages_apart=w["dtype"] == "f32")
+    replays = layer.graph_replays() - replays0
     ms_step = ms_total / steps
     res = {"workload": f"{name}: {w['desc']}", "ms_per_step": ms_step, "tokens_per_s": T / (ms_step * 1e-3),
            "steps": steps, "warmup": warmup, "stage_ms": stages, "gpu_launches": launches,
            "roofline": roofline_of(w, name, T, stages, ms_step, peaks, layer.tile_rows(T), 1, None, True),
-           "loss": float(loss.item()), "device_status": layer.device_status()}
+           "loss": float(loss.item()), "device_status": layer.device_status(), "graph_replays": replays}
+    if w["dtype"] == "f32":
+        res["timing_note"] = ("ms_per_step: bare moe_layer_forward calls with bound arguments (the library replays one captured "
+                              "CUDA graph per step); stage_ms: the same steps launched kernel by kernel with an event after each")
     if flush is not None:
         # the FP32 workload's weights fit in L2: time it again with L2 flushed before every step
         layer.set_profiling(steps)
@@ -508,13 +530,69 @@ def measure_other(name, torch, peaks, steps=10, warmup=3):
     return res
 
 
+def measure_llama_ffn(torch, peaks, calls=300, warmup=100):
+    """The MoE FFN of a converted Llama2 layer as the generation loop drives it: one host call of
+    moe_layer_forward_host per position (decode, T = 1) and one call for a whole 64-token prompt
+    (prefill), host buffers in and out, synchronous; per-call wall time with the library's graph
+    replay on and off.  Calls go straight to the C entry point with prebuilt arguments."""
+    import ctypes as C
+
+    import numpy as np
+
+    from mixtureofexperts_b200 import _lib
+
+    w = dict(WORKLOADS["c2"])
+    res = {"workload": f"c2: {w['desc']}", "calls": calls, "warmup": warmup,
+           "timing": "host clock around synchronous moe_layer_forward_host calls (pageable NumPy buffers), inference"}
+    rng = np.random.default_rng(SEED + 2)
+    for graphs in (1, 0):
+        old = os.environ.get("MOE_B200_GRAPHS")
+        os.environ["MOE_B200_GRAPHS"] = str(graphs)
+        try:
+            layer = build_layer(w, torch, 0)
+        finally:
+            if old is None:
+                del os.environ["MOE_B200_GRAPHS"]
+            else:
+                os.environ["MOE_B200_GRAPHS"] = old
+        for T, label in ((1, "decode_us_per_position"), (w["T"], "prefill_us_per_64_positions")):
+            x = np.ascontiguousarray(rng.standard_normal((T, w["D"])).astype(np.float32))
+            out = np.empty((T, w["O"]), dtype=np.float32)
+            loss = np.zeros(1, dtype=np.float32)
+            o = _lib.ForwardOutputs()
+            o.loss = loss.ctypes.data
+            args = (layer._handle, x.ctypes.data, _lib.DTYPE_F32, T, 0, out.ctypes.data, C.byref(o))
+            for _ in range(warmup):
+                _lib.check(_lib.lib.moe_layer_forward_host(*args))
+            launches0, replays0 = layer.launch_count(), layer.graph_replays()
+            t0 = time.perf_counter()
+            for _ in range(calls):
+                rc = _lib.lib.moe_layer_forward_host(*args)
+            dt = time.perf_counter() - t0
+            _lib.check(rc)
+            key = label + ("" if graphs else "_graphs_off")
+            res[key] = dt / calls * 1e6
+            if graphs:
+                res[label.split("_us_")[0] + "_launches_per_call"] = (layer.launch_count() - launches0) / calls
+                res[label.split("_us_")[0] + "_graph_replays"] = layer.graph_replays() - replays0
+                res[label.split("_us_")[0] + "_output_finite"] = bool(np.isfinite(out).all())
+        res["device_status"] = layer.device_status()
+        layer.close()
+    # two experts' weights are touched per position: 2 * 4 * H * (2D + O) bytes
+    nbytes = 2 * 4.0 * w["H"] * (2 * w["D"] + w["O"])
+    res["decode_weight_stream_gbs"] = nbytes / (res["decode_us_per_position"] * 1e-6) / 1e9
+    res["decode_note"] = (f"{nbytes / 1e6:.1f} MB of expert weights per position = {nbytes / peaks['hbm_gbs'] / 1e3:.1f} us at the "
+                          "measured HBM rate: the call is bound by launches, copies and the synchronisation, not by the stream")
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS))
+    ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(n for n in WORKLOADS if n != "c2"))
     ap.add_argument("--tokens", type=int, default=0, help="override the tokens per GPU (profiling of small cases)")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling of small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -579,7 +657,8 @@ def main():
     sampler = ClockSampler(str(torch.cuda.get_device_properties(local_rank).uuid))
     if rank == 0:
         sampler.start()
-    ms_total, launches, stages, loss, marks = measure_device(layer, x, out, args.steps, args.warmup, torch, barrier, sampler)
+    ms_total, launches, stages, loss, marks = measure_device(layer, x, out, args.steps, args.warmup, torch, barrier, sampler,
+                                                             stages_apart=w["dtype"] == "f32")
     clocks = sampler.stop(*marks) if rank == 0 else None
     status = layer.device_status()
     if world > 1:
@@ -637,6 +716,7 @@ def main():
         if world == 1 and not args.no_others and full_size:
             torch.cuda.empty_cache()
             others = {n: measure_other(n, torch, peaks) for n in ("c4", "c1") if n != name}
+            others["c2"] = measure_llama_ffn(torch, peaks)
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,

@@ -38,6 +38,8 @@
  *                              read from the activations in place (comparison; read at handle creation)
  *   MOE_B200_ROUTER_TC=0       keep the FP32-FMA router kernel for wide routers too (comparison; read at
  *                              handle creation)
+ *   MOE_B200_GRAPHS=0          small batches launch their kernels one by one instead of replaying a captured
+ *                              CUDA graph (comparison; read at handle creation)
  *   MOE_B200_EP_MODE=nccl      expert parallelism moves token rows with ncclSend/ncclRecv instead of
  *                              peer stores from the library's own kernels (read by moe_ep_init)
  */
@@ -255,6 +257,17 @@ int64_t moe_layer_launch_count(const moe_layer_t*);
  * receives how many tokens were re-evaluated through this handle since creation (0 for layers
  * that never take that path).  A diagnostic without counterpart in the reference; synchronises. */
 int moe_layer_router_rechecks(moe_layer_t*, int64_t* tokens);
+
+/* Small batches (T * selected experts per token <= 4096, no expert parallelism, no device bias
+ * update, profiling off): the second forward call with the same arguments -- x, out and optional
+ * output pointers, T, dtype, training flag, noise buffer -- is captured into a CUDA graph on a
+ * stream of the handle and that call and later ones replay it on the caller's stream (one
+ * launch instead of six; results are those of the same kernels).  A replay reads the buffers'
+ * current contents.  Setters, workspace growth and moe_layer_set_profiling drop the graphs;
+ * calls made while the caller's stream is itself being captured launch plainly into that
+ * capture.  *replays receives the number of forward calls served by a replay since creation.
+ * No counterpart in the reference. */
+int moe_layer_graph_replays(const moe_layer_t*, int64_t* replays);
 
 /* Value of the device status word after the last synchronising call (0 = clean). */
 int moe_layer_device_status(moe_layer_t*, int32_t* status);

@@ -140,23 +140,31 @@ __global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemm
 
 // ---- few rows per expert (decode, tiny batches): stream the weights once ------------------------
 // Bound: HBM, E*N*K*4 bytes of weights per GEMM.  A persistent CTA per SM walks work items (expert,
-// block of 16 output columns, pass of up to 16 of the expert's rows); a producer thread streams each
-// item as K tiles of 256 floats through a 4-stage shared-memory ring with TMA tensor loads (one
-// 16 x 256 box per weight matrix and one for the activation rows per stage, completion on an
+// block of 32 output columns, pass of up to 16 of the expert's rows); a producer thread streams each
+// item as K tiles of 128 floats through a 4-stage shared-memory ring with TMA tensor loads (one
+// 32 x 128 box per weight matrix and one 16 x 128 box of activation rows per stage, completion on an
 // mbarrier; 1-D bulk copies, one per row piece, were tried first and were bound by the ~50 ns the
-// TMA unit spends per copy), so ~190 KB per SM are in flight whatever the consumers do.
-// Eight consumer warps own two columns each (sixteen warps with one column each were no faster);
-// lanes split a K tile in 16-byte pieces (conflict-free shared-memory reads), keep (matrices x 2
-// columns x 16 rows) accumulators in registers over the whole K loop, rows taken in groups of four,
-// and finish with one multi-value butterfly (31 shuffles for 32 sums, fixed order) that leaves lane
-// l with the sum for (column l / 16, row l % 16).  Every wait is bounded like in
-// the tensor-core kernels.
-constexpr int ST_COLS = 16;          // output columns per work item
+// TMA unit spends per copy), so ~160 KB per SM are in flight whatever the consumers do.
+// Eight consumer warps own four columns each.  Lanes split a K tile in 16-byte pieces (conflict-free
+// shared-memory reads), keep (matrices x 4 columns x 16 rows) accumulators in registers over the
+// whole K loop, rows taken in groups of four, and finish with multi-value butterflies (31 shuffles
+// for 32 sums, fixed order) that leave lane l with the sum for (column l / 16, row l % 16) of a
+// column pair.  With two columns a warp the kernel was bound by shared-memory reads (every warp
+// reads the whole activation tile of a stage: four bytes of it per weight byte) and packed
+// two-wide FMAs changed nothing; one column a warp on sixteen warps was no faster either.  Every
+// wait is bounded like in the tensor-core kernels.
+constexpr int ST_CW = 4;             // output columns per consumer warp
+constexpr int ST_COLS = 32;          // output columns per work item (8 consumer warps)
 constexpr int ST_ROWS = 16;          // rows of an expert per pass
-constexpr int ST_KT = 256;           // floats of K per ring stage
+constexpr int ST_KT = 128;           // floats of K per ring stage: one float4 per lane
 constexpr int ST_STAGES = 4;
 constexpr int ST_CONSUMER_WARPS = 8;
-constexpr int ST_THREADS = (ST_CONSUMER_WARPS + 1) * 32;
+// Three warpgroups: two of consumers, one whose first warp is the producer.  Registers are handed
+// over at the start (setmaxnreg works on whole warpgroups): the producer group keeps 40 a thread,
+// the consumers grow to 232, enough for the 128 accumulators, 8 weight and 4 activation vectors.
+constexpr int ST_THREADS = (ST_CONSUMER_WARPS + 4) * 32;
+constexpr int ST_REGS_PRODUCER = 40;
+constexpr int ST_REGS_CONSUMER = 232;
 
 template <int NB>
 struct __align__(128) StreamStage {
@@ -169,6 +177,7 @@ struct __align__(128) StreamStorage {
     uint64_t full_bar[ST_STAGES];
     uint64_t empty_bar[ST_STAGES];
     volatile int abort_flag;
+    int expert_offset[MAX_EXPERTS + 1];   // read once: a global load per work item would sit on every item's critical path
 };
 
 __device__ __forceinline__ float dot4(const float4 a, const float4 b, float acc) {
@@ -219,17 +228,20 @@ group_gemm_f32_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    for (int e = threadIdx.x; e <= p.E; e += ST_THREADS) ss->expert_offset[e] = p.expert_offset[e];
     __syncthreads();
 
     int stage = 0;
     uint32_t phase = 0;
-    if (warp == ST_CONSUMER_WARPS) {
+    if (warp >= ST_CONSUMER_WARPS) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ST_REGS_PRODUCER));
+        if (warp > ST_CONSUMER_WARPS) return;   // the group's other warps only give their registers away
         // ------------------------------ producer ----------------------------------------------
         uint32_t armed = 0;
         bool ok = true;
         for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
             const int e = item / ncb, n0 = (item % ncb) * ST_COLS;
-            const int row_begin = p.expert_offset[e], row_end = p.expert_offset[e + 1];
+            const int row_begin = ss->expert_offset[e], row_end = ss->expert_offset[e + 1];
             for (int r0 = row_begin; ok && r0 < row_end; r0 += ST_ROWS) {
                 for (int kt = 0; kt < nkt; ++kt) {
                     int go = 1;
@@ -269,19 +281,26 @@ group_gemm_f32_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __
         return;
     }
 
-    // ------------------------------ consumers (warps 0..7): columns 2w, 2w+1 of the item -----------
-    const int c_lo = warp * 2;
+    // ------------------------------ consumers (warps 0..7): columns 4w .. 4w+3 of the item ----------
+    // Shared memory bandwidth is what the consumers live on: every warp reads the whole activation tile
+    // of a stage, so the more columns a warp owns the less of it is read per weight.  Four columns of
+    // both matrices against sixteen rows are 128 accumulators a lane, which is what the registers taken
+    // over from the producer group pay for.
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(ST_REGS_CONSUMER));
+    const int c_lo = warp * ST_CW;
     bool alive = true;
     for (int item = blockIdx.x; alive && item < num_items; item += gridDim.x) {
         const int e = item / ncb, n0 = (item % ncb) * ST_COLS;
-        const int row_begin = p.expert_offset[e], row_end = p.expert_offset[e + 1];
+        const int row_begin = ss->expert_offset[e], row_end = ss->expert_offset[e + 1];
         for (int r0 = row_begin; alive && r0 < row_end; r0 += ST_ROWS) {
             const int rc = min(ST_ROWS, row_end - r0);
-            float acc[NB][32];                       // [matrix][column (0/1) * 16 + row]
+            float acc[NB][ST_CW / 2][32];            // [matrix][column pair][column (0/1) * 16 + row]
 #pragma unroll
             for (int b = 0; b < NB; ++b)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[b][i] = 0.f;
+                for (int c = 0; c < ST_CW / 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[b][c][i] = 0.f;
             for (int kt = 0; kt < nkt; ++kt) {
                 int ready = 1;
                 if (lane == 0) ready = tc::mbar_wait(&ss->full_bar[stage], phase, &ss->abort_flag, p.status, DEV_TIMEOUT_TMA_FULL);
@@ -293,34 +312,29 @@ group_gemm_f32_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __
                 while (!tc::mbar_try_wait(&ss->full_bar[stage], phase)) {
                 }  // already complete: gives every lane its own acquire
                 const StreamStage<NB>& st = ss->st[stage];
-                const int klen = min(ST_KT, p.K - kt * ST_KT);
+                const int k = lane * 4;
+                if (k < p.K - kt * ST_KT) {
+                    float4 w[NB][ST_CW];
 #pragma unroll
-                for (int piece = 0; piece < ST_KT / 128; ++piece) {
-                    const int k = piece * 128 + lane * 4;
-                    if (k < klen) {
-                        float4 w[NB][2];
+                    for (int b = 0; b < NB; ++b)
 #pragma unroll
-                        for (int b = 0; b < NB; ++b) {
-                            w[b][0] = *reinterpret_cast<const float4*>(&st.w[b][c_lo][k]);
-                            w[b][1] = *reinterpret_cast<const float4*>(&st.w[b][c_lo + 1][k]);
-                        }
-                        // rows in groups of four (a group past the pass's rows is skipped as a whole; rows past
-                        // rc inside a group hold other experts' rows and their sums are never stored)
+                        for (int c = 0; c < ST_CW; ++c) w[b][c] = *reinterpret_cast<const float4*>(&st.w[b][c_lo + c][k]);
+                    // rows in groups of four (a group past the pass's rows is skipped as a whole; rows past
+                    // rc inside a group hold other experts' rows and their sums are never stored)
 #pragma unroll
-                        for (int g = 0; g < ST_ROWS / 4; ++g) {
-                            if (g * 4 < rc) {
-                                float4 xv[4];
+                    for (int g = 0; g < ST_ROWS / 4; ++g) {
+                        if (g * 4 < rc) {
+                            float4 xv[4];
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) xv[q] = *reinterpret_cast<const float4*>(&st.x[g * 4 + q][k]);
+                            for (int q = 0; q < 4; ++q) xv[q] = *reinterpret_cast<const float4*>(&st.x[g * 4 + q][k]);
 #pragma unroll
-                                for (int q = 0; q < 4; ++q) {
-                                    const int r = g * 4 + q;
+                            for (int q = 0; q < 4; ++q) {
+                                const int r = g * 4 + q;
 #pragma unroll
-                                    for (int b = 0; b < NB; ++b) {
-                                        acc[b][r] = dot4(w[b][0], xv[q], acc[b][r]);
-                                        acc[b][16 + r] = dot4(w[b][1], xv[q], acc[b][16 + r]);
-                                    }
-                                }
+                                for (int b = 0; b < NB; ++b)
+#pragma unroll
+                                    for (int c = 0; c < ST_CW; ++c)
+                                        acc[b][c >> 1][(c & 1) * 16 + r] = dot4(w[b][c], xv[q], acc[b][c >> 1][(c & 1) * 16 + r]);
                             }
                         }
                     }
@@ -334,19 +348,22 @@ group_gemm_f32_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __
             }
             if (!alive) break;
 #pragma unroll
-            for (int b = 0; b < NB; ++b) warp_reduce32(acc[b], lane);
-            // lane l now holds (column c_lo + l / 16, row r0 + l % 16)
-            const int n = n0 + c_lo + (lane >> 4), row = r0 + (lane & 15);
-            if (n < p.N && (lane & 15) < rc) {
-                float v;
-                if (MODE == 1) {
-                    v = apply_act(p.activation, acc[0][0]) * acc[NB - 1][0];
-                } else {
-                    v = acc[0][0];
-                    if (p.bias) v += p.bias[(size_t)e * p.N + n];
-                    if (p.epilogue_act >= 0) v = apply_act(p.epilogue_act, v);
+            for (int c = 0; c < ST_CW / 2; ++c) {
+#pragma unroll
+                for (int b = 0; b < NB; ++b) warp_reduce32(acc[b][c], lane);
+                // lane l now holds (column c_lo + 2c + l / 16, row r0 + l % 16)
+                const int n = n0 + c_lo + 2 * c + (lane >> 4), row = r0 + (lane & 15);
+                if (n < p.N && (lane & 15) < rc) {
+                    float v;
+                    if (MODE == 1) {
+                        v = apply_act(p.activation, acc[0][c][0]) * acc[NB - 1][c][0];
+                    } else {
+                        v = acc[0][c][0];
+                        if (p.bias) v += p.bias[(size_t)e * p.N + n];
+                        if (p.epilogue_act >= 0) v = apply_act(p.epilogue_act, v);
+                    }
+                    group_gemm_out_row<float>(p, e, row)[n] = v;
                 }
-                group_gemm_out_row<float>(p, e, row)[n] = v;
             }
         }
     }

@@ -124,6 +124,12 @@ struct moe_layer {
     size_t hout_bytes = 0;
     void* hopt = nullptr;
     size_t hopt_bytes = 0;
+    // pinned host staging of small host calls: [status word, padded to 256 | x | out | optional outputs].
+    // Copies between pageable memory and the device block the host one by one; through this block a
+    // small call is one copy in, three copies out and a single wait.
+    char* pin = nullptr;
+    size_t pin_bytes = 0;
+    static constexpr size_t PIN_SMALL_CALL = 1 << 20;   // calls moving no more than this go through `pin`
     // chunked host calls: copy-in / compute / copy-out overlap on three streams
     static constexpr int MAX_CHUNKS = 8;
     cudaStream_t s_in = nullptr, s_out = nullptr;
@@ -143,6 +149,34 @@ struct moe_layer {
 
     EpState* ep = nullptr;
     int ep_timeout_ms = 0;          // moe_ep_set_timeout_ms before moe_ep_init; 0 = default
+
+    // Small batches: a forward call is a chain of six short launches whose host cost is larger than
+    // their device time.  The second call with the same arguments (pointers, T, flags) is captured
+    // into a CUDA graph on the handle's own stream and later calls replay it on the caller's stream.
+    struct GraphEntry {
+        const void* x = nullptr;
+        int x_dtype = 0;
+        int64_t T = 0;
+        int training = 0;
+        float* out = nullptr;
+        moe_forward_outputs_t opt = {};   // loss / tokens_per_expert / routing_entropy: only whether they are wanted
+        const float* noise = nullptr;
+        float noise_scale = 0.f;
+        cudaGraphExec_t exec = nullptr;
+        bool refused = false;       // capture failed once: this key stays on plain launches
+        int launches = 0;           // kernels inside the graph
+        uint64_t tick = 0;          // last use (least recently used entry is replaced)
+    };
+    static constexpr int MAX_GRAPHS = 16;
+    static constexpr int64_t GRAPH_MAX_PAIRS = 4096;   // T * k_tot above this: launches are no longer the cost
+    std::vector<GraphEntry> graphs;
+    // a graph writes loss, entropy and the per-expert counts into this block of the handle, and one
+    // small kernel after the replay hands them to the caller's pointers (callers allocate those
+    // afresh for every call, so they cannot be part of the key): [loss, entropy, pad, pad | int64 counts[E]]
+    float* graph_small = nullptr;
+    uint64_t graph_tick = 0;
+    int64_t graph_replays = 0;
+    bool graphs_enabled = true;     // MOE_B200_GRAPHS = 0: every call launches its kernels one by one
 
     // experiment switches of the environment, read once when the handle is created
     int force_pair = -1;            // MOE_B200_PAIR = 0 / 1: force single-CTA / CTA-pair GEMM kernels
@@ -211,7 +245,19 @@ int ensure_weights(moe_layer* L) {
     return MOE_OK;
 }
 
+// Graphs hold the addresses and kernel arguments of the call they were captured from: whatever
+// changes the workspace or the layer's routing state drops them (callers synchronise first).
+void drop_graphs(moe_layer* L) {
+    bool any = false;
+    for (auto& g : L->graphs) any = any || g.exec;
+    if (any) cudaDeviceSynchronize();   // a replay may still be running on a caller's stream
+    for (auto& g : L->graphs)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    L->graphs.clear();
+}
+
 void free_workspace(moe_layer* L) {
+    drop_graphs(L);
     dev_free(L->idx);
     dev_free(L->gate);
     dev_free(L->pair_pos);
@@ -617,6 +663,117 @@ int forward_device(moe_layer* L, const void* x, int x_dtype, int64_t T, int trai
     return MOE_OK;
 }
 
+__global__ void graph_small_outputs_kernel(const float* __restrict__ block, int E, float* loss, float* entropy,
+                                           int64_t* tokens_per_expert) {
+    const int i = threadIdx.x;
+    if (i == 0 && loss) *loss = block[0];
+    if (i == 0 && entropy) *entropy = block[1];
+    if (tokens_per_expert) {
+        const int64_t* counts = reinterpret_cast<const int64_t*>(block + 4);
+        for (int e = i; e < E; e += blockDim.x) tokens_per_expert[e] = counts[e];
+    }
+}
+
+int replay_graph(moe_layer* L, const moe_layer::GraphEntry& e, const moe_forward_outputs_t& o, cudaStream_t s) {
+    CUDA_TRY(cudaGraphLaunch(e.exec, s));
+    L->launches += e.launches;
+    if (o.loss || o.routing_entropy || o.tokens_per_expert) {
+        graph_small_outputs_kernel<<<1, 128, 0, s>>>(L->graph_small, L->E, o.loss, o.routing_entropy, o.tokens_per_expert);
+        CUDA_TRY(cudaGetLastError());
+        L->launches += 1;
+    }
+    ++L->graph_replays;
+    return MOE_OK;
+}
+
+// Forward for batches small enough that launching costs more than computing: plain launches on
+// the first call with a set of arguments, capture on the second, replay from then on.  The graph
+// reads the same buffers as the launches would, so new contents of x (or of the noise buffer) are
+// seen by a replay; anything else that differs makes a different key.
+int forward_small(moe_layer* L, const void* x, int x_dtype, int64_t T, int training, float* out,
+                  const moe_forward_outputs_t* opt, cudaStream_t s) {
+    static const moe_forward_outputs_t none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    const moe_forward_outputs_t& o = opt ? *opt : none;
+    const bool eligible = L->graphs_enabled && !L->ep && T > 0 && T * (int64_t)L->k_tot <= moe_layer::GRAPH_MAX_PAIRS &&
+                          L->prof_slots == 0 && !(L->aux_free && training) && x && out && L->graph_small &&
+                          (x_dtype == MOE_DTYPE_F32 || x_dtype == MOE_DTYPE_BF16);
+    if (!eligible) return forward_device(L, x, x_dtype, T, training, out, opt, s);
+    CUDA_TRY(cudaSetDevice(L->device));
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();   // the caller is building a graph of its own: its capture takes our launches
+        return forward_device(L, x, x_dtype, T, training, out, opt, s);
+    }
+    const float* noise = (training && L->noise_scale > 0.f) ? L->noise : nullptr;
+    moe_layer::GraphEntry* e = nullptr;
+    for (auto& g : L->graphs)
+        if (g.x == x && g.x_dtype == x_dtype && g.T == T && g.training == training && g.out == out &&
+            !g.opt.loss == !o.loss && g.opt.indices == o.indices && g.opt.gates == o.gates && g.opt.probs == o.probs &&
+            g.opt.logits == o.logits && !g.opt.tokens_per_expert == !o.tokens_per_expert &&
+            !g.opt.routing_entropy == !o.routing_entropy && g.noise == noise && g.noise_scale == L->noise_scale) {
+            e = &g;
+            break;
+        }
+    if (e && e->exec) {
+        int rc = check_ready(L);
+        if (rc) return rc;
+        e->tick = ++L->graph_tick;
+        return replay_graph(L, *e, o, s);
+    }
+    if (!e) {   // first sighting: remember the key, run the launches (they also grow the workspace)
+        if ((int)L->graphs.size() >= moe_layer::MAX_GRAPHS) {
+            size_t victim = 0;
+            for (size_t i = 1; i < L->graphs.size(); ++i)
+                if (L->graphs[i].tick < L->graphs[victim].tick) victim = i;
+            if (L->graphs[victim].exec) cudaGraphExecDestroy(L->graphs[victim].exec);
+            L->graphs.erase(L->graphs.begin() + victim);
+        }
+        moe_layer::GraphEntry g;
+        g.x = x;
+        g.x_dtype = x_dtype;
+        g.T = T;
+        g.training = training;
+        g.out = out;
+        g.opt = o;
+        g.noise = noise;
+        g.noise_scale = L->noise_scale;
+        g.tick = ++L->graph_tick;
+        const int rc = forward_device(L, x, x_dtype, T, training, out, opt, s);   // may drop all graphs (growth)
+        if (rc == MOE_OK) L->graphs.push_back(g);
+        return rc;
+    }
+    e->tick = ++L->graph_tick;
+    if (e->refused || T > L->T_cap) return forward_device(L, x, x_dtype, T, training, out, opt, s);
+    // second sighting: record the same launches on the handle's stream instead of running them
+    const int64_t launches_before = L->launches;
+    if (cudaStreamBeginCapture(L->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        e->refused = true;
+        return forward_device(L, x, x_dtype, T, training, out, opt, s);
+    }
+    moe_forward_outputs_t inside = o;
+    inside.loss = o.loss ? L->graph_small : nullptr;
+    inside.routing_entropy = o.routing_entropy ? L->graph_small + 1 : nullptr;
+    inside.tokens_per_expert = o.tokens_per_expert ? reinterpret_cast<int64_t*>(L->graph_small + 4) : nullptr;
+    const int rc = forward_device(L, x, x_dtype, T, training, out, &inside, L->stream);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(L->stream, &graph);
+    const int recorded = (int)(L->launches - launches_before);
+    L->launches = launches_before;
+    cudaGraphExec_t exec = nullptr;
+    const bool ok = rc == MOE_OK && ce == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+    if (graph) cudaGraphDestroy(graph);
+    if (!ok) {
+        cudaGetLastError();
+        e->refused = true;
+        if (rc != MOE_OK) return rc;   // an argument error: nothing was recorded and nothing ran
+        return forward_device(L, x, x_dtype, T, training, out, opt, s);
+    }
+    e->exec = exec;
+    e->launches = recorded;
+    return replay_graph(L, *e, o, s);
+}
+
 int grow(void** p, size_t* cap, size_t need) {
     if (need <= *cap) return MOE_OK;
     if (*p) cudaFree(*p);
@@ -625,6 +782,22 @@ int grow(void** p, size_t* cap, size_t need) {
     CUDA_TRY(cudaMalloc(p, need));
     *cap = need;
     return MOE_OK;
+}
+
+int grow_pinned(char** p, size_t* cap, size_t need) {
+    if (need <= *cap) return MOE_OK;
+    if (*p) cudaFreeHost(*p);
+    *p = nullptr;
+    *cap = 0;
+    CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(p), need, cudaHostAllocDefault));
+    *cap = need;
+    return MOE_OK;
+}
+
+int status_to_rc(moe_layer* L, int32_t st) {
+    if (st == DEV_OK) return MOE_OK;
+    cudaMemset(L->status, 0, sizeof(int32_t));
+    return fail(st == DEV_BAD_INDEX ? MOE_ERR_INVALID : MOE_ERR_TIMEOUT, "device status %d after forward", st);
 }
 
 }  // namespace
@@ -667,6 +840,7 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     if (const char* ev = getenv("MOE_B200_HOST_TIMELINE")) L->host_timeline = atoi(ev) > 0;
     if (const char* ev = getenv("MOE_B200_ROUTER_TC")) L->router_tc_enabled = atoi(ev) != 0;
     if (const char* ev = getenv("MOE_B200_INPLACE_SHARED")) L->inplace_shared = atoi(ev) != 0;
+    if (const char* ev = getenv("MOE_B200_GRAPHS")) L->graphs_enabled = atoi(ev) != 0;
     auto cleanup = [&](int code) {
         moe_layer_destroy(L);
         return code;
@@ -687,6 +861,7 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
         if (cudaMemset(L->tc_recheck, 0, sizeof(int32_t)) != cudaSuccess) return cleanup(fail(MOE_ERR_CUDA, "cudaMemset failed"));
     }
     if (cudaMemset(L->status, 0, sizeof(int32_t)) != cudaSuccess) return cleanup(fail(MOE_ERR_CUDA, "cudaMemset failed"));
+    if ((rc = dev_alloc(&L->graph_small, (size_t)4 + 2 * L->E))) return cleanup(rc);
     if (cudaStreamCreateWithFlags(&L->stream, cudaStreamNonBlocking) != cudaSuccess)
         return cleanup(fail(MOE_ERR_CUDA, "cudaStreamCreate failed"));
     *out = L;
@@ -719,9 +894,11 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->tile_prefix);
     dev_free(L->loss_dev);
     dev_free(L->status);
+    dev_free(L->graph_small);
     dev_free(L->hx);
     dev_free(L->hout);
     dev_free(L->hopt);
+    if (L->pin) cudaFreeHost(L->pin);
     if (L->plan) tc_plan_destroy(L->plan);
     for (auto& e : L->ev) cudaEventDestroy(e);
     if (L->stream) cudaStreamDestroy(L->stream);
@@ -762,6 +939,7 @@ static int set_expert_impl(moe_layer_t* L, int expert, const void* w1, const voi
     if (expert < L->e_lo || expert >= L->e_hi)
         return fail(MOE_ERR_INVALID, "expert %d is not held by this rank (it holds %d..%d)", expert, L->e_lo, L->e_hi - 1);
     CUDA_TRY(cudaSetDevice(L->device));
+    drop_graphs(L);
     // Device sources may still be being written by work the caller queued on its own streams; the
     // repack below runs on the handle's stream, which is not ordered after them.
     if (src_is_device) CUDA_TRY(cudaDeviceSynchronize());
@@ -823,6 +1001,7 @@ int moe_layer_set_router(moe_layer_t* L, const float* w, const float* logit_bias
     if (!L || !w) return fail(MOE_ERR_INVALID, "null argument");
     if (layout != MOE_LAYOUT_IN_CONTIG && layout != MOE_LAYOUT_OUT_CONTIG) return fail(MOE_ERR_INVALID, "unknown layout");
     CUDA_TRY(cudaSetDevice(L->device));
+    drop_graphs(L);
     if (src_is_device) CUDA_TRY(cudaDeviceSynchronize());   // see moe_layer_set_expert
     const size_t bytes = (size_t)L->E_router * L->cfg.input_dim * sizeof(float);
     const void* src = w;
@@ -964,6 +1143,7 @@ int moe_layer_import_weights(moe_layer_t* L, const void* src, int64_t bytes) {
     if (memcmp(in.magic, "MOEB200W", 8) != 0) return fail(MOE_ERR_INVALID, "not a weight image: bad magic");
     if (in.version != 1) return fail(MOE_ERR_UNSUPPORTED, "weight image version %d is not supported", in.version);
     CUDA_TRY(cudaSetDevice(L->device));
+    drop_graphs(L);
     int rc = ensure_weights(L);
     if (rc) return rc;
     if (in.compute_dtype != L->cfg.compute_dtype || in.expert_kind != L->cfg.expert_kind || in.e_lo != L->e_lo ||
@@ -1022,6 +1202,7 @@ int moe_layer_import_weights(moe_layer_t* L, const void* src, int64_t bytes) {
 int moe_layer_set_aux_free(moe_layer_t* L, int enable, float learning_rate, float momentum, int update_freq,
                            const float* bias_momentum, int64_t update_counter) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");
+    drop_graphs(L);
     if (!enable) {
         L->aux_free = false;
         return MOE_OK;
@@ -1062,6 +1243,7 @@ int moe_layer_aux_free_state(moe_layer_t* L, float* bias, float* bias_momentum, 
 int moe_layer_set_router_noise_network(moe_layer_t* L, const float* noise_w, int layout, int src_is_device) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");
     CUDA_TRY(cudaSetDevice(L->device));
+    drop_graphs(L);
     if (!noise_w) {   // back to plain Gaussian noise
         CUDA_TRY(cudaStreamSynchronize(L->stream));
         dev_free(L->router_nw);
@@ -1108,7 +1290,7 @@ int moe_layer_set_router_noise(moe_layer_t* L, const float* noise, float noise_s
 int moe_layer_forward(moe_layer_t* L, const void* x, int x_dtype, int64_t T, int training, float* out,
                       const moe_forward_outputs_t* opt, void* cuda_stream) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");
-    return forward_device(L, x, x_dtype, T, training, out, opt, reinterpret_cast<cudaStream_t>(cuda_stream));
+    return forward_small(L, x, x_dtype, T, training, out, opt, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
 
 int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T, int training, float* out,
@@ -1283,14 +1465,35 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         }
         int32_t stc = 0;
         CUDA_TRY(cudaMemcpy(&stc, L->status, sizeof(stc), cudaMemcpyDeviceToHost));
-        if (stc != DEV_OK) {
-            cudaMemset(L->status, 0, sizeof(int32_t));
-            return fail(stc == DEV_BAD_INDEX ? MOE_ERR_INVALID : MOE_ERR_TIMEOUT, "device status %d after forward", stc);
+        return status_to_rc(L, stc);
+    }
+    const size_t x_off = 256, out_off = x_off + ((xb + 255) & ~(size_t)255), opt_off = out_off + ((ob + 255) & ~(size_t)255);
+    if (opt_off + off <= moe_layer::PIN_SMALL_CALL && !L->ep) {
+        if ((rc = grow_pinned(&L->pin, &L->pin_bytes, opt_off + off))) return rc;
+        if (xb) {
+            memcpy(L->pin + x_off, x, xb);
+            CUDA_TRY(cudaMemcpyAsync(L->hx, L->pin + x_off, xb, cudaMemcpyHostToDevice, s));
         }
-        return MOE_OK;
+        if ((rc = forward_small(L, L->hx, x_dtype, T, training, L->hout, &d, s))) return rc;
+        if (ob) CUDA_TRY(cudaMemcpyAsync(L->pin + out_off, L->hout, ob, cudaMemcpyDeviceToHost, s));
+        if (off) CUDA_TRY(cudaMemcpyAsync(L->pin + opt_off, L->hopt, off, cudaMemcpyDeviceToHost, s));
+        CUDA_TRY(cudaMemcpyAsync(L->pin, L->status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+        CUDA_TRY(cudaStreamSynchronize(s));
+        if (ob) memcpy(out, L->pin + out_off, ob);
+        const char* po = L->pin + opt_off;
+        if (opt->loss) memcpy(opt->loss, po + o_loss, 4);
+        if (opt->indices && T) memcpy(opt->indices, po + o_idx, (size_t)T * ku * 4);
+        if (opt->gates && T) memcpy(opt->gates, po + o_gate, (size_t)T * ku * 4);
+        if (opt->probs && T) memcpy(opt->probs, po + o_probs, (size_t)T * ep * 4);
+        if (opt->logits && T) memcpy(opt->logits, po + o_logits, (size_t)T * er * 4);
+        if (opt->tokens_per_expert) memcpy(opt->tokens_per_expert, po + o_tpe, (size_t)L->E * 8);
+        if (opt->routing_entropy) memcpy(opt->routing_entropy, po + o_ent, 4);
+        int32_t st = 0;
+        memcpy(&st, L->pin, sizeof(st));
+        return status_to_rc(L, st);
     }
     if (xb) CUDA_TRY(cudaMemcpyAsync(L->hx, x, xb, cudaMemcpyHostToDevice, s));
-    if ((rc = forward_device(L, L->hx, x_dtype, T, training, L->hout, &d, s))) return rc;
+    if ((rc = forward_small(L, L->hx, x_dtype, T, training, L->hout, &d, s))) return rc;
     if (ob) CUDA_TRY(cudaMemcpyAsync(out, L->hout, ob, cudaMemcpyDeviceToHost, s));
     if (d.loss) CUDA_TRY(cudaMemcpyAsync(opt->loss, d.loss, 4, cudaMemcpyDeviceToHost, s));
     if (d.indices && T) CUDA_TRY(cudaMemcpyAsync(opt->indices, d.indices, (size_t)T * ku * 4, cudaMemcpyDeviceToHost, s));
@@ -1303,11 +1506,7 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
     CUDA_TRY(cudaStreamSynchronize(s));
     int32_t st = 0;
     CUDA_TRY(cudaMemcpy(&st, L->status, sizeof(st), cudaMemcpyDeviceToHost));
-    if (st != DEV_OK) {
-        cudaMemset(L->status, 0, sizeof(int32_t));
-        return fail(st == DEV_BAD_INDEX ? MOE_ERR_INVALID : MOE_ERR_TIMEOUT, "device status %d after forward", st);
-    }
-    return MOE_OK;
+    return status_to_rc(L, st);
 }
 
 static int compute_gates_impl(int gate_kind, int num_experts, int num_shared, int top_k, int index_base,
@@ -1360,6 +1559,7 @@ int moe_layer_set_profiling(moe_layer_t* L, int slots) {
     if (!L) return fail(MOE_ERR_INVALID, "null handle");
     if (slots < 0 || slots > 1024) return fail(MOE_ERR_INVALID, "slots must be in 0..1024");
     CUDA_TRY(cudaSetDevice(L->device));
+    drop_graphs(L);
     CUDA_TRY(cudaDeviceSynchronize());
     for (auto& e : L->ev) cudaEventDestroy(e);
     L->ev.clear();
@@ -1412,6 +1612,12 @@ int moe_layer_tile_rows(moe_layer_t* L, int64_t T) {
     return pick_tile_m(L, T * L->k_tot, L->E);
 }
 
+int moe_layer_graph_replays(const moe_layer_t* L, int64_t* replays) {
+    if (!L || !replays) return fail(MOE_ERR_INVALID, "null argument");
+    *replays = L->graph_replays;
+    return MOE_OK;
+}
+
 int moe_layer_device_status(moe_layer_t* L, int32_t* status) {
     if (!L || !status) return fail(MOE_ERR_INVALID, "null argument");
     CUDA_TRY(cudaSetDevice(L->device));
@@ -1456,6 +1662,7 @@ int moe_ep_init(moe_layer_t* L, const void* id128, int rank, int world) {
     if (L->w1) return fail(MOE_ERR_STATE, "moe_ep_init must come before moe_layer_set_expert");
     if (L->ep) return fail(MOE_ERR_STATE, "expert parallelism is already initialised");
     CUDA_TRY(cudaSetDevice(L->device));
+    drop_graphs(L);
     EpConfig ec;
     ec.rank = rank;
     ec.world = world;

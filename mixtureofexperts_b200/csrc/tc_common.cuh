@@ -45,13 +45,20 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                           int32_t code, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    // the clock is first read after 64 failed attempts: most waits end well before that, and a read of
+    // the global timer in front of every retry would sit between the barrier's completion and its notice
+    unsigned long long t0 = 0;
+    bool timed = false;
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
+            const unsigned long long now = globaltimer_ns();
+            if (!timed) {
+                t0 = now;
+                timed = true;
+            } else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, DEV_OK, code);
                 return false;

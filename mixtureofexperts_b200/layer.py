@@ -150,6 +150,33 @@ class _HostValue:
         return float(self.v)
 
 
+class _BoundForward:
+    """One forward call with its arguments bound (MoELayer.bind_forward)."""
+
+    def __init__(self, layer, xt, out, T, training):
+        import torch
+
+        self._layer, self._xt, self.out, self.T, self.training = layer, xt, out, T, training
+        dev = xt.device
+        self.loss = torch.zeros((), dtype=torch.float32, device=dev)
+        self.tokens_per_expert = torch.zeros(layer.config.num_experts, dtype=torch.int64, device=dev)
+        self.routing_entropy = torch.zeros((), dtype=torch.float32, device=dev)
+        o = _lib.ForwardOutputs()
+        o.loss = self.loss.data_ptr()
+        o.tokens_per_expert, o.routing_entropy = self.tokens_per_expert.data_ptr(), self.routing_entropy.data_ptr()
+        self._o = o
+        self._args = (xt.data_ptr(), _lib.DTYPE_BF16 if xt.dtype == torch.bfloat16 else _lib.DTYPE_F32, T, int(training),
+                      out.data_ptr(), C.byref(o))
+        self._device = dev
+        self._current_stream = torch.cuda.current_stream
+
+    def __call__(self):
+        rc = _lib.lib.moe_layer_forward(self._layer._handle, *self._args, self._current_stream(self._device).cuda_stream)
+        if rc:
+            _lib.check(rc)
+        return self.out.t(), self.loss
+
+
 class MoELayer:
     """MoELayer(config) (src/core/moe_layer.jl:34-63) and its call
     ``moe(x; training=false, return_stats=false) -> (output, balance_loss[, training_stats])``
@@ -477,13 +504,14 @@ class MoELayer:
         elif (tuple(out.shape) != (T, cfg.output_dim) or out.dtype != torch.float32 or not out.is_contiguous()
               or out.device != dev):
             raise _lib.MoEError(_lib.ERR_INVALID, "out must be a contiguous float32 (T, output_dim) tensor on x's device")
-        loss = torch.zeros((), dtype=torch.float32, device=dev)
+        # the library writes every optional output it is given on every call (zeros for an empty batch)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
         o = _lib.ForwardOutputs()
         o.loss = loss.data_ptr()
         extra = {}
         if want_stats:
-            tpe = torch.zeros(cfg.num_experts, dtype=torch.int64, device=dev)
-            ent = torch.zeros((), dtype=torch.float32, device=dev)
+            tpe = torch.empty(cfg.num_experts, dtype=torch.int64, device=dev)
+            ent = torch.empty((), dtype=torch.float32, device=dev)
             o.tokens_per_expert, o.routing_entropy = tpe.data_ptr(), ent.data_ptr()
         if want_routing:
             idx = torch.empty((T, self.k_out), dtype=torch.int32, device=dev)
@@ -500,6 +528,32 @@ class MoELayer:
             extra["tokens_per_expert"] = tpe
             extra["routing_entropy"] = ent
         return out.t(), loss, extra
+
+    def bind_forward(self, x, out, training: bool = False):
+        """Bind the arguments of one device forward once and return a callable that only makes the C
+        call (no counterpart in the reference: for loops whose steps are shorter than the checks and
+        allocations of ``__call__``, e.g. token-by-token decoding into fixed buffers).  ``x`` is the
+        (input_dim, T) view of a contiguous (T, input_dim) float32/bfloat16 CUDA tensor and ``out`` a
+        contiguous float32 (T, output_dim) CUDA tensor; both are read and written in place by every
+        call, on the stream that is current when the call is made.  The returned object keeps
+        ``loss``, ``tokens_per_expert`` and ``routing_entropy`` tensors that every call overwrites;
+        ``training_stats`` is not updated by bound calls."""
+        import torch
+
+        cfg = self.config
+        xt = x.t()
+        if (x.ndim != 2 or x.shape[0] != cfg.input_dim or not x.is_cuda or not xt.is_contiguous()
+                or xt.dtype not in (torch.float32, torch.bfloat16)):
+            raise _lib.MoEError(_lib.ERR_INVALID, "x must be the (input_dim, T) view of a contiguous float32/bfloat16 CUDA tensor")
+        T = int(x.shape[1])
+        if (tuple(out.shape) != (T, cfg.output_dim) or out.dtype != torch.float32 or not out.is_contiguous()
+                or out.device != xt.device):
+            raise _lib.MoEError(_lib.ERR_INVALID, "out must be a contiguous float32 (T, output_dim) tensor on x's device")
+        if isinstance(self.balance_loss, AuxiliaryFreeLoss) and training and not self._aux_on_device:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "a host-side bias update needs __call__")
+        if training and float(getattr(self.router, "noise_scale", 0.0) or 0.0) > 0.0:
+            raise _lib.MoEError(_lib.ERR_UNSUPPORTED, "router noise is drawn per call: use __call__")
+        return _BoundForward(self, xt, out, T, bool(training))
 
     def _forward_host(self, x, T, training, want_stats, want_routing, out=None):
         """Host buffers (NumPy arrays or torch CPU tensors, pinned or not) through
@@ -580,6 +634,12 @@ class MoELayer:
         """Tokens whose logits the tensor-core router re-evaluated with FP32 FMAs since creation."""
         n = C.c_int64()
         _lib.check(_lib.lib.moe_layer_router_rechecks(self._handle, C.byref(n)))
+        return int(n.value)
+
+    def graph_replays(self) -> int:
+        """Forward calls served by replaying a captured CUDA graph (small batches) since creation."""
+        n = C.c_int64()
+        _lib.check(_lib.lib.moe_layer_graph_replays(self._handle, C.byref(n)))
         return int(n.value)
 
     def launch_count(self) -> int:
