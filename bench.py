@@ -530,11 +530,13 @@ def measure_other(name, torch, peaks, steps=10, warmup=3):
     return res
 
 
-def measure_llama_ffn(torch, peaks, calls=300, warmup=100):
+def measure_llama_ffn(torch, peaks, calls=1000, warmup=3000):
     """The MoE FFN of a converted Llama2 layer as the generation loop drives it: one host call of
     moe_layer_forward_host per position (decode, T = 1) and one call for a whole 64-token prompt
-    (prefill), host buffers in and out, synchronous; per-call wall time with the library's graph
-    replay on and off.  Calls go straight to the C entry point with prebuilt arguments."""
+    (prefill), host buffers in and out, synchronous; per-call wall time with the library's default
+    launch mode (chained plain launches) and with a graph replay instead.  Calls go straight to the
+    C entry point with prebuilt arguments; a few tenths of a second of warm-up calls bring the SM
+    clock up from idle first."""
     import ctypes as C
 
     import numpy as np
@@ -545,16 +547,18 @@ def measure_llama_ffn(torch, peaks, calls=300, warmup=100):
     res = {"workload": f"c2: {w['desc']}", "calls": calls, "warmup": warmup,
            "timing": "host clock around synchronous moe_layer_forward_host calls (pageable NumPy buffers), inference"}
     rng = np.random.default_rng(SEED + 2)
-    for graphs in (1, 0):
-        old = os.environ.get("MOE_B200_GRAPHS")
-        os.environ["MOE_B200_GRAPHS"] = str(graphs)
+    for graphs in (0, 1):     # 1: MOE_B200_CHAIN=0 makes small host calls replay a captured graph instead
+        old = os.environ.get("MOE_B200_CHAIN")
+        if graphs:
+            os.environ["MOE_B200_CHAIN"] = "0"
         try:
             layer = build_layer(w, torch, 0)
         finally:
-            if old is None:
-                del os.environ["MOE_B200_GRAPHS"]
-            else:
-                os.environ["MOE_B200_GRAPHS"] = old
+            if graphs:
+                if old is None:
+                    del os.environ["MOE_B200_CHAIN"]
+                else:
+                    os.environ["MOE_B200_CHAIN"] = old
         for T, label in ((1, "decode_us_per_position"), (w["T"], "prefill_us_per_64_positions")):
             x = np.ascontiguousarray(rng.standard_normal((T, w["D"])).astype(np.float32))
             out = np.empty((T, w["O"]), dtype=np.float32)
@@ -570,11 +574,12 @@ def measure_llama_ffn(torch, peaks, calls=300, warmup=100):
                 rc = _lib.lib.moe_layer_forward_host(*args)
             dt = time.perf_counter() - t0
             _lib.check(rc)
-            key = label + ("" if graphs else "_graphs_off")
+            key = label + ("_graph_replay" if graphs else "")
             res[key] = dt / calls * 1e6
             if graphs:
-                res[label.split("_us_")[0] + "_launches_per_call"] = (layer.launch_count() - launches0) / calls
                 res[label.split("_us_")[0] + "_graph_replays"] = layer.graph_replays() - replays0
+            else:
+                res[label.split("_us_")[0] + "_launches_per_call"] = (layer.launch_count() - launches0) / calls
                 res[label.split("_us_")[0] + "_output_finite"] = bool(np.isfinite(out).all())
         res["device_status"] = layer.device_status()
         layer.close()

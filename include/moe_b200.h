@@ -40,6 +40,8 @@
  *                              handle creation)
  *   MOE_B200_GRAPHS=0          small batches launch their kernels one by one instead of replaying a captured
  *                              CUDA graph (comparison; read at handle creation)
+ *   MOE_B200_CHAIN=0           small batches launch their kernels without programmatic dependent launch
+ *                              (comparison; read at handle creation)
  *   MOE_B200_EP_MODE=nccl      expert parallelism moves token rows with ncclSend/ncclRecv instead of
  *                              peer stores from the library's own kernels (read by moe_ep_init)
  */

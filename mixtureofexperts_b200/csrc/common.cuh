@@ -177,6 +177,34 @@ __device__ __forceinline__ T* group_gemm_out_row(const GroupGemmParams& p, int e
     return reinterpret_cast<T*>(p.seg_dst[(size_t)e * p.seg_per_expert + q]) + (size_t)(row - st[q]) * p.N;
 }
 
+// ---- chained launches (programmatic dependent launch) ------------------------------------------
+// The kernels of a small forward are each a few microseconds long, so the time between the end of one
+// and the start of the next is a large part of the call.  Launched as a chain, a kernel may be set up on
+// the SMs (blocks scheduled, shared memory and barriers initialised) while its predecessor is still
+// running; it calls chain_wait() before its first access to global memory, which returns when the
+// predecessor has completed and its writes are visible, and chain_release() at its start lets its own
+// successor be set up.  Both calls do nothing in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Set by the forward call around its launches (per thread: a handle is driven by one thread at a time).
+extern thread_local bool g_chain_launches;
+
+template <class... P, class... A>
+inline cudaError_t launch_kernel(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = g_chain_launches ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
 // ---- launchers (each returns the number of kernels it launched, or <0 on a launch error) ---
 int launch_router(const RouterParams& p, int x_dtype, int num_cta, int num_sms, cudaStream_t s);
 int router_tokens_per_cta(int64_t T, int e_router, int num_sms);   // 64, 32 or 16

@@ -34,6 +34,8 @@ __global__ void __launch_bounds__(THREADS) group_gemm_f32_kernel(const GroupGemm
     __shared__ float Bs[NB][BN][BK + 1];
 
     const int mtile = blockIdx.x;
+    chain_release();
+    chain_wait();
     if (mtile >= p.tile_prefix[p.E]) return;
     const int e = find_segment(p.tile_prefix, p.E, mtile);
     const int row0 = p.expert_offset[e] + (mtile - p.tile_prefix[e]) * BM;
@@ -228,6 +230,8 @@ group_gemm_f32_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    chain_release();
+    chain_wait();   // barriers are set up; everything below reads what the previous kernel wrote
     for (int e = threadIdx.x; e <= p.E; e += ST_THREADS) ss->expert_offset[e] = p.expert_offset[e];
     __syncthreads();
 
@@ -388,8 +392,7 @@ int launch_stream(const GroupGemmParams& p, int64_t rows, int num_sms, cudaStrea
         return -1;
     const long items = (long)p.E * ((p.N + ST_COLS - 1) / ST_COLS);
     const int grid = (int)(items < num_sms ? items : num_sms);
-    kern<<<grid, ST_THREADS, smem, s>>>(ma, mb0, mb1, p);
-    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+    return launch_kernel(kern, dim3(grid), dim3(ST_THREADS), smem, s, ma, mb0, mb1, p) == cudaSuccess ? 1 : -1;
 }
 
 }  // namespace
@@ -405,9 +408,9 @@ int launch_group_gemm_f32(const GroupGemmParams& p, int mode, int max_mtiles, in
         return mode == 1 ? launch_stream<1>(p, rows, num_sms, s) : launch_stream<2>(p, rows, num_sms, s);
     }
     dim3 grid(max_mtiles, (p.N + BN - 1) / BN);
-    if (mode == 1) group_gemm_f32_kernel<1><<<grid, THREADS, 0, s>>>(p);
-    else group_gemm_f32_kernel<2><<<grid, THREADS, 0, s>>>(p);
-    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+    const cudaError_t err = mode == 1 ? launch_kernel(group_gemm_f32_kernel<1>, grid, dim3(THREADS), 0, s, p)
+                                      : launch_kernel(group_gemm_f32_kernel<2>, grid, dim3(THREADS), 0, s, p);
+    return err == cudaSuccess ? 1 : -1;
 }
 
 }  // namespace moe

@@ -71,7 +71,6 @@ group_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // N_out columns per tile: mode 1 produces 128 hidden units (from 256 accumulator columns)
     constexpr int TILE_N_OUT = (MODE == 1) ? 128 : 256;
     const int n_tiles = (p.N + TILE_N_OUT - 1) / TILE_N_OUT;
-    const int total_tiles = p.tile_prefix[p.E] * n_tiles;
     const int num_kb = (p.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -92,6 +91,10 @@ group_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ss->tmem_base;
+    // barriers and TMEM are set up: from here on the kernel reads what its predecessor wrote
+    chain_release();
+    chain_wait();
+    const int total_tiles = p.tile_prefix[p.E] * n_tiles;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------------------
@@ -402,13 +405,17 @@ int launch_group_gemm_tc(const TcGemmPlan* plan_c, int stage, int mode, const Gr
     }
     const int gm = group_m_setting();
     const int grid = max_tiles < num_sms ? max_tiles : num_sms;
+    cudaError_t err;
     if (mode == 1)
-        group_gemm_tc_kernel<1><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w3, plan->map_x, p, gm);
+        err = launch_kernel(group_gemm_tc_kernel<1>, dim3(grid), dim3(NUM_THREADS), smem, s, plan->map_xp, plan->map_w1, plan->map_w3,
+                            plan->map_x, p, gm);
     else if (stage == 1)
-        group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_xp, plan->map_w1, plan->map_w1, plan->map_x, p, gm);
+        err = launch_kernel(group_gemm_tc_kernel<2>, dim3(grid), dim3(NUM_THREADS), smem, s, plan->map_xp, plan->map_w1, plan->map_w1,
+                            plan->map_x, p, gm);
     else
-        group_gemm_tc_kernel<2><<<grid, NUM_THREADS, smem, s>>>(plan->map_h, plan->map_w2, plan->map_w2, plan->map_h, p, gm);
-    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+        err = launch_kernel(group_gemm_tc_kernel<2>, dim3(grid), dim3(NUM_THREADS), smem, s, plan->map_h, plan->map_w2, plan->map_w2,
+                            plan->map_h, p, gm);
+    return err == cudaSuccess ? 1 : -1;
 }
 
 }  // namespace moe

@@ -32,6 +32,8 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_kernel(const PermutePara
     const int64_t tok0 = (int64_t)blockIdx.x * p.tokens_per_cta;
     const int ntok = (int)min((int64_t)p.tokens_per_cta, p.T - tok0);
     const int npairs = ntok * p.k_tot;
+    chain_release();
+    chain_wait();
 
     // s_base[e]: rank, inside expert e, of the first pair of this tile (pairs of earlier tiles)
     for (int e = threadIdx.x; e < p.E; e += PERM_THREADS) s_base[e] = p.cta_base[(size_t)blockIdx.x * p.E + e];
@@ -142,6 +144,8 @@ __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombinePara
     // the token's slots: one thread per slot fetches (expert, row, gate), so the loads overlap ...
     __shared__ int s_id_in[MAX_KTOT], s_row_in[MAX_KTOT];
     __shared__ float s_gate_in[MAX_KTOT];
+    chain_release();
+    chain_wait();
     if (threadIdx.x < p.k_tot) {
         const int j = threadIdx.x;
         s_id_in[j] = p.idx[t * p.k_tot + j];
@@ -237,22 +241,22 @@ __global__ void __launch_bounds__(COMB_THREADS) combine_kernel(const CombinePara
 
 int launch_permute(const PermuteParams& p, int x_dtype, int xp_dtype, int num_cta, cudaStream_t s) {
     if (x_dtype == MOE_DTYPE_F32 && xp_dtype == MOE_DTYPE_F32)
-        permute_kernel<float, float><<<num_cta, PERM_THREADS, 0, s>>>(p);
+        launch_kernel(permute_kernel<float, float>, dim3(num_cta), dim3(PERM_THREADS), 0, s, p);
     else if (x_dtype == MOE_DTYPE_BF16 && xp_dtype == MOE_DTYPE_BF16)
-        permute_kernel<__nv_bfloat16, __nv_bfloat16><<<num_cta, PERM_THREADS, 0, s>>>(p);
+        launch_kernel(permute_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(num_cta), dim3(PERM_THREADS), 0, s, p);
     else if (x_dtype == MOE_DTYPE_F32 && xp_dtype == MOE_DTYPE_BF16)
-        permute_kernel<float, __nv_bfloat16><<<num_cta, PERM_THREADS, 0, s>>>(p);
+        launch_kernel(permute_kernel<float, __nv_bfloat16>, dim3(num_cta), dim3(PERM_THREADS), 0, s, p);
     else
-        permute_kernel<__nv_bfloat16, float><<<num_cta, PERM_THREADS, 0, s>>>(p);
+        launch_kernel(permute_kernel<__nv_bfloat16, float>, dim3(num_cta), dim3(PERM_THREADS), 0, s, p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 
 int launch_combine(const CombineParams& p, int y_dtype, cudaStream_t s) {
     if (p.T == 0) return 0;
     if (y_dtype == MOE_DTYPE_F32)
-        combine_kernel<float><<<(unsigned)p.T, COMB_THREADS, 0, s>>>(p);
+        launch_kernel(combine_kernel<float>, dim3((unsigned)p.T), dim3(COMB_THREADS), 0, s, p);
     else
-        combine_kernel<__nv_bfloat16><<<(unsigned)p.T, COMB_THREADS, 0, s>>>(p);
+        launch_kernel(combine_kernel<__nv_bfloat16>, dim3((unsigned)p.T), dim3(COMB_THREADS), 0, s, p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 

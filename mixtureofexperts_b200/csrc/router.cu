@@ -97,6 +97,8 @@ router_kernel(const RouterParams p) {
     const int eg = tid % EG, tg = (tid / EG) % TG, ks = tid / (EG * TG);
     for (int i = tid; i < MAX_EXPERTS; i += NTHREADS) s_cnt[i] = 0;
     for (int i = tid; i < NWARPS * MAX_EXPERTS; i += NTHREADS) (&s_psum[0][0])[i] = 0.f;
+    chain_release();
+    chain_wait();   // x may be the output of the caller's previous kernel; the id/gate buffers are read by the previous forward's combine
 
     const int64_t tok0 = (int64_t)blockIdx.x * RT_BT;
     const XT* x = reinterpret_cast<const XT*>(p.x);
@@ -323,8 +325,7 @@ int launch_router_n(const RouterParams& p, int num_cta, cudaStream_t s) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
         attr_done[dev] = true;
     }
-    kern<<<num_cta, 16 * (E_PAD / 8) * KS, smem, s>>>(p);
-    return cudaGetLastError() == cudaSuccess ? 1 : -1;
+    return launch_kernel(kern, dim3(num_cta), dim3(16 * (E_PAD / 8) * KS), smem, s, p) == cudaSuccess ? 1 : -1;
 }
 
 template <int E_PAD, int BK, int KS, typename XT>

@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_loss_kernel(const ScanParam
     __shared__ double s_ent;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int NW = SCAN_THREADS / 32;
+    chain_release();
+    chain_wait();
 
     // (i) per expert: exclusive prefix of the per-CTA counts, in CTA (= token) order
     for (int e = warp; e < p.E; e += NW) {
@@ -247,7 +249,7 @@ int launch_aux_free_update(const int32_t* expert_count, int E, float* bias, floa
 }
 
 int launch_scan(const ScanParams& p, cudaStream_t s) {
-    scan_loss_kernel<<<1, SCAN_THREADS, 0, s>>>(p);
+    launch_kernel(scan_loss_kernel, dim3(1), dim3(SCAN_THREADS), 0, s, p);
     return cudaGetLastError() == cudaSuccess ? 1 : -1;
 }
 

@@ -115,23 +115,23 @@ def test_growth_setters_and_other_keys_do_not_reuse_a_stale_graph():
     layer.close()
 
 
-def test_host_calls_replay_too_and_the_switch_turns_it_off(monkeypatch):
+@pytest.mark.parametrize("chain,graphs,replays", [("1", "1", 0), ("0", "1", 3), ("0", "0", 0), ("1", "0", 0)])
+def test_small_host_calls_with_every_launch_mode(monkeypatch, chain, graphs, replays):
+    """Per-position host calls: chained plain launches by default, a graph replay keyed on the staging
+    buffers when chaining is switched off, plain launches when both are off -- same results each way."""
+    monkeypatch.setenv("MOE_B200_CHAIN", chain)
+    monkeypatch.setenv("MOE_B200_GRAPHS", graphs)
     layer, cfg, w = _layer("f32")
     D = 256
-    refs = []
     for call in range(4):
-        x, _ = _inputs(1, D, 300 + call, False)
-        out, loss = layer(np.asfortranarray(x.T), training=False)
-        ref, _, _ = orc.moe_layer_forward(cfg, w, x, training=False)
-        assert rel_inf(np.asarray(out).T, ref) < 1e-5
-        refs.append(ref)
-    assert layer.graph_replays() == 3      # per-token host calls: the staging buffers are the key
-    layer.close()
-    monkeypatch.setenv("MOE_B200_GRAPHS", "0")
-    layer, cfg, w = _layer("f32")
-    for call in range(3):
-        x, _ = _inputs(1, D, 300 + call, False)
-        out, _ = layer(np.asfortranarray(x.T), training=False)
-        assert rel_inf(np.asarray(out).T, refs[call]) < 1e-5
-    assert layer.graph_replays() == 0
+        for T in (1, 7):
+            x, _ = _inputs(T, D, 300 + 10 * call + T, False)
+            out, loss, routing = layer(np.asfortranarray(x.T), training=True, return_routing=True)
+            ref, ref_loss, aux = orc.moe_layer_forward(cfg, w, x, training=True)
+            assert rel_inf(np.asarray(out).T, ref) < 1e-5
+            assert abs(float(loss) - float(ref_loss)) <= 1e-5 * abs(float(ref_loss))
+            assert np.array_equal(np.asarray(routing["indices"]).T, aux["indices"])
+    # (the first calls of each batch size launch plainly; the staging block grows once in between)
+    assert (layer.graph_replays() >= 4) if replays else (layer.graph_replays() == 0)
+    assert layer.device_status() == 0
     layer.close()
