@@ -698,3 +698,44 @@ def test_bf16_mixtral_shaped_slice_sampled_against_oracle():
     err = rel_inf(out.cpu().numpy().T[sample], o_out)
     assert err < BF16_TOL, err
     layer.close()
+
+
+# ---- seeded sweep over shapes nobody picked by hand ----------------------------------------------------------------
+
+def _sweep_case(rng):
+    compute = str(rng.choice(["f32", "bf16"]))
+    kind = str(rng.choice(["topk", "switch", "shared"]))
+    E = int(rng.choice([2, 3, 5, 8, 16, 31, 33, 48, 64, 66, 80, 96, 128]))
+    S = int(rng.integers(1, 3)) if kind == "shared" else 0
+    if kind == "shared" and E - S < 1:
+        kind, S = "topk", 0
+    k = 1 if kind == "switch" else int(rng.integers(1, max(1, min(E - S, 8 - S)) + 1))
+    if compute == "bf16":      # the tensor-core path wants input and hidden widths in multiples of 8
+        D, H = int(rng.integers(1, 65)) * 8, int(rng.integers(1, 97)) * 8
+    else:
+        D, H = int(rng.integers(3, 400)), int(rng.integers(3, 500))
+    nse = 0
+    if kind != "shared" and E >= 4 and rng.integers(0, 4) == 0:      # forward_with_shared_experts
+        nse = int(rng.integers(1, 3))
+        k = max(1, min(k, E - nse, 8 - nse))
+    return dict(T=int(rng.choice([1, 2, 7, 33, 64, 100, 257, 1000, 2500])), D=D, H=H, O=int(rng.integers(1, 300)), E=E,
+                gate_kind=kind, k=k, S=S, compute=compute, host=bool(rng.integers(0, 2)), training=bool(rng.integers(0, 2)),
+                activation=str(rng.choice(["silu", "gelu", "relu"])), num_shared_experts=nse,
+                expert_kind=str(rng.choice(["gated", "gated", "standard"])),
+                x_bf16=bool(rng.integers(0, 2)) if compute == "bf16" else None)
+
+
+@pytest.mark.parametrize("block", range(4))
+def test_seeded_sweep_of_shapes_gates_and_dtypes(block):
+    """Twelve drawn configurations per block: widths that are no multiple of any tile, 1 to 2500 tokens, every gate,
+    both expert types and shared-expert mechanisms, device and host calls -- each against the oracle at the
+    tolerances of its dtype (run_case)."""
+    rng = np.random.default_rng(20240 + block)
+    for i in range(12):
+        c = _sweep_case(rng)
+        T, D, H, O, E = c.pop("T"), c.pop("D"), c.pop("H"), c.pop("O"), c.pop("E")
+        kind, k, S = c.pop("gate_kind"), c.pop("k"), c.pop("S")
+        try:
+            run_case(T, D, H, O, E, kind, k, S, seed=7000 + 100 * block + i, std=0.1, **c)
+        except AssertionError as exc:
+            raise AssertionError(f"case {i} of block {block}: T={T} D={D} H={H} O={O} E={E} {kind} k={k} S={S} {c}: {exc}") from exc
