@@ -256,6 +256,12 @@ function enable_aux_free!(moe::MoELayer, bias::Vector{Float32}, bias_momentum::V
     check(ccall((:moe_layer_set_aux_free, LIB), Cint, (Ptr{Cvoid}, Cint, Cfloat, Cfloat, Cint, Ptr{Float32}, Int64),
                 moe.handle, 1, Float32(learning_rate), Float32(momentum), update_freq, bias_momentum, update_counter))
 end
+"Forward calls of this layer that were served by replaying a captured CUDA graph (small batches on fixed device buffers)."
+function graph_replays(moe::MoELayer)
+    n = Ref{Int64}(0)
+    check(ccall((:moe_layer_graph_replays, LIB), Cint, (Ptr{Cvoid}, Ref{Int64}), moe.handle, n))
+    return n[]
+end
 function aux_free_state(moe::MoELayer)
     n = size(moe.router_weight, 1)
     bias, mom, cnt = zeros(Float32, n), zeros(Float32, n), Ref{Int64}(0)
