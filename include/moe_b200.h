@@ -30,7 +30,7 @@
  *   MOE_B200_PAIR=0|1          force the single-CTA (128-row tiles) or the CTA-pair (256-row tiles,
  *                              cta_group::2) tensor-core GEMM kernels instead of the per-batch choice
  *   MOE_B200_HOST_CHUNKS=n     moe_layer_forward_host cuts batches of 8192 tokens and more into n
- *                              equal chunks (1 = no chunking) instead of its default 1/5/5/4/1 schedule
+ *                              equal chunks (1 = no chunking) instead of its default schedule of 2/12/10/6/2 thirty-seconds
  *   MOE_B200_HOST_TIMELINE=1   print every chunk's copy and compute times to stderr
  *   MOE_B200_GROUP_M=n         m-tiles per group of the GEMM tile order (default 32)
  *   MOE_B200_ROUTER_TILE=16|32|64   force the token tile of the router and permute kernels

@@ -1394,8 +1394,8 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
             if ((rc = dev_alloc(&L->chunk_acc, (size_t)nsum))) return rc;
             if ((rc = dev_alloc(&L->chunk_tpe_acc, (size_t)L->E))) return rc;
         }
-        // Chunk boundaries (multiples of 64 tokens).  By default small first and last chunks: only the
-        // copy-in of the first and the copy-out of the last chunk are not hidden behind compute.
+        // Chunk boundaries (multiples of 64 tokens).  By default a small first chunk and a shrinking tail: only
+        // the copy-in of the first and the copy-out of the last chunk are not hidden behind compute.
         std::vector<int64_t> bounds;
         bounds.push_back(0);
         if (env_chunks > 0) {
@@ -1405,12 +1405,15 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
                 if (L->ep || (t > bounds.back() && t < T)) bounds.push_back(t);
             }
         } else {
-            static const int parts[] = {1, 5, 5, 4, 1};     // sixteenths of the batch
-            nchunks = 5;
-            int64_t acc16 = 0;
-            for (int i = 0; i < 4; ++i) {
-                acc16 += parts[i];
-                const int64_t t = std::min<int64_t>(T, (T * acc16 / 16 + 63) / 64 * 64);
+            // thirty-seconds of the batch: the copy-out of a chunk must fit under the next chunk's compute
+            // (the output is twice the input's bytes), so the chunks shrink towards the end
+            static const int parts[] = {2, 12, 10, 6, 2};
+            const int np = 5;
+            nchunks = np;
+            int64_t acc32 = 0;
+            for (int i = 0; i + 1 < np; ++i) {
+                acc32 += parts[i];
+                const int64_t t = std::min<int64_t>(T, (T * acc32 / 32 + 63) / 64 * 64);
                 if (L->ep || (t > bounds.back() && t < T)) bounds.push_back(t);
             }
         }
