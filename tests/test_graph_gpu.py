@@ -135,3 +135,41 @@ def test_small_host_calls_with_every_launch_mode(monkeypatch, chain, graphs, rep
     assert (layer.graph_replays() >= 4) if replays else (layer.graph_replays() == 0)
     assert layer.device_status() == 0
     layer.close()
+
+
+@pytest.mark.parametrize("compute", ["f32", "bf16"])
+def test_a_call_inside_the_callers_own_capture_joins_that_graph(compute):
+    """A forward made while the caller's stream is being captured (here: torch.cuda.graph) must not start
+    a capture of its own: its kernels become nodes of the caller's graph, and replaying that graph
+    computes the layer on the buffers' current contents."""
+    bf16 = compute == "bf16"
+    layer, cfg, w = _layer(compute)
+    T, D, O = 48, 256, 256
+    buf = torch.empty((T, D), device="cuda", dtype=torch.bfloat16 if bf16 else torch.float32)
+    out = torch.empty((T, O), device="cuda", dtype=torch.float32)
+    call = layer.bind_forward(buf.t(), out, training=True)
+    x, xt = _inputs(T, D, 41, bf16)
+    buf.copy_(xt)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call()                                  # plain launches: sizes the workspace outside any capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    replays_before = layer.graph_replays()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        call()
+    assert layer.graph_replays() == replays_before          # no graph of the library's own was involved
+    for seed in (42, 43):
+        x, xt = _inputs(T, D, seed, bf16)
+        buf.copy_(xt)
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        ref_out, ref_loss, _ = orc.moe_layer_forward(cfg, w, x, training=True)
+        assert rel_inf(out.cpu().numpy(), ref_out) < (2e-2 if bf16 else 1e-5)
+        assert abs(float(call.loss.item()) - float(ref_loss)) <= 1e-5 * abs(float(ref_loss))
+    assert layer.device_status() == 0
+    del g
+    layer.close()
