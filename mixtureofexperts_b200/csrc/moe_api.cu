@@ -139,6 +139,9 @@ struct moe_layer {
     // small call is one copy in, three copies out and a single wait.
     char* pin = nullptr;
     size_t pin_bytes = 0;
+    // device side of small host calls: [status word, padded to 256 | out | optional outputs], one block
+    // so that everything a small call returns comes back in a single copy (`status` points at its start)
+    char* small_dev = nullptr;
     static constexpr size_t PIN_SMALL_CALL = 1 << 20;   // calls moving no more than this go through `pin`
     // chunked host calls: copy-in / compute / copy-out overlap on three streams
     static constexpr int MAX_CHUNKS = 8;
@@ -871,7 +874,9 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     if ((rc = dev_alloc(&L->expert_offset, (size_t)L->E + 1))) return cleanup(rc);
     if ((rc = dev_alloc(&L->tile_prefix, (size_t)L->E + 1))) return cleanup(rc);
     if ((rc = dev_alloc(&L->loss_dev, 1))) return cleanup(rc);
-    if ((rc = dev_alloc(&L->status, 1))) return cleanup(rc);
+    if (cudaMalloc(reinterpret_cast<void**>(&L->small_dev), 256 + moe_layer::PIN_SMALL_CALL) != cudaSuccess)
+        return cleanup(fail(MOE_ERR_CUDA, "cudaMalloc failed"));
+    L->status = reinterpret_cast<int32_t*>(L->small_dev);
     if (router_tc_e_pad(L->E_router) && cfg->input_dim % 8 == 0) {
         L->rplan = router_tc_plan_create();
         if (cudaMalloc(&L->router_w3, (size_t)3 * router_tc_e_pad(L->E_router) * cfg->input_dim * 2) != cudaSuccess)
@@ -912,7 +917,7 @@ int moe_layer_destroy(moe_layer_t* L) {
     dev_free(L->expert_offset);
     dev_free(L->tile_prefix);
     dev_free(L->loss_dev);
-    dev_free(L->status);
+    dev_free(L->small_dev);
     dev_free(L->graph_small);
     dev_free(L->hx);
     dev_free(L->hout);
@@ -1337,10 +1342,16 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
                  o_logits = take(opt->logits, (size_t)T * er * 4), o_tpe = take(opt->tokens_per_expert, (size_t)L->E * 8),
                  o_ent = take(opt->routing_entropy, 4);
     int rc;
+    // small calls: status, output and optional outputs share one device block and one pinned block
+    const size_t out_off = 256, opt_off = out_off + ((ob + 255) & ~(size_t)255), x_off = opt_off + ((off + 255) & ~(size_t)255);
+    const bool small_call = !L->ep && x_off + xb <= moe_layer::PIN_SMALL_CALL;
     if ((rc = grow(&L->hx, &L->hx_bytes, xb))) return rc;
-    if ((rc = grow(reinterpret_cast<void**>(&L->hout), &L->hout_bytes, ob))) return rc;
-    if ((rc = grow(&L->hopt, &L->hopt_bytes, off))) return rc;
-    char* ob_dev = reinterpret_cast<char*>(L->hopt);
+    if (!small_call) {
+        if ((rc = grow(reinterpret_cast<void**>(&L->hout), &L->hout_bytes, ob))) return rc;
+        if ((rc = grow(&L->hopt, &L->hopt_bytes, off))) return rc;
+    }
+    float* out_dev = small_call ? reinterpret_cast<float*>(L->small_dev + out_off) : L->hout;
+    char* ob_dev = small_call ? L->small_dev + opt_off : reinterpret_cast<char*>(L->hopt);
     moe_forward_outputs_t d;
     d.loss = opt->loss ? reinterpret_cast<float*>(ob_dev + o_loss) : nullptr;
     d.indices = opt->indices ? reinterpret_cast<int32_t*>(ob_dev + o_idx) : nullptr;
@@ -1489,20 +1500,17 @@ int moe_layer_forward_host(moe_layer_t* L, const void* x, int x_dtype, int64_t T
         CUDA_TRY(cudaMemcpy(&stc, L->status, sizeof(stc), cudaMemcpyDeviceToHost));
         return status_to_rc(L, stc);
     }
-    const size_t x_off = 256, out_off = x_off + ((xb + 255) & ~(size_t)255), opt_off = out_off + ((ob + 255) & ~(size_t)255);
-    if (opt_off + off <= moe_layer::PIN_SMALL_CALL && !L->ep) {
-        if ((rc = grow_pinned(&L->pin, &L->pin_bytes, opt_off + off))) return rc;
+    if (small_call) {
+        if ((rc = grow_pinned(&L->pin, &L->pin_bytes, x_off + xb))) return rc;
         if (xb) {
             memcpy(L->pin + x_off, x, xb);
             CUDA_TRY(cudaMemcpyAsync(L->hx, L->pin + x_off, xb, cudaMemcpyHostToDevice, s));
         }
-        // Between a copy in and the copies out, chained plain launches beat a graph replay (measured on
+        // Between a copy in and the copy out, chained plain launches beat a graph replay (measured on
         // B200, one position of a 512/1376 layer: 57 against 62-66 us per call): the first kernel starts
         // sooner after the copy than a graph does.  MOE_B200_CHAIN=0 brings the replay back.
-        if ((rc = forward_small(L, L->hx, x_dtype, T, training, L->hout, &d, s, !L->chain_enabled))) return rc;
-        if (ob) CUDA_TRY(cudaMemcpyAsync(L->pin + out_off, L->hout, ob, cudaMemcpyDeviceToHost, s));
-        if (off) CUDA_TRY(cudaMemcpyAsync(L->pin + opt_off, L->hopt, off, cudaMemcpyDeviceToHost, s));
-        CUDA_TRY(cudaMemcpyAsync(L->pin, L->status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+        if ((rc = forward_small(L, L->hx, x_dtype, T, training, out_dev, &d, s, !L->chain_enabled))) return rc;
+        CUDA_TRY(cudaMemcpyAsync(L->pin, L->small_dev, opt_off + off, cudaMemcpyDeviceToHost, s));
         CUDA_TRY(cudaStreamSynchronize(s));
         if (ob) memcpy(out, L->pin + out_off, ob);
         const char* po = L->pin + opt_off;
