@@ -220,13 +220,18 @@ router_kernel(const RouterParams p) {
     constexpr int NJ = (E_PAD + 31) / 32;
     float lse2 = 0.f;
     double ent = 0.0;
-    for (int tok = warp; tok < RT_BT; tok += NWARPS) {
+    // routers of at most 8 / 16 columns: four / two tokens of a warp are gated side by side
+    constexpr int GW = (E_PAD <= 8) ? 8 : ((E_PAD <= 16) ? 16 : 32);
+    constexpr int TPW = 32 / GW;
+    for (int base = warp * TPW; base < RT_BT; base += NWARPS * TPW) {
+        if (tok0 + base >= p.T) break;
+        const int tok = base + lane / GW;
         const int64_t t = tok0 + tok;
-        if (t >= p.T) break;
+        const bool active = t < p.T;
         float lg[NJ], nl[NJ];
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
-            const int e = lane + 32 * j;
+            const int e = lane % GW + 32 * j;
             float s = 0.f, sn = 0.f;
             if (e < E_PAD) {
 #pragma unroll
@@ -239,7 +244,7 @@ router_kernel(const RouterParams p) {
             lg[j] = s;
             nl[j] = sn;
         }
-        gate_token<NJ, false>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent);
+        gate_token<NJ, false, GW>(c, t, lg, nl, lane, s_cnt, s_psum[warp], lse2, ent, 0.f, active);
     }
     if (lane == 0) {
         s_lse2[warp] = lse2;

@@ -30,14 +30,24 @@ struct GateCtx {
     float* u_logits;
 };
 
+// Reductions over groups of W consecutive lanes (W = 32: the whole warp).
+template <int W = 32>
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
-    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    for (int o = W / 2; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+template <int W = 32>
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
-    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    for (int o = W / 2; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Sum over the 32 / W lanes that hold the same column of different tokens (offsets W, 2W, ...).
+template <int W>
+__device__ __forceinline__ float across_tokens_sum(float v) {
+#pragma unroll
+    for (int o = W; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
 __device__ __forceinline__ double warp_sum_d(double v) {
@@ -46,7 +56,10 @@ __device__ __forceinline__ double warp_sum_d(double v) {
     return v;
 }
 
-// One token, one warp.  lg[j] is the raw logit of router column lane + 32*j.
+// One token per group of W lanes (W = 32: one token per warp; W = 8 or 16, for routers of at most W
+// columns: 4 or 2 tokens per warp side by side, NJ = 1).  lg[j] is the raw logit of router column
+// (lane % W) + 32*j of the group's token `t`; `active` is false for a group past the last token: it
+// runs along (the warp's shuffles need every lane) but leaves no trace.
 // Accumulators (per warp, lane-owned columns): s_psum[e] += prob, returns lse^2 and entropy.
 //
 // PROBE = true (tensor-core router): the logits carry a rounding error of about 1.5e-6 times their
@@ -54,10 +67,14 @@ __device__ __forceinline__ double warp_sum_d(double v) {
 // (k+1)-th probability, and if two neighbours of the top k+1 are closer than probe_rel * max(1,
 // largest |logit|) -- relative differences of probabilities are differences of logits -- the function
 // returns false WITHOUT side effects and the caller gates the token again from exact logits.
-template <int NJ, bool PROBE>
-__device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ], const float (&nl)[NJ], int lane,
-                                           int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc, float probe_rel = 0.f) {
+template <int NJ, bool PROBE, int W = 32>
+__device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const float (&lg_in)[NJ], const float (&nl)[NJ], int lane_in_warp,
+                                           int* s_cnt, float* s_psum, float& lse2_acc, double& ent_acc, float probe_rel = 0.f,
+                                           bool active = true) {
+    static_assert(W == 32 || (NJ == 1 && !PROBE && (W == 8 || W == 16)), "several tokens per warp: narrow routers only");
     constexpr unsigned FULL = 0xffffffffu;
+    const int lane = lane_in_warp % W;                     // column owner inside the token's lane group
+    const unsigned GROUP = W == 32 ? FULL : (((1u << (W % 32)) - 1u) << ((lane_in_warp / W) * W));
     // Training-time router noise (src/core/router.jl:32-41): logits + noise_scale * randn (times
     // softplus(noise_weight x) when the router has a noise network, nl[] = those logits) feed the
     // gate and are the logits the router returns; the z-loss is computed by a second, noise-free
@@ -70,7 +87,7 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
         const bool in = e < c.E_router;
         const float b = (in && c.bias) ? c.bias[e] : 0.f;
         float nz = 0.f;
-        if (in && c.noise) {
+        if (in && c.noise && active) {
             float draw = c.noise[t * c.E_router + e];
             // NNlib.softplus(x) = log1p(exp(-|x|)) + relu(x)
             if (c.noise_net) draw *= log1pf(expf(-fabsf(nl[j]))) + fmaxf(nl[j], 0.f);
@@ -89,14 +106,14 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
             if (valid[j]) m = fmaxf(m, lprob[j]);
-        m = warp_max(m);
+        m = warp_max<W>(m);
         float s = 0.f;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             pr[j] = valid[j] ? expf(lprob[j] - m) : 0.f;
             s += pr[j];
         }
-        s = warp_sum(s);
+        s = warp_sum<W>(s);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) pr[j] = pr[j] / s;
     }
@@ -105,14 +122,14 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
             if (valid[j]) m = fmaxf(m, lsel[j]);
-        m = warp_max(m);
+        m = warp_max<W>(m);
         float s = 0.f;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             psel[j] = valid[j] ? expf(lsel[j] - m) : 0.f;
             s += psel[j];
         }
-        s = warp_sum(s);
+        s = warp_sum<W>(s);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) psel[j] = psel[j] / s;
     } else {
@@ -143,8 +160,8 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
                 bk = key[j];
                 bj = j;
             }
-        const int m = __reduce_max_sync(FULL, bk);
-        int bi = __reduce_min_sync(FULL, (bk == m && m != INT_MIN) ? lane + 32 * bj : INT_MAX);
+        const int m = __reduce_max_sync(GROUP, bk);
+        int bi = __reduce_min_sync(GROUP, (bk == m && m != INT_MIN) ? lane + 32 * bj : INT_MAX);
         const float best = m == INT_MIN ? -2.f : __int_as_float(m);
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
@@ -163,29 +180,29 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
 
 #pragma unroll
     for (int j = 0; j < NJ; ++j)
-        if (lane + 32 * j < c.E_router && c.u_logits) c.u_logits[t * c.E_router + lane + 32 * j] = lprob[j];
+        if (active && lane + 32 * j < c.E_router && c.u_logits) c.u_logits[t * c.E_router + lane + 32 * j] = lprob[j];
     // logsumexp over every router column (src/balancing/losses.jl:103-114)
     {
         float m = -FLT_MAX;
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
             if (lane + 32 * j < c.E_router) m = fmaxf(m, lclean[j]);
-        m = warp_max(m);
+        m = warp_max<W>(m);
         float s = 0.f;
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
             if (lane + 32 * j < c.E_router) s += expf(lclean[j] - m);
-        s = warp_sum(s);
+        s = warp_sum<W>(s);
         const float lse = m + logf(s);
-        lse2_acc += lse * lse;
+        lse2_acc += across_tokens_sum<W>(active ? lse * lse : 0.f);
     }
     // gates = selected / sum(selected), summed in slot order like the reference
     float gsum = 0.f;
-    for (int s = 0; s < c.k; ++s) gsum += __shfl_sync(FULL, my_v, s);
+    for (int s = 0; s < c.k; ++s) gsum += __shfl_sync(FULL, my_v, s, W);
     const float g = my_v / gsum;
 
     const int n_shared_slots = (c.shared_mode == MOE_SHARED_NONE) ? 0 : c.S;
-    if (lane < c.k && my_i != INT_MAX) {
+    if (active && lane < c.k && my_i != INT_MAX) {
         const int layer_id = my_i + (c.shared_mode == MOE_SHARED_LAYER_BLEND ? c.S : 0);
         float gi = g;
         if (c.shared_mode == MOE_SHARED_GATING) gi = (float)((double)g * (1.0 - (double)c.S / (double)c.k_tot));
@@ -202,7 +219,7 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
             if (c.u_gate) c.u_gate[t * c.k_tot + slot] = gi;
         }
     }
-    if (lane < n_shared_slots) {
+    if (active && lane < n_shared_slots) {
         const float gs = (c.shared_mode == MOE_SHARED_GATING) ? 1.0f / (float)c.k_tot : 0.5f / (float)c.S;
         if (c.idx) c.idx[t * c.k_tot + lane] = lane + c.idx_base;
         if (c.gate) c.gate[t * c.k_tot + lane] = gs;
@@ -220,8 +237,9 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int e = lane + 32 * j;
-        if (e < c.E_probs) {
-            float pv;
+        const bool has = e < c.E_probs;
+        float pv = 0.f;
+        if (has && active) {
             if (c.shared_mode == MOE_SHARED_GATING) {
                 pv = (e < c.S) ? 1.0f / (float)c.E
                                : (float)((double)pr[j] * (1.0 - (double)c.S / (double)c.E));
@@ -229,12 +247,17 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
                 pv = pr[j];
             }
             if (c.u_probs) c.u_probs[t * c.E_probs + e] = pv;
-            s_psum[e] += pv;
             if (c.want_entropy) ent -= pv * logf(pv + 1e-8f);
+        }
+        if (W == 32) {
+            if (has) s_psum[e] += pv;
+        } else {
+            const float all = across_tokens_sum<W>(pv);      // the warp's tokens, always in the same order
+            if (has && lane_in_warp < W) s_psum[e] += all;
         }
     }
     (void)shared_scale;
-    if (c.want_entropy) ent_acc += (double)warp_sum(ent);
+    if (c.want_entropy) ent_acc += (double)warp_sum<32>(ent);
     return true;
 }
 
