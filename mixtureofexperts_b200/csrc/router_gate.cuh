@@ -101,6 +101,7 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
     }
     // softmax over the routed columns (NNlib.softmax: subtract max, exp, divide by the sum)
     float pr[NJ], psel[NJ];
+    float soft_m, soft_s;   // maximum and sum of exponentials of the probability softmax
     {
         float m = -FLT_MAX;
 #pragma unroll
@@ -114,6 +115,8 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
             s += pr[j];
         }
         s = warp_sum<W>(s);
+        soft_m = m;
+        soft_s = s;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) pr[j] = pr[j] / s;
     }
@@ -181,8 +184,13 @@ __device__ __forceinline__ bool gate_token(const GateCtx& c, int64_t t, const fl
 #pragma unroll
     for (int j = 0; j < NJ; ++j)
         if (active && lane + 32 * j < c.E_router && c.u_logits) c.u_logits[t * c.E_router + lane + 32 * j] = lprob[j];
-    // logsumexp over every router column (src/balancing/losses.jl:103-114)
-    {
+    // logsumexp over every router column (src/balancing/losses.jl:103-114).  Without noise, without a
+    // gates-only bias and with every column routed, these are the logits of the softmax above: its
+    // maximum and sum are the same numbers, computed the same way.
+    if (c.r0 == 0 && !c.noise && !(c.bias && c.bias_gates_only)) {
+        const float lse = soft_m + logf(soft_s);
+        lse2_acc += across_tokens_sum<W>(active ? lse * lse : 0.f);
+    } else {
         float m = -FLT_MAX;
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
