@@ -17,7 +17,8 @@ benchmark configurations; weights N(0, 0.02^2), activations N(0, 1), seeded):
 
 Keys of the line beyond the usual ones:
   roofline        the dominant kernel (expert GEMM 1): algorithmic FLOPs / mean CUDA-event time of
-                  the timed steps, against the measured cuBLAS BF16 peaks (burst and sustained)
+                  the timed steps, against the measured cuBLAS BF16 peaks (burst and sustained);
+                  `library_same_gpu`: cuBLAS timed on this GPU on the same GEMM shapes and data
   e2e             the same metric through moe_layer_forward_host with pinned host buffers
   cpu_baseline    the CPU restatement of the reference path on the host cores, same token count
   parity          outside the timed region: every rank compares its tokens' expert ids (all local
@@ -530,6 +531,44 @@ def measure_other(name, torch, peaks, steps=10, warmup=3):
     return res
 
 
+def library_gemm_yardstick(w, T, stages, torch, steps=20, warmup=5):
+    """cuBLAS (torch.matmul) on THIS GPU, on the expert GEMMs' shapes and value distributions, as a
+    yardstick beside `roofline`: the pool's GPUs differ by several percent and every run sits at the
+    power limit, so a figure from the same box says more about the kernels than the pool-wide peak.
+    One GEMM per stage over all (token, expert) rows against ONE expert's weights -- no grouping,
+    no gate * up epilogue, plain BF16 stores: the library's best case for the same FLOPs -- and the
+    two alternated like a layer does.  Not on the product path."""
+    rows, D, H, O = T * (w["k"] + w["S"]), w["D"], w["H"], w["O"]
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(SEED + 99)
+    mk = lambda r, c, std: (torch.randn((r, c), device=dev, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
+    a1, w13 = mk(rows, D, 1.0), mk(2 * H, D, w["std"])
+    h_in, w2 = mk(rows, H, 0.05), mk(O, H, w["std"])
+    h_out = torch.empty((rows, 2 * H), device=dev, dtype=torch.bfloat16)
+    y = torch.empty((rows, O), device=dev, dtype=torch.bfloat16)
+    for _ in range(warmup):
+        torch.matmul(a1, w13.t(), out=h_out)
+        torch.matmul(h_in, w2.t(), out=y)
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        torch.matmul(a1, w13.t(), out=h_out)
+        ev[2 * i + 1].record()
+        torch.matmul(h_in, w2.t(), out=y)
+        ev[2 * i + 2].record()
+    torch.cuda.synchronize()
+    t1 = sum(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(steps)) / steps
+    t2 = sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(steps)) / steps
+    f1, f2 = 2.0 * rows * 2 * H * D, 2.0 * rows * O * H
+    ours = stages.get("gemm1", 0.0) + stages.get("gemm2", 0.0)
+    return {"what": "torch.matmul (cuBLAS) BF16 on this GPU: all rows x one expert's [W1;W3], then x W2, alternated for "
+                    f"{steps} steps after {warmup}; no grouping, no activation epilogue",
+            "gemm1_ms": t1, "gemm2_ms": t2, "gemm1_tflops": f1 / t1 / 1e9, "gemm2_tflops": f2 / t2 / 1e9,
+            "pair_ms": t1 + t2, "pair_tflops": (f1 + f2) / (t1 + t2) / 1e9,
+            "ours_pair_ms": ours, "ours_vs_library": (t1 + t2) / ours if ours > 0 else None}
+
+
 def measure_llama_ffn(torch, peaks, calls=1000, warmup=3000):
     """The MoE FFN of a converted Llama2 layer as the generation loop drives it: one host call of
     moe_layer_forward_host per position (decode, T = 1) and one call for a whole 64-token prompt
@@ -718,6 +757,8 @@ def main():
             cpu = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "s_per_step": dt_cpu,
                    "sample": note + f", {done} timed pass(es)"}
         others = None
+        if world == 1 and not args.no_others and full_size and w["dtype"] == "bf16":
+            roof["library_same_gpu"] = library_gemm_yardstick(w, T, stages, torch, args.steps, args.warmup)
         if world == 1 and not args.no_others and full_size:
             torch.cuda.empty_cache()
             others = {n: measure_other(n, torch, peaks) for n in ("c4", "c1") if n != name}
