@@ -757,12 +757,13 @@ def main():
             cpu = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "s_per_step": dt_cpu,
                    "sample": note + f", {done} timed pass(es)"}
         others = None
-        if world == 1 and not args.no_others and full_size and w["dtype"] == "bf16":
-            roof["library_same_gpu"] = library_gemm_yardstick(w, T, stages, torch, args.steps, args.warmup)
         if world == 1 and not args.no_others and full_size:
             torch.cuda.empty_cache()
             others = {n: measure_other(n, torch, peaks) for n in ("c4", "c1") if n != name}
             others["c2"] = measure_llama_ffn(torch, peaks)
+        if world == 1 and not args.no_others and full_size and w["dtype"] == "bf16":
+            # last: two seconds of library GEMMs at the power limit would colour whatever is measured after them
+            roof["library_same_gpu"] = library_gemm_yardstick(w, T, stages, torch, args.steps, args.warmup)
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
