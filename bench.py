@@ -444,11 +444,11 @@ def roofline_of(w, name, T, stages, ms_step, peaks, tile_rows, world, clocks, fu
     mhz = (clocks or {}).get("sm_mhz")
     if w["dtype"] == "bf16" and stages.get("gemm1", 0) > 0 and world == 1:
         ach = f_g1 / (stages["gemm1"] * 1e-3) / 1e12
-        pair = tile_rows == 256
-        kernel = "group_gemm_tc2_kernel<1>" if pair else "group_gemm_tc_kernel<1>"
+        kernel = {0: "group_gemm_tc_kernel<1>", 1: "group_gemm_tc2_kernel<1>", 2: "group_gemm_tc_dual_kernel<1>"}[tile_rows]
+        kind = {0: "", 1: " (CTA pairs)", 2: " (two accumulators per CTA)"}[tile_rows]
         traffic, note = recorded_dram_traffic(name, kernel) if full_size else (None, "not the recorded workload size")
         burst, sust = peaks["bf16_tflops"], peaks["bf16_tflops_sustained"]
-        return {"bound": "tensor", "kernel": kernel + (" (CTA pairs)" if pair else "") + ": x W1^T, x W3^T, act*up",
+        return {"bound": "tensor", "kernel": kernel + kind + ": x W1^T, x W3^T, act*up",
                 "achieved": ach, "peak": burst, "unit": "TFLOP/s", "frac": ach / burst,
                 "frac_burst": ach / burst, "frac_sustained": ach / sust, "peak_sustained": sust,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 8192^3: burst {burst} (best of 10), sustained {sust} (4 s loop under the "
@@ -503,7 +503,7 @@ def measure_other(name, torch, peaks, steps=10, warmup=3):
     ms_step = ms_total / steps
     res = {"workload": f"{name}: {w['desc']}", "ms_per_step": ms_step, "tokens_per_s": T / (ms_step * 1e-3),
            "steps": steps, "warmup": warmup, "stage_ms": stages, "gpu_launches": launches,
-           "roofline": roofline_of(w, name, T, stages, ms_step, peaks, layer.tile_rows(T), 1, None, True),
+           "roofline": roofline_of(w, name, T, stages, ms_step, peaks, layer.gemm_kernel(T), 1, None, True),
            "loss": float(loss.item()), "device_status": layer.device_status(), "graph_replays": replays}
     if w["dtype"] == "f32":
         res["timing_note"] = ("ms_per_step: bare moe_layer_forward calls with bound arguments (the library replays one captured "
@@ -744,7 +744,7 @@ def main():
     if not args.no_parity:
         parity = parity_block(w, layer, x, torch, rank, world, dist, device)
 
-    tile_rows = layer.tile_rows(T)
+    tile_rows = layer.gemm_kernel(T)     # 0 / 1 / 2: which tensor-core kernel this batch gets
     layer.close()
     del layer
     fail = None

@@ -27,8 +27,9 @@
  *
  * Environment switches (experiments and comparisons; defaults are what the measurements use).
  * The first three are read when a handle is created, the others once per process:
- *   MOE_B200_PAIR=0|1          force the single-CTA (128-row tiles) or the CTA-pair (256-row tiles,
- *                              cta_group::2) tensor-core GEMM kernels instead of the per-batch choice
+ *   MOE_B200_PAIR=0|1|2        force the single-CTA (128-row tiles), the CTA-pair (256-row tiles, cta_group::2)
+ *                              or the two-accumulator (256-row tiles, one CTA) tensor-core GEMM kernels
+ *                              instead of the per-batch choice
  *   MOE_B200_HOST_CHUNKS=n     moe_layer_forward_host cuts batches of 8192 tokens and more into n
  *                              equal chunks (1 = no chunking) instead of its default schedule of 2/12/10/6/2 thirty-seconds
  *   MOE_B200_HOST_TIMELINE=1   print every chunk's copy and compute times to stderr
@@ -249,6 +250,12 @@ int moe_layer_stage_ms(moe_layer_t*, int calls_back, float ms[7]);
  * tensor-core kernel, 128 = single-CTA tensor-core kernel, 16 = FP32 kernels (no counterpart in the
  * reference: a profiling aid).  Negative = error. */
 int moe_layer_tile_rows(moe_layer_t*, int64_t T);
+
+/* Which tensor-core kernel a batch of T tokens gets on a layer without expert parallelism: 0 = single
+ * CTAs on 128-row tiles, 1 = CTA pairs (cta_group::2) on 256-row tiles, 2 = single CTAs with two
+ * accumulators sharing a weight tile on 256-row tiles; always 0 for FP32 layers.  A profiling aid
+ * like moe_layer_tile_rows.  Negative = error. */
+int moe_layer_gemm_kernel(moe_layer_t*, int64_t T);
 
 /* Number of kernel launches of this library issued through the handle since creation. */
 int64_t moe_layer_launch_count(const moe_layer_t*);

@@ -23,7 +23,7 @@ EXPERT_GATED, EXPERT_STANDARD = 0, 1
 EXPORTS = [
     "moe_layer_create", "moe_layer_set_expert", "moe_layer_set_expert_standard", "moe_layer_set_router", "moe_layer_set_router_noise", "moe_layer_weights_image_bytes", "moe_layer_export_weights", "moe_layer_import_weights", "moe_layer_set_aux_free", "moe_layer_aux_free_state", "moe_layer_set_router_noise_network", "moe_layer_dims",
     "moe_layer_forward", "moe_layer_forward_host", "moe_compute_gates", "moe_compute_gates_jitter", "moe_compute_loss",
-    "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_tile_rows", "moe_layer_launch_count", "moe_layer_router_rechecks",
+    "moe_layer_set_profiling", "moe_layer_stage_ms", "moe_layer_tile_rows", "moe_layer_gemm_kernel", "moe_layer_launch_count", "moe_layer_router_rechecks",
     "moe_layer_graph_replays",
     "moe_layer_device_status", "moe_selftest_bounded_wait", "moe_ep_unique_id", "moe_ep_init", "moe_ep_set_timeout_ms",
     "moe_ep_layout", "moe_layer_destroy",
@@ -97,6 +97,7 @@ def _load():
     lib.moe_layer_set_profiling.argtypes = [vp, i32]
     lib.moe_layer_stage_ms.argtypes = [vp, i32, C.POINTER(C.c_float)]
     lib.moe_layer_tile_rows.argtypes = [vp, i64]
+    lib.moe_layer_gemm_kernel.argtypes = [vp, i64]
     lib.moe_layer_launch_count.argtypes = [vp]
     lib.moe_layer_router_rechecks.argtypes = [vp, C.POINTER(C.c_int64)]
     lib.moe_layer_graph_replays.argtypes = [vp, C.POINTER(C.c_int64)]

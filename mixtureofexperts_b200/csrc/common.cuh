@@ -257,6 +257,8 @@ bool tc_plan_set_x(TcGemmPlan*, const void* x, int64_t T, int D);
 // mode 1: gated pair with act(gate)*up epilogue; mode 2: single matrix (+ bias, + activation).
 int launch_group_gemm_tc(const TcGemmPlan*, int stage, int mode, const GroupGemmParams& p, int max_tiles,
                          int num_sms, cudaStream_t s);
+int launch_group_gemm_tc_dual(const TcGemmPlan*, int stage, int mode, const GroupGemmParams& p, int max_tiles, int num_sms,
+                              cudaStream_t s);
 int launch_group_gemm_tc2(const TcGemmPlan*, int stage, int mode, const GroupGemmParams& p, int max_tiles,
                           int num_sms, cudaStream_t s);
 // one thread waits limit_us on an mbarrier nobody arrives on; 0 on success, the recorded status and waited time out

@@ -194,7 +194,7 @@ struct moe_layer {
     bool capturing = false;         // forward_small is recording a graph: its launches are not chained
 
     // experiment switches of the environment, read once when the handle is created
-    int force_pair = -1;            // MOE_B200_PAIR = 0 / 1: force single-CTA / CTA-pair GEMM kernels
+    int force_pair = -1;            // MOE_B200_PAIR = 0 / 1 / 2: force the single-CTA / CTA-pair / two-accumulator GEMM kernels
     int host_chunks = 0;            // MOE_B200_HOST_CHUNKS = n: n equal chunks per large host call
     bool host_timeline = false;     // MOE_B200_HOST_TIMELINE = 1: print every chunk's copy/compute times
 };
@@ -349,25 +349,31 @@ int check_ready(moe_layer* L) {
     return MOE_OK;
 }
 
-// m-tile height of the expert GEMMs: CTA pairs (256-row tiles, cta_group::2) or single CTAs (128-row
-// tiles) on the tensor-core path.  Measured on B200: with long K (Mixtral widths: d_model 4096, ffn
-// 14336) the single-CTA kernel wins by ~2.5 % in long, power-capped runs (the pair kernel is 2 %
-// faster per clock but settles at lower clocks); with short K (d 2048, hidden 1408, 66 experts) a
-// single CTA's four 48 KB stages cover too little load latency and the pair kernel, whose CTAs each
-// hold half of B and so have six stages, is 6.5 % faster for the whole layer.  Hence: pairs when both
-// GEMMs have short K and an expert has enough rows to fill 256-row tiles.  MOE_B200_PAIR = 0 / 1
-// forces the choice.
+// Which tensor-core kernel runs the expert GEMMs of a batch: 0 = single CTAs on 128-row tiles
+// (expert_tc.cu), 1 = CTA pairs with cta_group::2 on 256-row tiles (expert_tc2.cu), 2 = single CTAs with
+// two accumulators sharing a B tile on 256-row tiles (expert_tc_dual.cu).  Measured on B200, alternating
+// in one call.  Long K (Mixtral widths: d_model 4096, ffn 14336, ~4096 rows per expert): 9.00-9.12 ms per
+// layer with the two-accumulator kernel against 9.44 ms with single tiles and 9.65 ms with CTA pairs --
+// the kernels run at the board's power limit and the two-accumulator kernel moves a third less from L2 per
+// FLOP.  Short K (d 2048, hidden 1408, 66 experts): 4.07-4.10 ms with CTA pairs against 4.20-4.33 ms
+// (two accumulators) and 4.28 ms (single): a K loop of 22-32 blocks ends before the three 64 KB stages of
+// the two-accumulator kernel or the four of the single-CTA kernel have hidden the load latency, while the
+// pair kernel's six stages do, and the epilogue gap of the two-accumulator kernel weighs more per tile.
+// 256-row tiles waste half a tile per expert on average, twice what 128-row tiles do: with long K the
+// two-accumulator kernel is ahead at 4096 rows per expert (-3.2 %), level at 2048, behind at 1024 (+3 %)
+// and 512 (+8..14 %), so it takes experts of 3072 rows and more; the pair kernel needs an expert to fill
+// two tiles.  MOE_B200_PAIR = 0 / 1 / 2 forces the choice.
+int pick_gemm_kernel(const moe_layer* L, int64_t rows, int n_experts) {
+    if (L->cfg.compute_dtype != MOE_DTYPE_BF16) return 0;
+    if (L->force_pair >= 0) return L->force_pair;
+    const int64_t per_expert = n_experts > 0 ? rows / n_experts : 0;
+    if ((int64_t)L->cfg.input_dim + L->cfg.hidden_dim <= 6144) return per_expert >= 2 * TC_PAIR_TILE_M ? 1 : 0;
+    return per_expert >= 12 * TC_PAIR_TILE_M ? 2 : 0;
+}
+
 int pick_tile_m(const moe_layer* L, int64_t rows, int n_experts) {
     if (L->cfg.compute_dtype != MOE_DTYPE_BF16) return F32_TILE_M;
-    const int env_pair = L->force_pair;
-    bool pair;
-    if (env_pair >= 0) {
-        pair = env_pair > 0;
-    } else {
-        const int64_t per_expert = n_experts > 0 ? rows / n_experts : 0;
-        pair = (int64_t)L->cfg.input_dim + L->cfg.hidden_dim <= 6144 && per_expert >= 2 * TC_PAIR_TILE_M;
-    }
-    return pair ? TC_PAIR_TILE_M : TC_TILE_M;
+    return pick_gemm_kernel(L, rows, n_experts) ? TC_PAIR_TILE_M : TC_TILE_M;
 }
 
 // The grouped GEMM pair on `rows_cap` rows described by (expert_offset, tile_prefix).
@@ -404,7 +410,9 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.bias = standard ? L->b1 : nullptr;
     g.epilogue_act = standard ? c.activation : -1;
     g.inplace_experts = tc ? inplace_experts : 0;
-    if (pair) n = launch_group_gemm_tc2(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
+    const bool dual = pair && pick_gemm_kernel(L, rows, n_experts) == 2;   // 256-row tiles on one CTA with two accumulators
+    if (dual) n = launch_group_gemm_tc_dual(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
+    else if (pair) n = launch_group_gemm_tc2(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
     else if (tc) n = launch_group_gemm_tc(L->plan, 1, mode1, g, max_mtiles * ntile1, L->num_sms, s);
     else n = launch_group_gemm_f32(g, mode1, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 1 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -423,7 +431,8 @@ int run_experts(moe_layer* L, const void* a_in, void* h_buf, void* y_buf, const 
     g.seg_start = seg_start;      // expert-parallel peer mode: rows go straight to the token owners
     g.seg_dst = seg_dst;
     g.seg_per_expert = seg_per_expert;
-    if (pair) n = launch_group_gemm_tc2(L->plan, 2, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
+    if (dual) n = launch_group_gemm_tc_dual(L->plan, 2, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
+    else if (pair) n = launch_group_gemm_tc2(L->plan, 2, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
     else if (tc) n = launch_group_gemm_tc(L->plan, 2, 2, g, max_mtiles * ((c.output_dim + 255) / 256), L->num_sms, s);
     else n = launch_group_gemm_f32(g, 2, max_mtiles, rows, L->num_sms, s);
     if (n < 0) return fail(MOE_ERR_CUDA, "expert GEMM 2 launch failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -856,7 +865,7 @@ int moe_layer_create(const moe_config_t* cfg, int device, moe_layer_t** out) {
     L->E_probs = L->E_router;
     L->e_lo = 0;
     L->e_hi = L->E;
-    if (const char* ev = getenv("MOE_B200_PAIR")) L->force_pair = atoi(ev) > 0 ? 1 : 0;
+    if (const char* ev = getenv("MOE_B200_PAIR")) L->force_pair = atoi(ev) >= 2 ? 2 : (atoi(ev) > 0 ? 1 : 0);
     if (const char* ev = getenv("MOE_B200_HOST_CHUNKS")) L->host_chunks = atoi(ev) > 0 ? atoi(ev) : 0;
     if (const char* ev = getenv("MOE_B200_HOST_TIMELINE")) L->host_timeline = atoi(ev) > 0;
     if (const char* ev = getenv("MOE_B200_ROUTER_TC")) L->router_tc_enabled = atoi(ev) != 0;
@@ -1643,6 +1652,11 @@ int moe_layer_router_rechecks(moe_layer_t* L, int64_t* tokens) {
 int moe_layer_tile_rows(moe_layer_t* L, int64_t T) {
     if (!L || T < 0) return fail(MOE_ERR_INVALID, "bad argument");
     return pick_tile_m(L, T * L->k_tot, L->E);
+}
+
+int moe_layer_gemm_kernel(moe_layer_t* L, int64_t T) {
+    if (!L || T < 0) return fail(MOE_ERR_INVALID, "bad argument");
+    return pick_gemm_kernel(L, T * L->k_tot, L->E);
 }
 
 int moe_layer_graph_replays(const moe_layer_t* L, int64_t* replays) {

@@ -622,6 +622,13 @@ class MoELayer:
         names = ["router", "scan_loss", "permute", "gemm1", "gemm2", "combine", "exchange"]
         return dict(zip(names, [float(v) for v in ms]))
 
+    def gemm_kernel(self, T: int) -> int:
+        """0 / 1 / 2: the single-CTA, CTA-pair or two-accumulator tensor-core kernel a batch of T tokens gets."""
+        n = int(_lib.lib.moe_layer_gemm_kernel(self._handle, int(T)))
+        if n < 0:
+            _lib.check(n)
+        return n
+
     def tile_rows(self, T: int) -> int:
         """Rows per m-tile of the expert GEMMs for a batch of T tokens (256: CTA-pair kernel, 128:
         single-CTA tensor-core kernel, 16: FP32 kernels)."""

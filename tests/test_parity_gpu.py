@@ -616,7 +616,7 @@ def test_f32_standard_expert_with_layer_blend_and_without_bias():
     layer.close()
 
 
-@pytest.mark.parametrize("pair", ["0", "1"])
+@pytest.mark.parametrize("pair", ["0", "1", "2"])
 @pytest.mark.parametrize("T,E,k,D,H,O", [(1000, 8, 2, 512, 1024, 512), (300, 4, 1, 136, 200, 104), (3, 66, 2, 128, 256, 128)])
 def test_bf16_standard_expert_on_both_tensor_core_kernels(pair, T, E, k, D, H, O, monkeypatch):
     monkeypatch.setenv("MOE_B200_PAIR", pair)
@@ -655,13 +655,17 @@ def test_bf16_tensor_core_path(T, E, k, D, H, O):
     assert err < BF16_TOL
 
 
-@pytest.mark.parametrize("pair", ["0", "1"])
+@pytest.mark.parametrize("pair", ["0", "1", "2"])
 def test_bf16_both_tensor_core_kernels_on_ragged_experts(pair, monkeypatch):
-    """MOE_B200_PAIR forces the single-CTA (128-row tiles) or the CTA-pair kernel (256-row tiles)
-    on a shape with empty experts, partial last tiles and widths off the tile edges."""
+    """MOE_B200_PAIR forces the single-CTA kernel (128-row tiles), the CTA-pair kernel or the two-accumulator
+    kernel (256-row tiles) on shapes with empty experts, partial last tiles (with and without rows in
+    their second half), widths off the tile edges, shared experts read in place, many tiles per expert."""
     monkeypatch.setenv("MOE_B200_PAIR", pair)
     assert run_case(777, 136, 200, 104, 10, "topk", 3, seed=91, compute="bf16", std=0.05) < BF16_TOL
     assert run_case(3, 128, 256, 128, 66, "topk", 2, seed=92, compute="bf16", std=0.05) < BF16_TOL
+    assert run_case(4500, 128, 256, 128, 2, "topk", 1, seed=93, compute="bf16", std=0.05) < BF16_TOL
+    assert run_case(1500, 256, 512, 264, 10, "shared", 3, 2, seed=94, compute="bf16", std=0.05) < BF16_TOL
+    assert run_case(2048, 1024, 1536, 512, 4, "topk", 2, seed=95, compute="bf16", std=0.03) < BF16_TOL
 
 
 def test_bf16_shared_gating_and_f32_input():
