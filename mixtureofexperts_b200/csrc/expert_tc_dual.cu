@@ -13,7 +13,8 @@
 // The price: two 128 x 256 FP32 accumulators are all 512 TMEM columns, so there is no second
 // accumulator set for the next tile while the epilogue drains this one.  Eight epilogue warps (four per
 // accumulator) keep that gap short, and each accumulator has its own "drained" barrier so the MMAs of
-// the next tile start on the first accumulator while the second is still being read.
+// the next tile start on the first accumulator while the second is still being read.  (GEMM 1's exposed
+// epilogue is bound by the special-function unit: hence one such operation per element in tc::act_fast.)
 //
 // Structure (320 threads): warp 0 = TMA producer (3-stage ring of 64 KB, full/empty mbarriers), warp 1 =
 // MMA issuer, warps 2..5 = epilogue of accumulator 0, warps 6..9 = epilogue of accumulator 1.  A pair
@@ -50,19 +51,6 @@ struct __align__(1024) DualStorage {
     uint32_t tmem_base;
     volatile int abort_flag;
 };
-
-// With both accumulators in use nothing hides the epilogue, and in GEMM 1 it is bound by the special-function
-// unit: x * sigmoid(x) through exp and a division are two of its operations per element.  sigmoid(x) =
-// 0.5 + 0.5 tanh(x / 2) needs one (tanh.approx: absolute error below 2^-10.9, i.e. 2.6e-4 of the sigmoid; the
-// BF16 rounding of the result is 2^-9 relative).  Other activations keep act_fast.
-__device__ __forceinline__ float act_one_sfu(int act, float v) {
-    if (act == MOE_ACT_SILU) {
-        float t;
-        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * v));
-        return 0.5f * v * (1.0f + t);
-    }
-    return act_fast(act, v);
-}
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -225,7 +213,7 @@ group_gemm_tc_dual_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                         float v[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            v[i] = act_one_sfu(p.activation, __uint_as_float(g[i])) * __uint_as_float(u[i]);
+                            v[i] = act_fast(p.activation, __uint_as_float(g[i])) * __uint_as_float(u[i]);
                         if (row_ok) store_row32(dst_row, col_base + c, p.N, v, vec_ok);
                     }
                 } else {

@@ -173,15 +173,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Activations of the BF16 epilogues.  One special-function operation per element: sigmoid(x) = 0.5 + 0.5 tanh(x/2)
+// and the tanh of GELU's approximation both go through tanh.approx (absolute error below 2^-10.9, i.e. 2.6e-4 on
+// the sigmoid, against the 2^-9 relative rounding of the BF16 result).  The exp-and-divide forms cost two, which
+// the kernel whose epilogue is not hidden behind MMAs (expert_tc_dual.cu) felt; every tensor-core kernel uses
+// this one function, so a layer gives the same bits whichever kernel a batch size selects.
+__device__ __forceinline__ float tanh_fast(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+    return t;
+}
 __device__ __forceinline__ float act_fast(int act, float v) {
     switch (act) {
         case MOE_ACT_SILU:
-            return __fdividef(v, 1.0f + __expf(-v));
-        case MOE_ACT_GELU_TANH: {
-            const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-            const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));  // tanh(u)
-            return 0.5f * v * (1.0f + t);
-        }
+            return 0.5f * v * (1.0f + tanh_fast(0.5f * v));
+        case MOE_ACT_GELU_TANH:
+            return 0.5f * v * (1.0f + tanh_fast(0.7978845608028654f * (v + 0.044715f * v * v * v)));
         case MOE_ACT_RELU:
             return fmaxf(v, 0.f);
         default:

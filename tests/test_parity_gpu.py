@@ -743,3 +743,22 @@ def test_seeded_sweep_of_shapes_gates_and_dtypes(block):
             run_case(T, D, H, O, E, kind, k, S, seed=7000 + 100 * block + i, std=0.1, **c)
         except AssertionError as exc:
             raise AssertionError(f"case {i} of block {block}: T={T} D={D} H={H} O={O} E={E} {kind} k={k} S={S} {c}: {exc}") from exc
+
+
+@pytest.mark.parametrize("expert_kind,activation", [("gated", "silu"), ("standard", "gelu")])
+def test_the_three_tensor_core_kernels_give_the_same_bits(expert_kind, activation, monkeypatch):
+    """Which kernel a batch gets depends on its size (rows per expert, K): the results must not.  The same layer
+    and input through the single-CTA, the CTA-pair and the two-accumulator kernel: identical outputs, bit for bit."""
+    T, D, H, O, E = 1500, 256, 512, 264, 4
+    x, w = orc.make_layer_inputs(17, T, D, H, O, E, init="normal", std=0.05, bf16=True, expert_kind=expert_kind)
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    outs = []
+    for kernel in ("0", "1", "2"):
+        monkeypatch.setenv("MOE_B200_PAIR", kernel)
+        layer = make_device_layer(w, D=D, H=H, O=O, gate=device_gate("topk", 2, 0, E), activation=activation, compute_dtype="bf16")
+        assert layer.gemm_kernel(T) == int(kernel)
+        out, _ = layer(xt.t(), training=False)
+        torch.cuda.synchronize()
+        outs.append(out.clone())
+        layer.close()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
